@@ -1,0 +1,153 @@
+/*
+ * int8kv_b200 — C ABI of the B200 (sm_100a) INT8 paged-KV decode kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides; no framework
+ * types cross this boundary.  All calls are asynchronous on `stream` (a cudaStream_t passed
+ * as void*), never synchronise the device, never allocate device memory and never throw:
+ * they return 0 or a negative INT8KV_E_* code.  The caller owns every buffer, including the
+ * split-KV workspace.  The library keeps no mutable state apart from a per-device "kernel
+ * attributes configured" flag, so it may be called from several host threads and streams.
+ *
+ * Tensor conventions (the reference prototype cjsmt/Int8-kvcache uses the same ones):
+ *   key/value (new tokens)  [T, Hkv, D]                bf16 / fp16 / fp32, any strides
+ *   key_cache/value_cache   [num_blocks, BS, Hkv, D]   int8 (or bf16/fp16 for the baseline)
+ *   slot_mapping            [T]        int32/int64, slot = block*BS + offset, slot < 0 = skip
+ *   query / out             [B, Hq, D]                 bf16 / fp16 / fp32
+ *   block_tables            [B, width] int32/int64, logical block -> physical block
+ *   seq_lens                [B]        int32/int64
+ *   k_scale / v_scale       [Hkv]      fp32
+ * Query head h reads KV head h / (Hq/Hkv).  Strides are in ELEMENTS of the tensor's dtype.
+ */
+#ifndef INT8KV_B200_H
+#define INT8KV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define INT8KV_ABI_VERSION 1
+
+/* status codes */
+#define INT8KV_OK 0
+#define INT8KV_E_NULLPTR (-1)     /* a required pointer is NULL */
+#define INT8KV_E_BAD_SHAPE (-2)   /* sizes/strides inconsistent (Hq % Hkv, negative sizes, ...) */
+#define INT8KV_E_BAD_DTYPE (-3)   /* dtype code out of range */
+#define INT8KV_E_UNSUPPORTED (-4) /* valid request that no kernel here covers */
+#define INT8KV_E_LAUNCH (-5)      /* CUDA reported an error at launch / attribute set-up */
+#define INT8KV_E_WORKSPACE (-6)   /* workspace missing or smaller than int8kv_workspace_bytes() */
+
+/* dtype codes for float tensors */
+#define INT8KV_BF16 0
+#define INT8KV_FP16 1
+#define INT8KV_FP32 2
+
+/* Bits set by a kernel in the workspace's trailing status word (see int8kv_workspace_status_offset). */
+#define INT8KV_DEV_WAIT_TIMEOUT 1u /* a bounded wait for a staged page ran out; result invalid */
+
+int int8kv_abi_version(void);
+const char* int8kv_status_str(int status);
+
+/*
+ * INT8 KV cache write.  Replaces int8_kv_cache_write and its Triton kernel
+ * (reference src/triton_ops/int8_cache_write.py:7-149): q = clamp(rint(x / max(scale,1e-6)), -127, 127)
+ * with an IEEE fp32 quotient and round-half-to-even (the rounding of the reference's own oracle,
+ * src/quant.py:37-40), stored at cache[slot / BS, slot % BS, head, :]; rows with slot < 0 are skipped and
+ * every other cache byte is left untouched.  Slots >= num_blocks*BS are skipped as well.
+ */
+int int8kv_cache_write(const void* key, const void* value, int in_dtype,
+                       int64_t num_tokens, int num_kv_heads, int head_dim,
+                       const int64_t key_strides[3], const int64_t value_strides[3],
+                       int8_t* key_cache, int8_t* value_cache,
+                       const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                       int64_t num_blocks, int block_size,
+                       const void* slot_mapping, int slot_is_i64,
+                       const float* k_scale, const float* v_scale,
+                       void* stream);
+
+/*
+ * INT8 paged decode attention.  Replaces int8_paged_attention with its V3/V4 kernels and the split-KV
+ * merge (reference src/triton_ops/int8_paged_attention.py:68-769).  out[b,h,:] = softmax(q.K^T * k_scale/sqrt(D)) .
+ * V * v_scale over the first seq_lens[b] tokens of sequence b.  A sequence with seq_len <= 0 yields zeros.
+ *   num_splits  0 = choose from the shape (int8kv_choose_splits), >= 1 = use exactly that many KV splits
+ *   max_seq_len_hint  upper bound of seq_lens used only to size the grid; <= 0 means width*BS
+ *   workspace   required when the effective split count is > 1: int8kv_workspace_bytes() bytes
+ *   quantize_q  non-zero: quantise each query head to INT8 (absmax/127, round half away from zero) before
+ *               the dot product, as the reference's QUANTIZE_Q option (:137-146)
+ */
+int int8kv_paged_attn_int8(const void* query, int q_dtype, const int64_t q_strides[3],
+                           int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                           const int8_t* key_cache, const int8_t* value_cache,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                           const float* k_scale, const float* v_scale,
+                           void* out, int out_dtype, const int64_t out_strides[3],
+                           int num_splits, void* workspace, int64_t workspace_bytes,
+                           int quantize_q, void* stream);
+
+/*
+ * BF16/FP16 paged decode attention, the same-run baseline.  Replaces bf16_paged_attention
+ * (reference src/triton_ops/bf16_paged_attention.py:9-165).  `cache_dtype` is INT8KV_BF16 or INT8KV_FP16.
+ */
+int int8kv_paged_attn_bf16(const void* query, int q_dtype, const int64_t q_strides[3],
+                           int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                           const void* key_cache, const void* value_cache, int cache_dtype,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                           void* out, int out_dtype, const int64_t out_strides[3],
+                           int num_splits, void* workspace, int64_t workspace_bytes,
+                           void* stream);
+
+/*
+ * Variants that return unmerged partial attention for a sequence-parallel split: every rank attends to its own
+ * tokens and writes rows of int8kv_partial_row_floats(D) fp32 = [out (D floats, normalised) | lse | padding] into
+ * `partial` ([B, Hq, row]); lse is the natural-log sum-exp of the scaled scores, -inf for an empty range.  The rows
+ * of all ranks, gathered into local memory, are combined by int8kv_merge_partials.  This is the split-KV step of
+ * the reference (:293-318) exposed across devices; the reference itself has no multi-GPU path.
+ */
+int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t q_strides[3],
+                           int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                           const int8_t* key_cache, const int8_t* value_cache,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                           const float* k_scale, const float* v_scale,
+                           float* partial,
+                           int num_splits, void* workspace, int64_t workspace_bytes,
+                           int quantize_q, void* stream);
+
+/*
+ * Merge `num_parts` partial results.  Replaces _merge_split_kv_kernel (reference
+ * src/triton_ops/int8_paged_attention.py:330-388): out = sum_r w_r * out_r / sum_r w_r, w_r = exp(lse_r - max lse);
+ * parts with lse = -inf are ignored; all-empty rows give zeros.  `parts` is [num_parts, rows, row_floats] fp32 with
+ * rows = B*Hq and row_floats = int8kv_partial_row_floats(D).
+ */
+int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_q_heads, int head_dim,
+                          void* out, int out_dtype, const int64_t out_strides[3], void* stream);
+
+/* Floats per partial row: D for the output, one for the lse, padded to a multiple of 4. */
+int int8kv_partial_row_floats(int head_dim);
+
+/* Bytes of split-KV workspace for `num_splits` splits (includes the trailing status word). */
+int64_t int8kv_workspace_bytes(int batch, int num_q_heads, int head_dim, int num_splits);
+
+/* Byte offset of the 32-bit device status word inside a workspace of `workspace_bytes` bytes. */
+int64_t int8kv_workspace_status_offset(int64_t workspace_bytes);
+
+/* Split count the library would pick for this shape on a device with `sm_count` SMs
+ * (re-derivation of _choose_num_splits, reference :39-49, for 148 SMs). */
+int int8kv_choose_splits(int batch, int num_kv_heads, int64_t max_seq_len, int block_size, int sm_count);
+
+/* Largest split count any entry point accepts. */
+int int8kv_max_splits(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INT8KV_B200_H */

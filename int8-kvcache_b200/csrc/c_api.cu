@@ -1,0 +1,327 @@
+// extern "C" entry points declared in include/int8kv_b200.h: argument validation, path selection
+// (TMA-tiled kernels vs the generic kernel), tensor-map construction, split-KV planning and launches.
+// Nothing here synchronises, allocates device memory or throws.
+#include <atomic>
+#include <cmath>
+#include <cstring>
+
+#include "common.cuh"
+
+using namespace int8kv;
+
+namespace {
+
+// ---- per-device facts, queried once -----------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+std::atomic<int> g_sm_count[kMaxDevices];
+
+int device_sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = g_sm_count[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  g_sm_count[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// ---- cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda) -----------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// Tensor map over a cache [num_blocks, BS, Hkv, row_bytes] viewed in bytes as
+// (byte-in-row, token-in-block, head, block) with a 128 B x 16 token box and the 128-byte swizzle.
+bool make_cache_map(CUtensorMap* map, const void* base, int elem_bytes, int D, int Hkv, int64_t num_blocks,
+                    int block_size, const int64_t st[4]) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D) * elem_bytes, static_cast<cuuint64_t>(block_size),
+                              static_cast<cuuint64_t>(Hkv), static_cast<cuuint64_t>(num_blocks)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st[1]) * elem_bytes, static_cast<cuuint64_t>(st[2]) * elem_bytes,
+                                 static_cast<cuuint64_t>(st[0]) * elem_bytes};
+  const cuuint32_t box[4] = {128, 16, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool tma_friendly(const void* base, int elem_bytes, const int64_t st[4], int64_t num_blocks) {
+  if (reinterpret_cast<uintptr_t>(base) & 15u) return false;
+  if (st[3] != 1) return false;
+  for (int i = 0; i < 3; ++i) {
+    const int64_t bytes = st[i] * elem_bytes;
+    if (bytes <= 0 || (bytes & 15) != 0 || bytes >= (int64_t(1) << 40)) return false;
+  }
+  return num_blocks > 0 && num_blocks < (int64_t(1) << 31);
+}
+
+bool valid_float_dtype(int d) { return d == INT8KV_BF16 || d == INT8KV_FP16 || d == INT8KV_FP32; }
+
+int partial_row_floats(int D) { return ((D + 1) + 3) / 4 * 4; }
+
+int64_t ws_bytes(int B, int Hq, int D, int S) {
+  int64_t rows = S > 1 ? static_cast<int64_t>(S) * B * Hq * partial_row_floats(D) * 4 : 0;
+  return rows + 16;  // trailing 16 bytes hold the status word
+}
+
+int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
+  (void)block_size;
+  if (B <= 0 || Hkv <= 0 || max_seq <= 0) return 1;
+  const int64_t tiles = (max_seq + 15) / 16;
+  const int64_t items = static_cast<int64_t>(B) * Hkv;
+  // One warp serves one (sequence, kv head, split).  Aim at about 12 warps per SM, never fewer than
+  // 8 tiles (128 tokens, 32 KB of INT8 K+V) per split so that the partial rows stay a small fraction of the
+  // traffic, and leave unsplit whatever already fills the machine.
+  const int64_t want = static_cast<int64_t>(sm_count) * 12;
+  if (items >= want) return 1;
+  int64_t s = (want + items - 1) / items;
+  const int64_t by_len = tiles / 8;
+  if (s > by_len) s = by_len;
+  if (s > kMaxSplits) s = kMaxSplits;
+  if (s < 1) s = 1;
+  return static_cast<int>(s);
+}
+
+struct AttnCall {
+  const void* query; int q_dtype; const int64_t* q_st;
+  int B, Hq, Hkv, D;
+  const void* kc; const void* vc; int cache_kind; const int64_t* kc_st; const int64_t* vc_st;
+  int64_t num_blocks; int block_size;
+  const void* bt; int bt_is_i64; const int64_t* bt_st; int64_t bt_width;
+  const void* sl; int sl_is_i64; int64_t max_seq_hint;
+  const float* k_scale; const float* v_scale;
+  void* out; int out_dtype; const int64_t* o_st;
+  float* partial_out;  // non-null: emit merged partial rows instead of `out`
+  int num_splits; void* ws; int64_t ws_bytes;
+  int quantize_q; cudaStream_t stream;
+};
+
+int run_attention(const AttnCall& a) {
+  if (a.B < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.D <= 0 || a.block_size <= 0 || a.num_blocks < 0 || a.bt_width < 0)
+    return INT8KV_E_BAD_SHAPE;
+  if (a.Hq % a.Hkv != 0) return INT8KV_E_BAD_SHAPE;
+  if (a.num_splits < 0 || a.num_splits > kMaxSplits) return INT8KV_E_BAD_SHAPE;
+  if (!valid_float_dtype(a.q_dtype)) return INT8KV_E_BAD_DTYPE;
+  if (a.partial_out == nullptr && !valid_float_dtype(a.out_dtype)) return INT8KV_E_BAD_DTYPE;
+  if (a.B == 0) return INT8KV_OK;
+  if (!a.query || !a.kc || !a.vc || !a.bt || !a.sl || !a.q_st || !a.kc_st || !a.vc_st || !a.bt_st)
+    return INT8KV_E_NULLPTR;
+  if (a.partial_out == nullptr && (!a.out || !a.o_st)) return INT8KV_E_NULLPTR;
+  if (a.cache_kind == kCacheInt8 && (!a.k_scale || !a.v_scale)) return INT8KV_E_NULLPTR;
+  if (a.kc_st[3] != 1 || a.vc_st[3] != 1) return INT8KV_E_UNSUPPORTED;  // the reference asserts unit last stride too
+
+  const int G = a.Hq / a.Hkv;
+  const int sm = device_sm_count();
+  int64_t max_seq = a.max_seq_hint > 0 ? a.max_seq_hint : a.bt_width * a.block_size;
+  if (max_seq > a.bt_width * a.block_size) max_seq = a.bt_width * a.block_size;
+  int S = a.num_splits > 0 ? a.num_splits : choose_splits(a.B, a.Hkv, max_seq, a.block_size, sm);
+  // more splits than 16-token tiles only produces empty parts
+  const int64_t tiles = (max_seq + 15) / 16;
+  if (S > tiles) S = tiles > 0 ? static_cast<int>(tiles) : 1;
+
+  const int rf = partial_row_floats(a.D);
+  const int64_t need = ws_bytes(a.B, a.Hq, a.D, S);
+  unsigned int* status = nullptr;
+  if (a.ws != nullptr && a.ws_bytes >= 16)
+    status = reinterpret_cast<unsigned int*>(static_cast<char*>(a.ws) + int8kv_workspace_status_offset(a.ws_bytes));
+  if (S > 1) {
+    if (a.ws == nullptr || a.ws_bytes < need) return INT8KV_E_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(a.ws) & 15u) return INT8KV_E_WORKSPACE;
+  }
+
+  AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = a.query; p.q_dtype = a.q_dtype;
+  for (int i = 0; i < 3; ++i) p.q_st[i] = a.q_st[i];
+  p.B = a.B; p.Hq = a.Hq; p.Hkv = a.Hkv; p.G = G; p.D = a.D;
+  p.kc = a.kc; p.vc = a.vc; p.cache_kind = a.cache_kind;
+  for (int i = 0; i < 4; ++i) { p.kc_st[i] = a.kc_st[i]; p.vc_st[i] = a.vc_st[i]; }
+  p.num_blocks = a.num_blocks; p.block_size = a.block_size;
+  p.tiles_per_block = a.block_size / 16;
+  p.bt = a.bt; p.bt_is_i64 = a.bt_is_i64; p.bt_st[0] = a.bt_st[0]; p.bt_st[1] = a.bt_st[1]; p.bt_width = a.bt_width;
+  p.sl = a.sl; p.sl_is_i64 = a.sl_is_i64;
+  p.k_scale = a.k_scale; p.v_scale = a.v_scale;
+  p.out = a.out; p.out_dtype = a.out_dtype;
+  if (a.o_st) for (int i = 0; i < 3; ++i) p.o_st[i] = a.o_st[i];
+  p.num_splits = S;
+  p.row_floats = rf;
+  p.quantize_q = a.quantize_q;
+  p.sm_scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(a.D)));
+  p.status = status;
+  if (S > 1) p.part = reinterpret_cast<float*>(a.ws);
+  else p.part = a.partial_out;  // null for the ordinary call: write `out` directly
+
+  const int esz = a.cache_kind == kCacheInt8 ? 1 : 2;
+  const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
+                     tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
+                     (rf % 4 == 0);
+  int rc;
+  if (tiled) {
+    alignas(64) CUtensorMap tmK, tmV;
+    if (!make_cache_map(&tmK, a.kc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.kc_st) ||
+        !make_cache_map(&tmV, a.vc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.vc_st))
+      return INT8KV_E_LAUNCH;
+    rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, a.stream)
+                                    : launch_attn_tiled_f16(p, tmK, tmV, a.stream);
+  } else {
+    if (a.cache_kind != kCacheInt8 && a.quantize_q) return INT8KV_E_UNSUPPORTED;
+    rc = launch_attn_generic(p, a.stream);
+  }
+  if (rc != INT8KV_OK || S == 1) return rc;
+
+  MergeParams m;
+  std::memset(&m, 0, sizeof(m));
+  m.parts = p.part; m.R = S; m.rows = static_cast<int64_t>(a.B) * a.Hq; m.Hq = a.Hq; m.D = a.D; m.row_floats = rf;
+  m.out = a.out; m.out_dtype = a.out_dtype;
+  if (a.o_st) for (int i = 0; i < 3; ++i) m.o_st[i] = a.o_st[i];
+  m.part_out = a.partial_out;
+  return launch_merge(m, a.stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+int int8kv_abi_version(void) { return INT8KV_ABI_VERSION; }
+
+const char* int8kv_status_str(int status) {
+  switch (status) {
+    case INT8KV_OK: return "ok";
+    case INT8KV_E_NULLPTR: return "null pointer argument";
+    case INT8KV_E_BAD_SHAPE: return "inconsistent shape or stride";
+    case INT8KV_E_BAD_DTYPE: return "unknown dtype code";
+    case INT8KV_E_UNSUPPORTED: return "unsupported configuration";
+    case INT8KV_E_LAUNCH: return "CUDA launch or set-up error";
+    case INT8KV_E_WORKSPACE: return "split-KV workspace missing, misaligned or too small";
+    default: return "unknown status";
+  }
+}
+
+int int8kv_partial_row_floats(int head_dim) { return partial_row_floats(head_dim); }
+
+int64_t int8kv_workspace_bytes(int batch, int num_q_heads, int head_dim, int num_splits) {
+  if (batch < 0 || num_q_heads <= 0 || head_dim <= 0 || num_splits < 0) return -1;
+  return ws_bytes(batch, num_q_heads, head_dim, num_splits);
+}
+
+int64_t int8kv_workspace_status_offset(int64_t workspace_bytes) {
+  return workspace_bytes >= 16 ? ((workspace_bytes - 16) & ~int64_t(15)) : 0;
+}
+
+int int8kv_choose_splits(int batch, int num_kv_heads, int64_t max_seq_len, int block_size, int sm_count) {
+  return choose_splits(batch, num_kv_heads, max_seq_len, block_size, sm_count > 0 ? sm_count : 148);
+}
+
+int int8kv_max_splits(void) { return kMaxSplits; }
+
+int int8kv_cache_write(const void* key, const void* value, int in_dtype, int64_t num_tokens, int num_kv_heads,
+                       int head_dim, const int64_t key_strides[3], const int64_t value_strides[3],
+                       int8_t* key_cache, int8_t* value_cache, const int64_t key_cache_strides[4],
+                       const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                       const void* slot_mapping, int slot_is_i64, const float* k_scale, const float* v_scale,
+                       void* stream) {
+  if (num_tokens < 0 || num_kv_heads <= 0 || head_dim <= 0 || num_blocks < 0 || block_size <= 0)
+    return INT8KV_E_BAD_SHAPE;
+  if (!valid_float_dtype(in_dtype)) return INT8KV_E_BAD_DTYPE;
+  if (num_tokens == 0) return INT8KV_OK;
+  if (!key || !value || !key_cache || !value_cache || !slot_mapping || !k_scale || !v_scale || !key_strides ||
+      !value_strides || !key_cache_strides || !value_cache_strides)
+    return INT8KV_E_NULLPTR;
+  WriteParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.key = key; p.value = value; p.in_dtype = in_dtype;
+  p.T = num_tokens; p.Hkv = num_kv_heads; p.D = head_dim;
+  for (int i = 0; i < 3; ++i) { p.k_st[i] = key_strides[i]; p.v_st[i] = value_strides[i]; }
+  p.kc = key_cache; p.vc = value_cache;
+  for (int i = 0; i < 4; ++i) { p.kc_st[i] = key_cache_strides[i]; p.vc_st[i] = value_cache_strides[i]; }
+  p.num_slots = num_blocks * block_size;
+  p.block_size = block_size;
+  p.slots = slot_mapping; p.slot_is_i64 = slot_is_i64;
+  p.k_scale = k_scale; p.v_scale = v_scale;
+  return launch_cache_write(p, device_sm_count(), static_cast<cudaStream_t>(stream));
+}
+
+int int8kv_paged_attn_int8(const void* query, int q_dtype, const int64_t q_strides[3], int batch, int num_q_heads,
+                           int num_kv_heads, int head_dim, const int8_t* key_cache, const int8_t* value_cache,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size, const void* block_tables, int bt_is_i64,
+                           const int64_t bt_strides[2], int64_t bt_width, const void* seq_lens, int sl_is_i64,
+                           int64_t max_seq_len_hint, const float* k_scale, const float* v_scale, void* out,
+                           int out_dtype, const int64_t out_strides[3], int num_splits, void* workspace,
+                           int64_t workspace_bytes, int quantize_q, void* stream) {
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             k_scale, v_scale, out, out_dtype, out_strides, nullptr,
+             num_splits, workspace, workspace_bytes, quantize_q, static_cast<cudaStream_t>(stream)};
+  return run_attention(a);
+}
+
+int int8kv_paged_attn_bf16(const void* query, int q_dtype, const int64_t q_strides[3], int batch, int num_q_heads,
+                           int num_kv_heads, int head_dim, const void* key_cache, const void* value_cache,
+                           int cache_dtype, const int64_t key_cache_strides[4],
+                           const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint, void* out, int out_dtype,
+                           const int64_t out_strides[3], int num_splits, void* workspace, int64_t workspace_bytes,
+                           void* stream) {
+  if (cache_dtype != INT8KV_BF16 && cache_dtype != INT8KV_FP16) return INT8KV_E_BAD_DTYPE;
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, cache_dtype == INT8KV_BF16 ? kCacheBf16 : kCacheFp16,
+             key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             nullptr, nullptr, out, out_dtype, out_strides, nullptr,
+             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+  return run_attention(a);
+}
+
+int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t q_strides[3], int batch,
+                                   int num_q_heads, int num_kv_heads, int head_dim, const int8_t* key_cache,
+                                   const int8_t* value_cache, const int64_t key_cache_strides[4],
+                                   const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                                   const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                                   int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                                   const float* k_scale, const float* v_scale, float* partial, int num_splits,
+                                   void* workspace, int64_t workspace_bytes, int quantize_q, void* stream) {
+  if (partial == nullptr) return INT8KV_E_NULLPTR;
+  if (reinterpret_cast<uintptr_t>(partial) & 15u) return INT8KV_E_BAD_SHAPE;
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             k_scale, v_scale, nullptr, INT8KV_FP32, nullptr, partial,
+             num_splits, workspace, workspace_bytes, quantize_q, static_cast<cudaStream_t>(stream)};
+  return run_attention(a);
+}
+
+int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_q_heads, int head_dim, void* out,
+                          int out_dtype, const int64_t out_strides[3], void* stream) {
+  if (num_parts <= 0 || batch < 0 || num_q_heads <= 0 || head_dim <= 0) return INT8KV_E_BAD_SHAPE;
+  if (!valid_float_dtype(out_dtype)) return INT8KV_E_BAD_DTYPE;
+  if (batch == 0) return INT8KV_OK;
+  if (!parts || !out || !out_strides) return INT8KV_E_NULLPTR;
+  if (reinterpret_cast<uintptr_t>(parts) & 15u) return INT8KV_E_BAD_SHAPE;
+  MergeParams m;
+  std::memset(&m, 0, sizeof(m));
+  m.parts = parts; m.R = num_parts; m.rows = static_cast<int64_t>(batch) * num_q_heads; m.Hq = num_q_heads;
+  m.D = head_dim; m.row_floats = partial_row_floats(head_dim);
+  m.out = out; m.out_dtype = out_dtype;
+  for (int i = 0; i < 3; ++i) m.o_st[i] = out_strides[i];
+  m.part_out = nullptr;
+  return launch_merge(m, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,85 @@
+// Parameter blocks and host launchers shared by the kernel files and the C-ABI layer.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace int8kv {
+
+struct WriteParams {
+  const void* key;
+  const void* value;
+  int in_dtype;
+  int64_t T;
+  int Hkv, D;
+  int64_t k_st[3], v_st[3];
+  int8_t* kc;
+  int8_t* vc;
+  int64_t kc_st[4], vc_st[4];
+  int64_t num_slots;
+  int block_size;
+  const void* slots;
+  int slot_is_i64;
+  const float* k_scale;
+  const float* v_scale;
+};
+
+// cache element kinds
+enum CacheKind { kCacheInt8 = 0, kCacheBf16 = 1, kCacheFp16 = 2 };
+
+struct AttnParams {
+  const void* q;
+  int q_dtype;
+  int64_t q_st[3];
+  int B, Hq, Hkv, G, D;
+  const void* kc;  // cache base pointers (used directly by the generic kernel; the tiled kernels use tensor maps)
+  const void* vc;
+  int cache_kind;
+  int64_t kc_st[4];
+  int64_t vc_st[4];
+  int64_t num_blocks;
+  int block_size;
+  int tiles_per_block;  // block_size / 16 (tiled kernels)
+  const void* bt;
+  int bt_is_i64;
+  int64_t bt_st[2];
+  int64_t bt_width;
+  const void* sl;
+  int sl_is_i64;
+  const float* k_scale;  // null for float caches
+  const float* v_scale;
+  void* out;  // final output, used when `part` is null
+  int out_dtype;
+  int64_t o_st[3];
+  int num_splits;
+  float* part;  // [num_splits, B*Hq, row_floats] partial rows; null = write `out` directly (num_splits must be 1)
+  int row_floats;
+  int quantize_q;
+  float sm_scale_log2;   // log2(e) / sqrt(D)
+  unsigned int* status;  // device status word, may be null
+};
+
+struct MergeParams {
+  const float* parts;  // [R, rows, row_floats]
+  int R;
+  int64_t rows;  // B*Hq
+  int Hq, D;
+  int row_floats;
+  void* out;  // final output (dtype/strides) when part_out is null
+  int out_dtype;
+  int64_t o_st[3];
+  float* part_out;  // [rows, row_floats] merged partial rows (out | lse), or null
+};
+
+int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
+int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream);
+int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream);
+int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
+int launch_merge(const MergeParams& p, cudaStream_t stream);
+
+// resident warps per SM the tiled int8 kernel is sized for (used by the split heuristic)
+constexpr int kTiledWarpsPerCta = 4;
+constexpr int kMaxSplits = 128;
+
+}  // namespace int8kv

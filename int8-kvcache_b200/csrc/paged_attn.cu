@@ -1,0 +1,760 @@
+// Paged decode attention for sm_100a over an INT8 (or bf16/fp16) block cache [num_blocks, BS, Hkv, D].
+//
+// Work decomposition.  The unit of work is one WARP serving one (sequence, KV head, KV split): it reads every
+// 16-token tile of that head's K and V exactly once and serves all query heads of the GQA group from that single
+// read (group <= 8 heads sit on the N=8 side of the tensor-core tile, so 7 heads cost 8/7 padding, not 16/7).  A
+// CTA is four such warps working on consecutive items (with Hkv = 4: the four KV heads of the same pages, whose
+// rows interleave in memory, so one CTA consumes whole contiguous 8 KB pages).  Warps never synchronise with each
+// other; there is no __syncthreads in the kernel.
+//
+// Data movement.  Each warp runs its own NST-deep ring of shared-memory stages filled by TMA: one
+// cp.async.bulk.tensor tile load per 16x128-byte K tile and V tile, issued by lane 0, completion counted on an
+// mbarrier per stage.  The tensor map views the cache as (bytes-in-row, token-in-block, head, block) and applies
+// the 128-byte swizzle, which makes both access patterns below bank-conflict free.  Block ids come from
+// block_tables through a register window (32 ids per load, next window prefetched).  Waits are bounded: if a
+// stage never arrives the warp sets a status bit, drains what it issued and returns.
+//
+// Math (INT8 cache).  S^T = K . Q^T with tokens on M (16 per tile), heads on N (8), dims on K, as fp16 MMA
+// m16n8k16 with fp32 accumulation: int8 -> fp16 is exact (bytes are spliced into 0x64xx = 1024+u and 1152 is
+// subtracted), Q is held as fp16 B fragments whose k-order is permuted so that each lane's A operand is 32
+// consecutive bytes of a K row.  Online softmax runs in the log2 domain on the C fragment (max via three shuffles,
+// the row sum is reduced once at the end).  P^T is obtained from the C fragment with movmatrix (8x8 transpose) and
+// O^T = V^T . P^T puts dims on M: the V^T A fragment needs pairs of tokens at one dim, produced by byte
+// interleaving (prmt) of 16-byte row pieces on the way to fp16.  v_scale and 1/l are applied once in the epilogue.
+#include "common.cuh"
+
+namespace int8kv {
+
+constexpr int kTile = 16;  // tokens per tile
+
+// ---------------------------------------------------------------------------------------------
+// Per-warp TMA ring over the tiles [t0, t1) of one (sequence, kv head).
+// ---------------------------------------------------------------------------------------------
+template <int NST, int STAGE_BYTES, int LOADS_PER_TENSOR>
+struct TileRing {
+  uint32_t stage0;  // shared address of stage 0 (1024-byte aligned)
+  uint32_t bar0;    // shared address of the first mbarrier
+  const CUtensorMap* tmK;
+  const CUtensorMap* tmV;
+  const void* bt_row;  // block table row of this sequence
+  int bt_is_i64;
+  int64_t bt_stride;
+  int64_t bt_limit;  // number of valid entries in the row
+  int tpb;           // tiles per cache block
+  int head;
+  int t0;   // first tile
+  int lb0;  // logical block of tile t0
+  int cur_win;
+  int bt_cur, bt_next;
+  int lane;
+
+  __device__ __forceinline__ int load_window(int win) const {
+    const int64_t lb = static_cast<int64_t>(lb0) + static_cast<int64_t>(win) * 32 + lane;
+    if (lb >= bt_limit) return -1;  // out-of-range ids make TMA zero-fill; such tiles are never consumed
+    return static_cast<int>(load_index(bt_row, bt_is_i64, lb * bt_stride));
+  }
+
+  __device__ __forceinline__ void init(int lane_) {
+    lane = lane_;
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < NST; ++s) mbar_init(bar0 + 8 * s, 1);
+      mbar_fence_init();
+    }
+    cur_win = 0;
+    bt_cur = load_window(0);
+    bt_next = load_window(1);
+    __syncwarp();
+  }
+
+  // Issue the loads of tile ordinal i (tile t0 + i) into stage i % NST.  Called by all lanes, in order of i.
+  __device__ __forceinline__ void issue(int i) {
+    const int tau = t0 + i;
+    const int lb = tau / tpb;
+    const int sub = tau - lb * tpb;
+    const int idx = lb - lb0;
+    const int win = idx >> 5;
+    if (win != cur_win) {
+      bt_cur = bt_next;
+      cur_win = win;
+      bt_next = load_window(win + 1);
+    }
+    const int blk = __shfl_sync(kFull, bt_cur, idx & 31);
+    if (lane == 0) {
+      const int st = i % NST;
+      const uint32_t bar = bar0 + 8 * st;
+      const uint32_t dst = stage0 + st * STAGE_BYTES;
+      mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+      for (int x = 0; x < LOADS_PER_TENSOR; ++x)
+        tma_load_4d(dst + x * 2048, tmK, bar, x * 128, sub * kTile, head, blk);
+#pragma unroll
+      for (int x = 0; x < LOADS_PER_TENSOR; ++x)
+        tma_load_4d(dst + (LOADS_PER_TENSOR + x) * 2048, tmV, bar, x * 128, sub * kTile, head, blk);
+    }
+  }
+
+  // Wait for tile ordinal i; false if the bounded wait ran out on any lane.
+  __device__ __forceinline__ bool wait(int i, uint32_t limit = kWaitSpinLimit) const {
+    const bool ok = mbar_wait_bounded(bar0 + 8 * (i % NST), (i / NST) & 1, limit);
+    return __all_sync(kFull, ok);
+  }
+
+  __device__ __forceinline__ uint32_t stage(int i) const { return stage0 + (i % NST) * STAGE_BYTES; }
+};
+
+struct ItemCoord {
+  int b, h, c;       // sequence, kv head, split
+  int seq_len;       // tokens of the sequence (clamped to what the table can address)
+  int t0, t1;        // tile range of this split
+};
+
+__device__ __forceinline__ bool decode_item(const AttnParams& p, int64_t item, ItemCoord& it) {
+  const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  if (item >= total) return false;
+  it.h = static_cast<int>(item % p.Hkv);
+  const int64_t r = item / p.Hkv;
+  it.c = static_cast<int>(r % p.num_splits);
+  it.b = static_cast<int>(r / p.num_splits);
+  int64_t sl = load_index(p.sl, p.sl_is_i64, it.b);
+  const int64_t cap = p.bt_width * p.block_size;
+  if (sl > cap) sl = cap;
+  if (sl < 0) sl = 0;
+  it.seq_len = static_cast<int>(sl);
+  const int ntiles = (it.seq_len + kTile - 1) / kTile;
+  const int per = (ntiles + p.num_splits - 1) / p.num_splits;
+  it.t0 = it.c * per;
+  it.t1 = min(it.t0 + per, ntiles);
+  return true;
+}
+
+// Result of an empty tile range: zeros to `out` (direct mode) or lse = -inf (partial mode).
+__device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord& it, int lane) {
+  if (p.part == nullptr) {
+    for (int hg = 0; hg < p.G; ++hg) {
+      const int hq = it.h * p.G + hg;
+      for (int d = lane; d < p.D; d += kWarp)
+        store_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], 0.f);
+    }
+  } else if (lane < p.G) {
+    const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + it.h * p.G + lane;
+    p.part[row * p.row_floats + p.D] = -INFINITY;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// INT8 cache, D = 128, group <= 8
+// ---------------------------------------------------------------------------------------------
+template <int NST>
+__global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp)
+paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const AttnParams p) {
+  constexpr int kStage = 4096;  // 16x128 K bytes + 16x128 V bytes
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  ItemCoord it;
+  if (!decode_item(p, static_cast<int64_t>(blockIdx.x) * kTiledWarpsPerCta + warp, it)) return;
+  if (it.t0 >= it.t1) {
+    write_empty(p, it, lane);
+    return;
+  }
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  TileRing<NST, kStage, 1> ring;
+  ring.stage0 = smem_base + warp * (NST * kStage);
+  ring.bar0 = smem_base + kTiledWarpsPerCta * NST * kStage + warp * (NST * 8);
+  ring.tmK = &tmK;
+  ring.tmV = &tmV;
+  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
+  ring.bt_is_i64 = p.bt_is_i64;
+  ring.bt_stride = p.bt_st[1];
+  ring.bt_limit = p.bt_width;
+  ring.tpb = p.tiles_per_block;
+  ring.head = it.h;
+  ring.t0 = it.t0;
+  ring.lb0 = it.t0 / p.tiles_per_block;
+  if (lane == 0) {
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  ring.init(lane);
+
+  const int n = it.t1 - it.t0;
+  const int pre = n < NST ? n : NST;
+  for (int i = 0; i < pre; ++i) ring.issue(i);
+
+  // ---- Q fragments: lane (g, t) holds head g of the group, dims [32t, 32t+32) as 16 half2 -------------
+  uint32_t qf[16];
+  float q_mul = 1.f;  // per-head multiplier of the raw dot product (query quantisation scale)
+  {
+    float qv[32];
+    const int hq = it.h * p.G + g;
+    if (g < p.G) {
+      const int64_t base = it.b * p.q_st[0] + hq * p.q_st[1];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) qv[i] = load_as_float(p.q, p.q_dtype, base + (32 * t + i) * p.q_st[2]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) qv[i] = 0.f;
+    }
+    if (p.quantize_q) {
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+      const float qs = fmaxf(amax / 127.f, 1e-6f);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float s = qv[i] / qs;
+        const float r = s >= 0.f ? floorf(s + 0.5f) : -floorf(-s + 0.5f);  // half away from zero
+        qv[i] = fminf(fmaxf(r, -127.f), 127.f);
+      }
+      q_mul = qs;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qf[i] = pack_half2(qv[2 * i], qv[2 * i + 1]);
+  }
+  // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
+  const float kmul = fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
+  const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
+  const float sc1 = kmul * __shfl_sync(kFull, q_mul, (2 * t + 1) * 4);
+
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  bool timed_out = false;
+  int i = 0;
+  for (; i < n; ++i) {
+    if (!ring.wait(i)) {
+      timed_out = true;
+      break;
+    }
+    const uint32_t kb = ring.stage(i);
+    const uint32_t vb = kb + 2048;
+
+    // ---- S^T = K . Q^T ------------------------------------------------------------------------------
+    uint32_t ka[8], kc[8];
+    {
+      const uint4 a0 = lds128(kb + swz128(g, 2 * t)), a1 = lds128(kb + swz128(g, 2 * t + 1));
+      const uint4 c0 = lds128(kb + swz128(g + 8, 2 * t)), c1 = lds128(kb + swz128(g + 8, 2 * t + 1));
+      ka[0] = a0.x; ka[1] = a0.y; ka[2] = a0.z; ka[3] = a0.w; ka[4] = a1.x; ka[5] = a1.y; ka[6] = a1.z; ka[7] = a1.w;
+      kc[0] = c0.x; kc[1] = c0.y; kc[2] = c0.z; kc[3] = c0.w; kc[4] = c1.x; kc[5] = c1.y; kc[6] = c1.z; kc[7] = c1.w;
+    }
+    // V pieces are requested now so that their latency hides under the score phase
+    uint4 vx[4];
+    vx[0] = lds128(vb + swz128(2 * t, g));
+    vx[1] = lds128(vb + swz128(2 * t + 1, g));
+    vx[2] = lds128(vb + swz128(2 * t + 8, g));
+    vx[3] = lds128(vb + swz128(2 * t + 9, g));
+
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const uint32_t wa = ka[s] ^ 0x80808080u, wc = kc[s] ^ 0x80808080u;
+      const uint32_t a0 = u8pair_to_half2(wa, 0x4140u), a2 = u8pair_to_half2(wa, 0x4342u);
+      const uint32_t a1 = u8pair_to_half2(wc, 0x4140u), a3 = u8pair_to_half2(wc, 0x4342u);
+      if (s & 1) mma_f16(sb, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
+      else mma_f16(sa, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
+    }
+
+    // ---- online softmax on the C fragment: rows = tokens g / g+8, cols = heads 2t / 2t+1 ---------------
+    const int tok0 = (it.t0 + i) * kTile + g;
+    float v0 = (sa[0] + sb[0]) * sc0, v1 = (sa[1] + sb[1]) * sc1;
+    float v2 = (sa[2] + sb[2]) * sc0, v3 = (sa[3] + sb[3]) * sc1;
+    if (tok0 >= it.seq_len) v0 = v1 = -INFINITY;
+    if (tok0 + 8 >= it.seq_len) v2 = v3 = -INFINITY;
+    float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 4));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 4));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 8));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 8));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 16));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 16));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    if (__any_sync(kFull, (mn0 != m0) || (mn1 != m1))) {
+      const float al0 = exp2_fast(m0 - mn0), al1 = exp2_fast(m1 - mn1);
+      l0 *= al0;
+      l1 *= al1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j][0] *= al0; acc[j][1] *= al1; acc[j][2] *= al0; acc[j][3] *= al1;
+      }
+      m0 = mn0;
+      m1 = mn1;
+    }
+    const float p0 = exp2_fast(v0 - m0), p1 = exp2_fast(v1 - m1);
+    const float p2 = exp2_fast(v2 - m0), p3 = exp2_fast(v3 - m1);
+    l0 += p0 + p2;
+    l1 += p1 + p3;
+    // P^T as the B operand: (tokens 2t,2t+1 | head g) and (tokens 2t+8,2t+9 | head g)
+    const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
+
+    // ---- O^T += V^T . P^T : rows = dims (16g+2j, 16g+2j+1), k = tokens, cols = heads ----------------------
+    const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&vx[0]);
+    const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&vx[1]);
+    const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&vx[2]);
+    const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&vx[3]);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t x0 = w0[c] ^ 0x80808080u, x1 = w1[c] ^ 0x80808080u;
+      const uint32_t x2 = w2[c] ^ 0x80808080u, x3 = w3[c] ^ 0x80808080u;
+      const uint32_t lo01 = prmt(x0, x1, 0x5140u), hi01 = prmt(x0, x1, 0x7362u);
+      const uint32_t lo23 = prmt(x2, x3, 0x5140u), hi23 = prmt(x2, x3, 0x7362u);
+      mma_f16(acc[2 * c], u8pair_to_half2(lo01, 0x4140u), u8pair_to_half2(lo01, 0x4342u),
+              u8pair_to_half2(lo23, 0x4140u), u8pair_to_half2(lo23, 0x4342u), pb0, pb1);
+      mma_f16(acc[2 * c + 1], u8pair_to_half2(hi01, 0x4140u), u8pair_to_half2(hi01, 0x4342u),
+              u8pair_to_half2(hi23, 0x4140u), u8pair_to_half2(hi23, 0x4342u), pb0, pb1);
+    }
+
+    __syncwarp();  // every lane has consumed the stage before lane 0 refills it
+    if (i + NST < n) ring.issue(i + NST);
+  }
+
+  if (timed_out) {
+    if (lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
+    // drain the loads that were already issued, again with a limit, so that none lands after this warp left
+    const int issued = (i + NST < n) ? i + NST : n;
+    for (int j = i + 1; j < issued; ++j) ring.wait(j, 1u << 16);
+    return;
+  }
+
+  // ---- epilogue: reduce the row sums over the token lanes, normalise, apply v_scale ----------------------
+  l0 += __shfl_xor_sync(kFull, l0, 4);
+  l1 += __shfl_xor_sync(kFull, l1, 4);
+  l0 += __shfl_xor_sync(kFull, l0, 8);
+  l1 += __shfl_xor_sync(kFull, l1, 8);
+  l0 += __shfl_xor_sync(kFull, l0, 16);
+  l1 += __shfl_xor_sync(kFull, l1, 16);
+  const float vs = fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int hg = 2 * t + e;
+    if (hg >= p.G) continue;
+    const int hq = it.h * p.G + hg;
+    const float l = e ? l1 : l0;
+    const float m = e ? m1 : m0;
+    const float inv = l > 0.f ? vs / l : 0.f;
+    float o[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[2 * j] = acc[j][e] * inv;
+      o[2 * j + 1] = acc[j][e + 2] * inv;
+    }
+    if (p.part == nullptr) {
+      const int64_t base = it.b * p.o_st[0] + hq * p.o_st[1];
+#pragma unroll
+      for (int d = 0; d < 16; ++d) store_from_float(p.out, p.out_dtype, base + (16 * g + d) * p.o_st[2], o[d]);
+    } else {
+      const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + hq;
+      float4* dst = reinterpret_cast<float4*>(p.part + row * p.row_floats + 16 * g);
+#pragma unroll
+      for (int d = 0; d < 4; ++d) dst[d] = make_float4(o[4 * d], o[4 * d + 1], o[4 * d + 2], o[4 * d + 3]);
+      if (g == 0) p.part[row * p.row_floats + p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// bf16 / fp16 cache, D = 128, group <= 8: same ring, fragments straight from shared memory with ldmatrix
+// ---------------------------------------------------------------------------------------------
+template <bool IS_BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  return IS_BF16 ? pack_bf162(lo, hi) : pack_half2(lo, hi);
+}
+template <bool IS_BF16>
+__device__ __forceinline__ void mma16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (IS_BF16) mma_bf16(d, a[0], a[1], a[2], a[3], b0, b1);
+  else mma_f16(d, a[0], a[1], a[2], a[3], b0, b1);
+}
+
+template <int NST, bool IS_BF16>
+__global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp)
+paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                      const AttnParams p) {
+  constexpr int kStage = 8192;  // K: two 16x128-byte halves (dims 0-63, 64-127), then V likewise
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  ItemCoord it;
+  if (!decode_item(p, static_cast<int64_t>(blockIdx.x) * kTiledWarpsPerCta + warp, it)) return;
+  if (it.t0 >= it.t1) {
+    write_empty(p, it, lane);
+    return;
+  }
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  TileRing<NST, kStage, 2> ring;
+  ring.stage0 = smem_base + warp * (NST * kStage);
+  ring.bar0 = smem_base + kTiledWarpsPerCta * NST * kStage + warp * (NST * 8);
+  ring.tmK = &tmK;
+  ring.tmV = &tmV;
+  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
+  ring.bt_is_i64 = p.bt_is_i64;
+  ring.bt_stride = p.bt_st[1];
+  ring.bt_limit = p.bt_width;
+  ring.tpb = p.tiles_per_block;
+  ring.head = it.h;
+  ring.t0 = it.t0;
+  ring.lb0 = it.t0 / p.tiles_per_block;
+  if (lane == 0) {
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  ring.init(lane);
+
+  const int n = it.t1 - it.t0;
+  const int pre = n < NST ? n : NST;
+  for (int i = 0; i < pre; ++i) ring.issue(i);
+
+  // Q as B fragments: step s covers dims 16s..16s+15; lane (g,t) holds head g, dims 16s+2t,+1 and 16s+8+2t,+1
+  uint32_t qf[16];
+  {
+    const int hq = it.h * p.G + g;
+    const int64_t base = it.b * p.q_st[0] + hq * p.q_st[1];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      float a = 0.f, b = 0.f, c = 0.f, d = 0.f;
+      if (g < p.G) {
+        a = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t) * p.q_st[2]);
+        b = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t + 1) * p.q_st[2]);
+        c = load_as_float(p.q, p.q_dtype, base + (16 * s + 8 + 2 * t) * p.q_st[2]);
+        d = load_as_float(p.q, p.q_dtype, base + (16 * s + 9 + 2 * t) * p.q_st[2]);
+      }
+      qf[2 * s] = pack16<IS_BF16>(a, b);
+      qf[2 * s + 1] = pack16<IS_BF16>(c, d);
+    }
+  }
+  const float sc = p.sm_scale_log2;
+
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  // ldmatrix lane roles: matrix mi = lane / 8, row r = lane % 8
+  const int mi = lane >> 3, r = lane & 7;
+  const int k_tok = r + 8 * (mi & 1), k_chunk = mi >> 1;   // K (non-transposed): matrices (tok lo/hi, chunk +0/+1)
+  const int v_tok = r + 8 * (mi >> 1), v_chunk = mi & 1;   // V (transposed)
+
+  bool timed_out = false;
+  int i = 0;
+  for (; i < n; ++i) {
+    if (!ring.wait(i)) {
+      timed_out = true;
+      break;
+    }
+    const uint32_t kb = ring.stage(i);
+    const uint32_t vb = kb + 4096;
+
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const int ch = 2 * s + k_chunk;  // 16-byte chunk of the 256-byte row
+      uint32_t a[4];
+      ldmatrix_x4(a, kb + (ch >> 3) * 2048 + swz128(k_tok, ch & 7));
+      if (s & 1) mma16<IS_BF16>(sb, a, qf[2 * s], qf[2 * s + 1]);
+      else mma16<IS_BF16>(sa, a, qf[2 * s], qf[2 * s + 1]);
+    }
+
+    const int tile_tok = (it.t0 + i) * kTile;
+    const int tok0 = tile_tok + g;
+    float v0 = (sa[0] + sb[0]) * sc, v1 = (sa[1] + sb[1]) * sc;
+    float v2 = (sa[2] + sb[2]) * sc, v3 = (sa[3] + sb[3]) * sc;
+    if (tok0 >= it.seq_len) v0 = v1 = -INFINITY;
+    if (tok0 + 8 >= it.seq_len) v2 = v3 = -INFINITY;
+    float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 4));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 4));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 8));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 8));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 16));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 16));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    if (__any_sync(kFull, (mn0 != m0) || (mn1 != m1))) {
+      const float al0 = exp2_fast(m0 - mn0), al1 = exp2_fast(m1 - mn1);
+      l0 *= al0;
+      l1 *= al1;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j][0] *= al0; acc[j][1] *= al1; acc[j][2] *= al0; acc[j][3] *= al1;
+      }
+      m0 = mn0;
+      m1 = mn1;
+    }
+    const float p0 = exp2_fast(v0 - m0), p1 = exp2_fast(v1 - m1);
+    const float p2 = exp2_fast(v2 - m0), p3 = exp2_fast(v3 - m1);
+    l0 += p0 + p2;
+    l1 += p1 + p3;
+    const uint32_t pb0 = movmatrix_trans(pack16<IS_BF16>(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack16<IS_BF16>(p2, p3));
+
+    // In the last tile of a sequence the rows past seq_len hold whatever the block had before; a float cache
+    // may hold NaN/Inf there, and 0 * NaN would poison the sum, so those V values are zeroed.
+    const int nvalid = it.seq_len - tile_tok;  // >= 1
+    uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // masks for (tokens 2t,2t+1) and (2t+8,2t+9)
+    if (nvalid < kTile) {
+      keep_lo = (2 * t < nvalid ? 0x0000ffffu : 0u) | (2 * t + 1 < nvalid ? 0xffff0000u : 0u);
+      keep_hi = (2 * t + 8 < nvalid ? 0x0000ffffu : 0u) | (2 * t + 9 < nvalid ? 0xffff0000u : 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int ch = 2 * j + v_chunk;
+      uint32_t a[4];
+      ldmatrix_x4_trans(a, vb + (ch >> 3) * 2048 + swz128(v_tok, ch & 7));
+      a[0] &= keep_lo; a[1] &= keep_lo; a[2] &= keep_hi; a[3] &= keep_hi;
+      mma16<IS_BF16>(acc[j], a, pb0, pb1);
+    }
+
+    __syncwarp();
+    if (i + NST < n) ring.issue(i + NST);
+  }
+
+  if (timed_out) {
+    if (lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
+    const int issued = (i + NST < n) ? i + NST : n;
+    for (int j = i + 1; j < issued; ++j) ring.wait(j, 1u << 16);
+    return;
+  }
+
+  l0 += __shfl_xor_sync(kFull, l0, 4);
+  l1 += __shfl_xor_sync(kFull, l1, 4);
+  l0 += __shfl_xor_sync(kFull, l0, 8);
+  l1 += __shfl_xor_sync(kFull, l1, 8);
+  l0 += __shfl_xor_sync(kFull, l0, 16);
+  l1 += __shfl_xor_sync(kFull, l1, 16);
+  // C fragment of tile j: rows = dims 16j+g (regs 0,1) and 16j+g+8 (regs 2,3), cols = heads 2t, 2t+1
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const int hg = 2 * t + e;
+    if (hg >= p.G) continue;
+    const int hq = it.h * p.G + hg;
+    const float l = e ? l1 : l0;
+    const float m = e ? m1 : m0;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (p.part == nullptr) {
+      const int64_t base = it.b * p.o_st[0] + hq * p.o_st[1];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        store_from_float(p.out, p.out_dtype, base + (16 * j + g) * p.o_st[2], acc[j][e] * inv);
+        store_from_float(p.out, p.out_dtype, base + (16 * j + g + 8) * p.o_st[2], acc[j][e + 2] * inv);
+      }
+    } else {
+      const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + hq;
+      float* dst = p.part + row * p.row_floats;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dst[16 * j + g] = acc[j][e] * inv;
+        dst[16 * j + g + 8] = acc[j][e + 2] * inv;
+      }
+      if (g == 0) dst[p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic kernel: any head_dim <= 512, any block size, any group, any strides.  One warp per
+// (sequence, query head, split); correctness path for shapes the tiled kernels do not cover.
+// ---------------------------------------------------------------------------------------------
+constexpr int kGenericMaxD = 512;
+
+__device__ __forceinline__ float cache_elem(const void* base, int kind, int64_t idx) {
+  if (kind == kCacheInt8) return static_cast<float>(reinterpret_cast<const int8_t*>(base)[idx]);
+  if (kind == kCacheBf16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+}
+
+__global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hq;
+  if (item >= total) return;
+  const int hq = static_cast<int>(item % p.Hq);
+  const int64_t rr = item / p.Hq;
+  const int c = static_cast<int>(rr % p.num_splits);
+  const int b = static_cast<int>(rr / p.num_splits);
+  const int hkv = hq / p.G;
+  int64_t sl = load_index(p.sl, p.sl_is_i64, b);
+  const int64_t cap = p.bt_width * p.block_size;
+  sl = sl > cap ? cap : (sl < 0 ? 0 : sl);
+  const int64_t nblk = (sl + p.block_size - 1) / p.block_size;
+  const int64_t per = (nblk + p.num_splits - 1) / p.num_splits;
+  const int64_t tok_lo = c * per * p.block_size;
+  int64_t tok_hi = (c + 1) * per * p.block_size;
+  if (tok_hi > sl) tok_hi = sl;
+  const int64_t row = (static_cast<int64_t>(c) * p.B + b) * p.Hq + hq;
+
+  constexpr int kSlots = kGenericMaxD / kWarp;
+  float q[kSlots], acc[kSlots];
+  float q_mul = 1.f;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    const int d = lane + kWarp * s;
+    q[s] = d < p.D ? load_as_float(p.q, p.q_dtype, b * p.q_st[0] + hq * p.q_st[1] + d * p.q_st[2]) : 0.f;
+    acc[s] = 0.f;
+  }
+  if (p.quantize_q) {
+    float amax = 0.f;
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) amax = fmaxf(amax, fabsf(q[s]));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
+    const float qs = fmaxf(amax / 127.f, 1e-6f);
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      const float x = q[s] / qs;
+      const float r = x >= 0.f ? floorf(x + 0.5f) : -floorf(-x + 0.5f);
+      q[s] = fminf(fmaxf(r, -127.f), 127.f);
+    }
+    q_mul = qs;
+  }
+  const float ks = p.k_scale ? fmaxf(__ldg(p.k_scale + hkv), 1e-6f) : 1.f;
+  const float vs = p.v_scale ? fmaxf(__ldg(p.v_scale + hkv), 1e-6f) : 1.f;
+  const float sc = ks * q_mul * p.sm_scale_log2;
+  float m = -INFINITY, l = 0.f;
+  for (int64_t tok = tok_lo; tok < tok_hi; ++tok) {
+    const int64_t lb = tok / p.block_size;
+    const int64_t off = tok - lb * p.block_size;
+    const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+    if (blk < 0 || blk >= p.num_blocks) continue;  // never read outside the cache
+    const int64_t kof = blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
+    const int64_t vof = blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
+    float dot = 0.f;
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      const int d = lane + kWarp * s;
+      if (d < p.D) dot += q[s] * cache_elem(p.kc, p.cache_kind, kof + d * p.kc_st[3]);
+    }
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(kFull, dot, o);
+    const float sv = dot * sc;
+    const float mn = fmaxf(m, sv);
+    const float al = exp2f(m - mn);
+    const float pe = exp2f(sv - mn);
+    l = l * al + pe;
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      const int d = lane + kWarp * s;
+      if (d < p.D) acc[s] = acc[s] * al + pe * cache_elem(p.vc, p.cache_kind, vof + d * p.vc_st[3]);
+    }
+    m = mn;
+  }
+  const float inv = l > 0.f ? vs / l : 0.f;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    const int d = lane + kWarp * s;
+    if (d >= p.D) continue;
+    if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[s] * inv);
+    else p.part[row * p.row_floats + d] = acc[s] * inv;
+  }
+  if (p.part != nullptr && lane == 0)
+    p.part[row * p.row_floats + p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Merge of partial rows [R, rows, row_floats] (out | lse | pad): one warp per row
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) merge_partials_kernel(const MergeParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (row >= p.rows) return;
+  const int64_t stride_r = p.rows * p.row_floats;
+  const float* base = p.parts + row * p.row_floats;
+  float top = -INFINITY;
+  for (int r = lane; r < p.R; r += kWarp) top = fmaxf(top, base[r * stride_r + p.D]);
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
+  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row % p.Hq);
+  float den = 0.f;
+  for (int d0 = 0; d0 < p.D; d0 += 4 * kWarp) {
+    const int d = d0 + 4 * lane;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    den = 0.f;
+    for (int r = 0; r < p.R; ++r) {
+      const float lse = base[r * stride_r + p.D];
+      if (lse == -INFINITY) continue;  // empty part: its out row was never written
+      const float w = __expf(lse - top);
+      den += w;
+      if (d < p.D) {
+        const float4 o = *reinterpret_cast<const float4*>(base + r * stride_r + d);
+        a.x += w * o.x; a.y += w * o.y; a.z += w * o.z; a.w += w * o.w;
+      }
+    }
+    if (d < p.D) {
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+      if (p.part_out != nullptr) {
+        *reinterpret_cast<float4*>(p.part_out + row * p.row_floats + d) = a;
+      } else {
+        const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
+        store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
+        if (d + 1 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
+        if (d + 2 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
+        if (d + 3 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
+      }
+    }
+  }
+  if (p.part_out != nullptr && lane == 0)
+    p.part_out[row * p.row_floats + p.D] = den > 0.f ? top + __logf(den) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------
+constexpr int kInt8Stages = 4;
+constexpr int kF16Stages = 3;
+
+template <typename K>
+static int set_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+}
+
+static int64_t tiled_ctas(const AttnParams& p) {
+  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  return (items + kTiledWarpsPerCta - 1) / kTiledWarpsPerCta;
+}
+
+int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
+  constexpr int smem = kTiledWarpsPerCta * kInt8Stages * 4096 + kTiledWarpsPerCta * kInt8Stages * 8 + 1024;
+  auto kernel = paged_attn_int8_kernel<kInt8Stages>;
+  if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+  const int64_t ctas = tiled_ctas(p);
+  if (ctas <= 0) return INT8KV_OK;
+  kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
+  constexpr int smem = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
+  const int64_t ctas = tiled_ctas(p);
+  if (ctas <= 0) return INT8KV_OK;
+  if (p.cache_kind == kCacheBf16) {
+    auto kernel = paged_attn_f16_kernel<kF16Stages, true>;
+    if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+    kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
+  } else {
+    auto kernel = paged_attn_f16_kernel<kF16Stages, false>;
+    if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+    kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
+  if (p.D > kGenericMaxD) return INT8KV_E_UNSUPPORTED;
+  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hq;
+  if (items <= 0) return INT8KV_OK;
+  paged_attn_generic_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+int launch_merge(const MergeParams& p, cudaStream_t stream) {
+  if (p.rows <= 0) return INT8KV_OK;
+  merge_partials_kernel<<<static_cast<unsigned>((p.rows + 3) / 4), 128, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+}  // namespace int8kv

@@ -1,0 +1,353 @@
+"""Host-side operators over the C ABI: INT8 KV cache write, INT8 paged decode attention, and the
+BF16 paged-attention baseline.
+
+Call signatures, argument meaning and error behaviour mirror the reference prototype's operator
+modules (src/triton_ops/int8_cache_write.py:85-149, src/triton_ops/int8_paged_attention.py:683-769,
+src/triton_ops/bf16_paged_attention.py:118-165): argument violations raise AssertionError, an
+unknown `impl` raises ValueError, the write mutates the caches in place and returns None, attention
+allocates and returns its output.  Everything runs asynchronously on the current CUDA stream.
+PyTorch is used for device memory and streams only; all arithmetic happens in the CUDA library.
+"""
+
+from __future__ import annotations
+
+import threading
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_FLOAT_CODES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float32: _lib.FP32}
+
+# ---------------------------------------------------------------------------------------------------
+# split-KV workspace: one growing buffer per (device, stream), owned by this module like the
+# partial_out/partial_m/partial_l tensors that the reference allocates per call (:595-597)
+# ---------------------------------------------------------------------------------------------------
+_WS: Dict[Tuple[int, int], torch.Tensor] = {}
+_WS_LOCK = threading.Lock()
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    with _WS_LOCK:
+        buf = _WS.get(key)
+        if buf is None or buf.numel() < nbytes:
+            grow = max(nbytes, 1 << 20)
+            buf = torch.zeros(grow, dtype=torch.uint8, device=device)
+            _WS[key] = buf
+        return buf
+
+
+def release_workspaces() -> None:
+    """Drop every cached split-KV workspace."""
+    with _WS_LOCK:
+        _WS.clear()
+
+
+def device_status(device=None) -> int:
+    """Read (and clear) the status word the kernels set when a bounded wait ran out.
+
+    Synchronises the device; meant for tests and debugging, not for the serving path.
+    """
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    buf = _WS.get(key)
+    if buf is None:
+        return 0
+    off = _lib.load().int8kv_workspace_status_offset(buf.numel())
+    word = buf[off : off + 4].view(torch.int32)
+    value = int(word.item())
+    if value:
+        word.zero_()
+    return value
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _as_f32_scale(scale: torch.Tensor) -> torch.Tensor:
+    if scale.dtype != torch.float32:
+        scale = scale.float()
+    return scale.contiguous()
+
+
+def _require_lib():
+    return _lib.load()
+
+
+# ---------------------------------------------------------------------------------------------------
+# INT8 KV cache write
+# ---------------------------------------------------------------------------------------------------
+def int8_kv_cache_write(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    num_warps: int = 4,
+    num_stages: int = 2,
+) -> None:
+    """Quantise key/value [T, Hkv, D] with static per-head scales and scatter them into the INT8 paged
+    caches [num_blocks, BS, Hkv, D] at slot_mapping (slot = block*BS + offset; slot < 0 skips the token).
+
+    `num_warps` / `num_stages` are accepted for call compatibility and ignored.
+    """
+    assert key.is_cuda and value.is_cuda
+    assert key_cache.is_cuda and value_cache.is_cuda
+    assert slot_mapping.is_cuda and k_scale.is_cuda and v_scale.is_cuda
+    assert key.ndim == 3 and value.ndim == 3
+    assert key_cache.ndim == 4 and value_cache.ndim == 4
+    assert key.shape == value.shape and key_cache.shape == value_cache.shape
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    assert key.dtype in _FLOAT_CODES and value.dtype == key.dtype
+    num_tokens, num_kv_heads, head_dim = key.shape
+    num_blocks, block_size, cache_heads, cache_dim = key_cache.shape
+    assert cache_heads == num_kv_heads and cache_dim == head_dim
+    assert slot_mapping.ndim == 1 and slot_mapping.numel() == num_tokens
+    assert k_scale.ndim == 1 and v_scale.ndim == 1
+    assert k_scale.numel() == num_kv_heads and v_scale.numel() == num_kv_heads
+    assert slot_mapping.dtype in (torch.int32, torch.int64)
+    lib = _require_lib()
+    k_scale = _as_f32_scale(k_scale)
+    v_scale = _as_f32_scale(v_scale)
+    if slot_mapping.stride(0) != 1:
+        slot_mapping = slot_mapping.contiguous()
+    rc = lib.int8kv_cache_write(
+        key.data_ptr(), value.data_ptr(), _FLOAT_CODES[key.dtype],
+        num_tokens, num_kv_heads, head_dim,
+        _lib.i64(key.stride()), _lib.i64(value.stride()),
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        num_blocks, block_size,
+        slot_mapping.data_ptr(), int(slot_mapping.dtype == torch.int64),
+        k_scale.data_ptr(), v_scale.data_ptr(),
+        _stream_ptr(key.device),
+    )
+    _lib.check("int8kv_cache_write", rc)
+
+
+# ---------------------------------------------------------------------------------------------------
+# paged decode attention
+# ---------------------------------------------------------------------------------------------------
+def _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens):
+    assert query.is_cuda
+    assert key_cache.is_cuda and value_cache.is_cuda
+    assert block_tables.is_cuda and seq_lens.is_cuda
+    assert query.ndim == 3 and key_cache.ndim == 4 and value_cache.ndim == 4
+    assert block_tables.ndim == 2 and seq_lens.ndim == 1
+    assert query.dtype in _FLOAT_CODES
+    assert block_tables.dtype in (torch.int32, torch.int64)
+    assert seq_lens.dtype in (torch.int32, torch.int64)
+    B, Hq, D = query.shape
+    _, block_size, Hkv, cache_D = key_cache.shape
+    assert value_cache.shape == key_cache.shape
+    assert cache_D == D and Hq % Hkv == 0
+    assert block_tables.shape[0] == B and seq_lens.numel() == B
+    assert key_cache.stride(-1) == 1 and value_cache.stride(-1) == 1
+    return B, Hq, Hkv, D, block_size
+
+
+def _max_seq_len(seq_lens, block_tables, block_size, max_seq_len, validate=True):
+    """The reference checks seq_lens on the host (two device syncs, :720-723).  With `max_seq_len`
+    given, no sync happens and the kernels clamp lengths to what the block table can address."""
+    if max_seq_len is not None:
+        return int(max_seq_len)
+    if seq_lens.numel() == 0:
+        return 0
+    lo, hi = torch.aminmax(seq_lens)
+    lo, hi = int(lo.item()), int(hi.item())
+    if validate:
+        assert lo > 0
+        assert block_tables.shape[1] >= (hi + block_size - 1) // block_size
+    return hi
+
+
+def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits):
+    if num_splits is None:
+        sm = torch.cuda.get_device_properties(device).multi_processor_count
+        splits = lib.int8kv_choose_splits(B, Hkv, max_seq, block_size, sm)
+    else:
+        splits = max(1, min(int(num_splits), lib.int8kv_max_splits()))
+    nbytes = lib.int8kv_workspace_bytes(B, Hq, D, splits)
+    ws = _workspace(device, nbytes)
+    return splits, ws
+
+
+def int8_paged_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    *,
+    quantize_q: bool = False,
+    num_warps: int = 4,
+    impl: str = "auto",
+    num_splits: Optional[int] = None,
+    max_seq_len: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Decode attention of query [B, Hq, D] over an INT8 paged cache; returns [B, Hq, D] in query.dtype.
+
+    impl: "auto", "v3" or "v4" are accepted (the reference's two kernel generations); one kernel
+    family serves all of them here.  num_splits: None picks the KV split count from the shape, an int
+    is honoured.  max_seq_len / out are extensions: an upper bound of seq_lens that avoids the host
+    synchronisation, and a preallocated output.
+    """
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    assert k_scale.is_cuda and v_scale.is_cuda
+    assert k_scale.ndim == 1 and v_scale.ndim == 1
+    assert k_scale.numel() == Hkv and v_scale.numel() == Hkv
+    if impl not in ("auto", "v3", "v4"):
+        raise ValueError(f"Unknown impl={impl!r}; expected 'auto', 'v3' or 'v4'")
+    lib = _require_lib()
+    k_scale = _as_f32_scale(k_scale)
+    v_scale = _as_f32_scale(v_scale)
+    max_seq = _max_seq_len(seq_lens, block_tables, block_size, max_seq_len)
+    if out is None:
+        out = torch.empty((B, Hq, D), device=query.device, dtype=query.dtype)
+    else:
+        assert out.shape == (B, Hq, D) and out.dtype in _FLOAT_CODES and out.is_cuda
+    if B == 0:
+        return out
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, max_seq, num_splits)
+    rc = lib.int8kv_paged_attn_int8(
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
+        k_scale.data_ptr(), v_scale.data_ptr(),
+        out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
+        splits, ws.data_ptr(), ws.numel(),
+        int(bool(quantize_q)), _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_paged_attn_int8", rc)
+    return out
+
+
+def bf16_paged_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    num_splits: Optional[int] = None,
+    max_seq_len: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Decode attention over a bf16 (or fp16) paged cache: the same-run baseline for the INT8 path.
+
+    Unlike the reference's baseline, which walks all block_tables.shape[1] blocks
+    (src/triton_ops/bf16_paged_attention.py:155), only the blocks below seq_lens are read.
+    """
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype in (torch.bfloat16, torch.float16) and value_cache.dtype == key_cache.dtype
+    lib = _require_lib()
+    max_seq = _max_seq_len(seq_lens, block_tables, block_size, max_seq_len, validate=False)
+    if max_seq_len is None:
+        max_seq = min(max_seq, block_tables.shape[1] * block_size)
+    if out is None:
+        out = torch.empty_like(query)
+    else:
+        assert out.shape == (B, Hq, D) and out.dtype in _FLOAT_CODES and out.is_cuda
+    if B == 0:
+        return out
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, max_seq, num_splits)
+    rc = lib.int8kv_paged_attn_bf16(
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(), _FLOAT_CODES[key_cache.dtype],
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
+        out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
+        splits, ws.data_ptr(), ws.numel(),
+        _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_paged_attn_bf16", rc)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# partial attention + merge (sequence-parallel split across devices)
+# ---------------------------------------------------------------------------------------------------
+def partial_row_floats(head_dim: int) -> int:
+    return _require_lib().int8kv_partial_row_floats(int(head_dim))
+
+
+def int8_paged_attention_partial(
+    query, key_cache, value_cache, block_tables, seq_lens, k_scale, v_scale,
+    *, quantize_q: bool = False, num_splits: Optional[int] = None, max_seq_len: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Unmerged attention over the tokens this cache holds: fp32 rows [B, Hq, row] with
+    row = [normalised out (D) | natural-log sum-exp | padding]; sequences with seq_len <= 0 give lse = -inf."""
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    lib = _require_lib()
+    k_scale = _as_f32_scale(k_scale)
+    v_scale = _as_f32_scale(v_scale)
+    max_seq = _max_seq_len(seq_lens, block_tables, block_size, max_seq_len, validate=False)
+    max_seq = min(max_seq, block_tables.shape[1] * block_size)
+    rf = lib.int8kv_partial_row_floats(D)
+    if out is None:
+        out = torch.empty((B, Hq, rf), device=query.device, dtype=torch.float32)
+    assert out.shape == (B, Hq, rf) and out.dtype == torch.float32 and out.is_contiguous()
+    if B == 0:
+        return out
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, max(max_seq, 1), num_splits)
+    rc = lib.int8kv_paged_attn_int8_partial(
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
+        k_scale.data_ptr(), v_scale.data_ptr(),
+        out.data_ptr(),
+        splits, ws.data_ptr(), ws.numel(),
+        int(bool(quantize_q)), _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_paged_attn_int8_partial", rc)
+    return out
+
+
+def merge_partials(parts: torch.Tensor, head_dim: int, dtype=torch.bfloat16, out: Optional[torch.Tensor] = None):
+    """parts: fp32 [R, B, Hq, row] partial rows (as produced above, one slab per rank) -> [B, Hq, D]."""
+    assert parts.is_cuda and parts.dtype == torch.float32 and parts.ndim == 4 and parts.is_contiguous()
+    lib = _require_lib()
+    R, B, Hq, rf = parts.shape
+    assert rf == lib.int8kv_partial_row_floats(head_dim)
+    if out is None:
+        out = torch.empty((B, Hq, head_dim), device=parts.device, dtype=dtype)
+    assert out.dtype in _FLOAT_CODES
+    rc = lib.int8kv_merge_partials(
+        parts.data_ptr(), R, B, Hq, head_dim, out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
+        _stream_ptr(parts.device),
+    )
+    _lib.check("int8kv_merge_partials", rc)
+    return out
