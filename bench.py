@@ -1,0 +1,398 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8 paged decode-attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c4|c5]
+
+Default workload (`c2`): the largest cell of the single-GPU kernel sweep — B=8 sequences of 4096
+tokens, Hq=28, Hkv=4, D=128, block_size=16 — for 28 layers, each with its own INT8 cache (28 x 67 MB,
+larger than L2, so every call reads its pages from HBM).  One step = one decode pass over the 28
+layers = 28 int8_paged_attention calls.  Under torchrun every rank runs the same shard (its own batch
+of sequences on its own GPU, no collective): weak scaling.
+
+Printed JSON (one line, rank 0):
+  value      achieved GB/s of algorithmic bytes, device-resident inputs, step replayed as a CUDA graph
+  e2e        same metric through the Python operators with pinned-host inputs copied in and the result
+             copied out inside the timed region
+  roofline   the attention call against the measured HBM copy peak
+  cpu_baseline  the CPU oracle (a port of the reference's PyTorch CPU path) on one layer of the workload
+`--impl reference` times that CPU path alone with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+HBM_NOMINAL_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+
+
+# ---------------------------------------------------------------------------------------------------
+# workload description
+# ---------------------------------------------------------------------------------------------------
+def workload_spec(name: str):
+    """(shape kwargs, seq_lens per rank, layers, description)"""
+    gen = torch.Generator().manual_seed(1234)
+    if name == "c2":
+        return dict(hq=28, hkv=4), [4096] * 8, 28, "sweep cell B=8 seq=4096, 28 distinct layer caches"
+    if name == "c4":
+        lens = torch.randint(1024, 8193, (256,), generator=gen).tolist()
+        return dict(hq=28, hkv=4), lens, 4, "B=256 seq~U[1024,8192], 4 distinct layer caches"
+    if name == "c5":
+        return dict(hq=64, hkv=8), [65536] * 32, 1, "B=32 ctx 65536 Hq=64 Hkv=8, one layer"
+    raise SystemExit(f"unknown workload {name}")
+
+
+def algorithmic_bytes(seq_lens, hq, hkv, d=128, bs=16, elem=1) -> int:
+    """K+V bytes + block ids + query in / out + scales + seq_lens, per call."""
+    tok = sum(seq_lens)
+    blocks = sum((s + bs - 1) // bs for s in seq_lens)
+    return tok * hkv * d * 2 * elem + blocks * 4 + len(seq_lens) * hq * d * 2 * 2 + 8 * hkv + 4 * len(seq_lens)
+
+
+class Layer:
+    pass
+
+
+def build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed, with_bf16=False):
+    """Per layer: INT8 caches filled through the product write kernel from seeded bf16 K/V."""
+    shape = wl.LayerShape(hq, hkv, 128, 16)
+    B = len(seq_lens)
+    need = int(wl.blocks_needed(seq_lens, 16).sum())
+    num_blocks = need * 2 if need * 2 * 16 * hkv * 128 < (8 << 30) else need + 64
+    out = []
+    gen = torch.Generator(device=device)
+    for li in range(layers):
+        L = Layer()
+        L.k_scale, L.v_scale = [t.to(device) for t in wl.calibrate_scales(shape, seed, li)]
+        tables = wl.permuted_block_tables(seq_lens, 16, num_blocks, seed + 13 * li)
+        L.block_tables = tables.to(device)
+        L.seq_lens = torch.tensor(seq_lens, dtype=torch.int32, device=device)
+        L.kc = torch.zeros(num_blocks, 16, hkv, 128, dtype=torch.int8, device=device)
+        L.vc = torch.zeros_like(L.kc)
+        if with_bf16:
+            L.kb = torch.zeros(num_blocks, 16, hkv, 128, dtype=torch.bfloat16, device=device)
+            L.vb = torch.zeros_like(L.kb)
+        gain = wl.channel_gain(shape, seed, device)
+        gen.manual_seed(seed * 1000003 + li)
+        for b in range(B):  # one sequence at a time bounds the bf16 staging memory
+            T = seq_lens[b]
+            k, v = wl.draw_kv(T, shape, gen, gain)
+            tok = torch.arange(T, device=device)
+            slots = L.block_tables[b, tok // 16].long() * 16 + tok % 16
+            kv.int8_kv_cache_write(k, v, L.kc, L.vc, slots, L.k_scale, L.v_scale)
+            if with_bf16:
+                L.kb.view(-1, hkv, 128)[slots] = k
+                L.vb.view(-1, hkv, 128)[slots] = v
+        L.query = wl.draw_query(B, shape, gen)
+        L.out = torch.empty_like(L.query)
+        out.append(L)
+    torch.cuda.synchronize(device)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in text.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference's PyTorch CPU path)
+# ---------------------------------------------------------------------------------------------------
+def cpu_layer_inputs(wl, hq, hkv, seq_lens, seed=0):
+    import oracle
+
+    case = wl.make_decode_case(seq_lens, wl.LayerShape(hq, hkv, 128, 16), seed=seed)
+    kc = torch.zeros(case.num_blocks, 16, hkv, 128, dtype=torch.int8)
+    vc = torch.zeros_like(kc)
+    oracle.cache_write(case.key, case.value, kc, vc, case.slot_mapping, case.k_scale, case.v_scale)
+    return case, kc, vc
+
+
+def cpu_one_call(case, kc, vc):
+    import oracle
+
+    B = case.query.shape[0]
+    # decode step of one layer: write one new token per sequence over its last slot, then attend
+    last = torch.tensor([int(case.seq_lens[:b + 1].sum()) - 1 for b in range(B)])
+    oracle.cache_write(case.key[last], case.value[last], kc, vc, case.slot_mapping[last], case.k_scale, case.v_scale)
+    return oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, case.seq_lens.tolist(),
+                                              case.k_scale, case.v_scale)
+
+
+def time_cpu(wl, hq, hkv, seq_lens, budget_s, min_reps=3, warm=1):
+    # bound the sample: at most ~64k tokens of context per call
+    sample = list(seq_lens)
+    while sum(sample) > 65536 and len(sample) > 1:
+        sample = sample[: len(sample) // 2]
+    if sum(sample) > 65536:
+        sample = [65536]
+    torch.set_num_threads(os.cpu_count() or 1)
+    case, kc, vc = cpu_layer_inputs(wl, hq, hkv, sample)
+    for _ in range(warm):
+        cpu_one_call(case, kc, vc)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < min_reps or time.perf_counter() < t_end:
+        t0 = time.perf_counter()
+        cpu_one_call(case, kc, vc)
+        times.append(time.perf_counter() - t0)
+        if len(times) >= 200:
+            break
+    med = statistics.median(times)
+    nbytes = algorithmic_bytes(sample, hq, hkv)
+    desc = f"one layer call (write {len(sample)} tokens + attention), B={len(sample)}, {sum(sample)} context tokens, {len(times)} reps, median"
+    return nbytes / med / 1e9, med, torch.get_num_threads(), desc, sample
+
+
+# ---------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"])
+    ap.add_argument("--num-splits", type=int, default=None)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    shape_kw, seq_lens, layers, desc = workload_spec(args.workload)
+    hq, hkv = shape_kw["hq"], shape_kw["hkv"]
+    wl = importlib.import_module("int8-kvcache_b200.workloads")
+    metric = "int8_paged_decode_attn_achieved_hbm_gbps"
+    config = {"workload": f"{args.workload}: {desc}", "Hq": hq, "Hkv": hkv, "head_dim": 128, "block_size": 16,
+              "batch_per_gpu": len(seq_lens), "layers": layers,
+              "l2": "inputs larger than L2: each call reads a different layer's cache",
+              "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"}
+
+    # ---------------- reference arm: the CPU path on the host cores -------------------------------
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        gbs, med, cores, sample_desc, sample = time_cpu(wl, hq, hkv, seq_lens, budget_s=0.0,
+                                                        min_reps=max(1, args.steps), warm=max(0, args.warmup))
+        line = {"impl": "reference", "metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8 KV, fp32 math", "data": "synthetic",
+                "config": config,
+                "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample_desc},
+                "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "us_per_call": med * 1e6, "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    # ---------------- our arm ------------------------------------------------------------------------
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the kernels)")
+    kv = importlib.import_module("int8-kvcache_b200")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    layers_data = build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed=100 + rank)
+    max_seq = max(seq_lens)
+    B = len(seq_lens)
+    nbytes_call = algorithmic_bytes(seq_lens, hq, hkv)
+    nbytes_step = nbytes_call * layers
+
+    def device_step():
+        for L in layers_data:
+            kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
+                                    num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
+
+    lib = kv._lib.load()
+    sm = torch.cuda.get_device_properties(device).multi_processor_count
+    splits = args.num_splits or lib.int8kv_choose_splits(B, hkv, max_seq, 16, sm)
+    launches_per_call = 1 + (1 if splits > 1 else 0)
+
+    # warm up eagerly (kernel attribute set-up, workspace allocation), then capture one step as a CUDA graph
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            device_step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            device_step()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+
+        def barrier():
+            torch.cuda.synchronize(device)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize(device)
+
+        sampler = ClockSampler(local_rank)
+        barrier()
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        dev_ms = e0.elapsed_time(e1)
+
+        # ---- e2e: Python operators, pinned host inputs in, result out, every step -------------------
+        shape = wl.LayerShape(hq, hkv, 128, 16)
+        g = torch.Generator().manual_seed(7)
+        host_q = [wl.draw_query(B, shape, g).pin_memory() for _ in range(layers)]
+        host_kv = [tuple(t.pin_memory() for t in wl.draw_kv(B, shape, g, wl.channel_gain(shape, 0))) for _ in range(layers)]
+        host_out = [torch.empty(B, hq, 128, dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
+        last_slots, host_bt, host_sl = [], [], []
+        for L in layers_data:
+            last = torch.tensor([s - 1 for s in seq_lens], device=device)
+            slots = L.block_tables[torch.arange(B, device=device), last // 16].long() * 16 + last % 16
+            last_slots.append(slots.cpu().pin_memory())
+            host_bt.append(L.block_tables.cpu().pin_memory())
+            host_sl.append(L.seq_lens.cpu().pin_memory())
+        d_q = torch.empty(B, hq, 128, dtype=torch.bfloat16, device=device)
+        d_k = torch.empty(B, hkv, 128, dtype=torch.bfloat16, device=device)
+        d_v = torch.empty_like(d_k)
+        d_slots = torch.empty(B, dtype=torch.int64, device=device)
+        d_bt = torch.empty_like(layers_data[0].block_tables)
+        d_sl = torch.empty(B, dtype=torch.int32, device=device)
+        d_out = torch.empty(B, hq, 128, dtype=torch.bfloat16, device=device)
+        h2d = layers * (host_q[0].numel() * 2 + 2 * host_kv[0][0].numel() * 2 + last_slots[0].numel() * 8
+                        + host_bt[0].numel() * 4 + host_sl[0].numel() * 4)
+        d2h = layers * host_out[0].numel() * 2
+
+        def e2e_step():
+            for i, L in enumerate(layers_data):
+                d_q.copy_(host_q[i], non_blocking=True)
+                d_k.copy_(host_kv[i][0], non_blocking=True)
+                d_v.copy_(host_kv[i][1], non_blocking=True)
+                d_slots.copy_(last_slots[i], non_blocking=True)
+                d_bt.copy_(host_bt[i], non_blocking=True)
+                d_sl.copy_(host_sl[i], non_blocking=True)
+                kv.int8_kv_cache_write(d_k, d_v, L.kc, L.vc, d_slots, L.k_scale, L.v_scale)
+                kv.int8_paged_attention(d_q, L.kc, L.vc, d_bt, d_sl, L.k_scale, L.v_scale,
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=d_out)
+                host_out[i].copy_(d_out, non_blocking=True)
+            stream.synchronize()
+
+        for _ in range(args.warmup):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = [float(x) for x in times.tolist()]
+    status = kv.device_status(device)
+
+    if rank == 0:
+        ms_per_step = dev_ms / args.steps
+        value = world * nbytes_step / (ms_per_step * 1e-3) / 1e9
+        e2e_value = world * nbytes_step / (e2e_ms / args.steps * 1e-3) / 1e9
+        peaks_path = REPO / "MEASURED_PEAKS.json"
+        if peaks_path.exists():
+            peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = FALLBACK_PEAK_GBS, "fallback 6.65 TB/s"
+        per_call_s = ms_per_step * 1e-3 / layers
+        achieved = nbytes_call / per_call_s / 1e9
+        line = {
+            "metric": metric, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 KV, fp16 tensor-core products, fp32 accumulate/softmax",
+            "data": "synthetic", "config": config,
+            "us_per_call": per_call_s * 1e6,
+            "tokens_layers_per_s": world * B * layers / (ms_per_step * 1e-3),
+            "frac_of_8TBps": value / world / HBM_NOMINAL_GBS,
+            "num_splits": splits,
+            "gpu_launches": launches_per_call * layers * args.steps,
+            "clocks": clocks,
+            "device_status": status,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps,
+                    "what": "pinned-host q/k/v/slots/tables/seq_lens -> device, cache write + attention through the "
+                            "Python operators, output -> pinned host, per layer, synchronised per step"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": "paged_attn_int8_kernel (+ merge_partials_kernel when split), per call inside the graph",
+                         "algorithmic_bytes_per_call": nbytes_call},
+        }
+        if not args.no_cpu:
+            gbs, med, cores, sample_desc, _ = time_cpu(wl, hq, hkv, seq_lens, budget_s=args.cpu_seconds)
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": sample_desc, "ms_per_call": med * 1e3}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

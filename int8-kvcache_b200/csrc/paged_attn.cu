@@ -21,6 +21,8 @@
 // the row sum is reduced once at the end).  P^T is obtained from the C fragment with movmatrix (8x8 transpose) and
 // O^T = V^T . P^T puts dims on M: the V^T A fragment needs pairs of tokens at one dim, produced by byte
 // interleaving (prmt) of 16-byte row pieces on the way to fp16.  v_scale and 1/l are applied once in the epilogue.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace int8kv {
@@ -707,9 +709,18 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const MergeParams p
 constexpr int kInt8Stages = 4;
 constexpr int kF16Stages = 3;
 
+// The dynamic shared-memory limit is raised once per (kernel, device); later calls, which may sit inside a
+// stream capture, launch without touching function attributes.
 template <typename K>
 static int set_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+  static std::atomic<bool> done[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  const bool track = dev >= 0 && dev < 64;
+  if (track && done[dev].load(std::memory_order_acquire)) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
+  if (track) done[dev].store(true, std::memory_order_release);
+  return 0;
 }
 
 static int64_t tiled_ctas(const AttnParams& p) {

@@ -1,0 +1,241 @@
+"""GPU parity of INT8 paged decode attention and of the BF16 baseline, through the C ABI.
+
+Bars: max-abs <= 2e-2 against the reference's result in bf16, cosine >= 0.9999 against the fp32
+dequantise-then-attend oracle."""
+
+import math
+
+import pytest
+import torch
+
+import oracle
+from conftest import cosine, load_golden, max_abs
+
+pytestmark = pytest.mark.gpu
+MAX_ABS = 2e-2
+MIN_COS = 0.9999
+
+
+def _dev(*ts):
+    return [t.cuda() for t in ts]
+
+
+def _check(out, want_f32, want_bf16=None):
+    out = out.float().cpu()
+    assert torch.isfinite(out).all()
+    assert cosine(out, want_f32) >= MIN_COS
+    ref = want_f32.to(torch.bfloat16).float() if want_bf16 is None else want_bf16.float()
+    assert max_abs(out, ref) <= MAX_ABS
+
+
+def _run_int8(kv, g, seq_lens=None, **kw):
+    q, kc, vc, bt, ks, vs = _dev(g["query"], g["key_cache"], g["value_cache"], g["block_tables"], g["k_scale"], g["v_scale"])
+    sl = (g["seq_lens"] if seq_lens is None else torch.tensor(seq_lens, dtype=torch.int32)).cuda()
+    out = kv.int8_paged_attention(q, kc, vc, bt, sl, ks, vs, **kw)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    return out
+
+
+@pytest.mark.parametrize("name", ["attn_127_301", "attn_97_256"])
+@pytest.mark.parametrize("splits", [None, 1, 2, 4, 7, 64])
+def test_golden_cases(kv, name, splits):
+    g = load_golden(name)
+    out = _run_int8(kv, g, num_splits=splits)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (2, 28, 128)
+    _check(out, g["out_chain_f32"], g["out_loop_bf16"])
+
+
+@pytest.mark.parametrize("impl", ["auto", "v3", "v4"])
+def test_impl_names_are_accepted(kv, impl):
+    g = load_golden("attn_97_256")
+    _check(_run_int8(kv, g, impl=impl), g["out_chain_f32"], g["out_loop_bf16"])
+
+
+def test_unknown_impl_raises(kv):
+    g = load_golden("attn_97_256")
+    with pytest.raises(ValueError):
+        _run_int8(kv, g, impl="v5")
+
+
+def test_config1_before_and_after_the_written_token(kv):
+    g = load_golden("config1")
+    dev = "cuda"
+    kc = torch.zeros(g["key_cache"].shape, dtype=torch.int8, device=dev)
+    vc = torch.zeros_like(kc)
+    ks, vs, slots = g["k_scale"].cuda(), g["v_scale"].cuda(), g["slot_mapping"].cuda()
+    key, value = g["key"].cuda(), g["value"].cuda()
+    kv.int8_kv_cache_write(key[:512], value[:512], kc, vc, slots[:512], ks, vs)
+    q, bt = g["query"].cuda(), g["block_tables"].cuda()
+    out512 = kv.int8_paged_attention(q, kc, vc, bt, torch.tensor([512], dtype=torch.int32, device=dev), ks, vs)
+    _check(out512, g["out_ctx512_f32"])
+    kv.int8_kv_cache_write(key[512:], value[512:], kc, vc, slots[512:], ks, vs)
+    assert torch.equal(kc.cpu(), g["key_cache"]) and torch.equal(vc.cpu(), g["value_cache"])
+    out513 = kv.int8_paged_attention(q, kc, vc, bt, torch.tensor([513], dtype=torch.int32, device=dev), ks, vs)
+    _check(out513, g["out_ctx513_f32"])
+
+
+def _case_on_gpu(kv, workloads, seq_lens, shape=None, seed=0, **kw):
+    case = workloads.make_decode_case(seq_lens, shape or workloads.QWEN25_7B, seed=seed, **kw)
+    sh = case.shape
+    kc = torch.zeros(case.num_blocks, sh.block_size, sh.num_kv_heads, sh.head_dim, dtype=torch.int8)
+    vc = torch.zeros_like(kc)
+    oracle.cache_write(case.key, case.value, kc, vc, case.slot_mapping, case.k_scale, case.v_scale)
+    return case, kc, vc
+
+
+def test_every_length_1_to_48_and_every_split(kv, workloads):
+    """Ragged tails, single-token sequences, splits that end up empty."""
+    lens = list(range(1, 49))
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=2)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    q, kcd, vcd, bt, sl, ks, vs = _dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    for splits in (None, 1, 2, 3, 5):
+        out = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits=splits)
+        _check(out, want)
+    assert kv.device_status() == 0
+
+
+@pytest.mark.parametrize("B,seq", [(1, 512), (2, 1024), (4, 2048), (8, 4096)])
+def test_sweep_cells_int8_and_bf16_baseline(kv, workloads, B, seq):
+    case, kc, vc = _case_on_gpu(kv, workloads, [seq] * B, seed=B)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, [seq] * B, case.k_scale, case.v_scale)
+    q, kcd, vcd, bt, sl, ks, vs = _dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    out = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs)
+    _check(out, want)
+    # determinism: same launch twice gives the same bits
+    out2 = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs)
+    assert torch.equal(out, out2)
+    # BF16 baseline on the un-quantised cache with identical block tables
+    sh = case.shape
+    kb = torch.zeros(case.num_blocks, sh.block_size, sh.num_kv_heads, sh.head_dim, dtype=torch.bfloat16)
+    vb = torch.zeros_like(kb)
+    s = case.slot_mapping
+    kb[s // 16, s % 16] = case.key
+    vb[s // 16, s % 16] = case.value
+    want_b = oracle.float_paged_attention_oracle(case.query, kb, vb, case.block_tables, [seq] * B)
+    bf = package_bf16(kv)(q, kb.cuda(), vb.cuda(), bt, sl)
+    _check(bf, want_b)
+    assert kv.device_status() == 0
+
+
+def package_bf16(kv):
+    return kv.bf16_paged_attention
+
+
+def test_bf16_baseline_ragged_with_nan_padding(kv, workloads):
+    """Rows past seq_len in the last block may hold anything, NaN included; they must not leak."""
+    lens = [1, 15, 16, 17, 100, 333]
+    case = workloads.make_decode_case(lens, seed=4)
+    sh = case.shape
+    for dtype in (torch.bfloat16, torch.float16):
+        kb = torch.full((case.num_blocks, 16, sh.num_kv_heads, sh.head_dim), float("nan"), dtype=dtype)
+        vb = torch.full_like(kb, float("nan"))
+        s = case.slot_mapping
+        kb[s // 16, s % 16] = case.key.to(dtype)
+        vb[s // 16, s % 16] = case.value.to(dtype)
+        want = oracle.float_paged_attention_oracle(case.query, kb, vb, case.block_tables, lens)
+        for splits in (None, 1, 3):
+            out = kv.bf16_paged_attention(case.query.cuda(), kb.cuda(), vb.cuda(), case.block_tables.cuda(),
+                                          case.seq_lens.cuda(), num_splits=splits)
+            _check(out, want)
+
+
+@pytest.mark.parametrize("qdtype", [torch.float16, torch.float32])
+def test_query_dtypes_int64_tables_and_views(kv, workloads, qdtype):
+    lens = [77, 513, 260]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=6)
+    q = case.query.to(qdtype)
+    want = oracle.int8_paged_attention_oracle(q, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    # query as a non-owning slice of a padded buffer, int64 tables wider than needed with garbage beyond the end
+    padded = torch.zeros(8, 28, 128, dtype=qdtype, device="cuda")
+    padded[:3] = q.cuda()
+    wide = torch.full((3, case.block_tables.shape[1] + 9), 10 ** 6, dtype=torch.int64)
+    for b, T in enumerate(lens):
+        n = (T + 15) // 16
+        wide[b, :n] = case.block_tables[b, :n]
+    out = kv.int8_paged_attention(padded[:3], kc.cuda(), vc.cuda(), wide.cuda(), case.seq_lens.to(torch.int64).cuda(),
+                                  case.k_scale.double().cuda(), case.v_scale.double().cuda())
+    assert out.dtype == qdtype
+    out_f = out.float().cpu()
+    assert cosine(out_f, want) >= MIN_COS and max_abs(out_f, want) <= MAX_ABS
+    assert kv.device_status() == 0
+
+
+def test_generic_path_shapes(kv, workloads):
+    """Shapes outside the tiled kernels: head_dim 64, block size 8, GQA group 16, MHA."""
+    for (hq, hkv, d, bs) in [(8, 2, 64, 8), (32, 2, 128, 16), (4, 4, 96, 16)]:
+        shape = workloads.LayerShape(hq, hkv, d, bs)
+        lens = [5, 64, 131]
+        case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=hq)
+        want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+        for splits in (None, 1, 3):
+            out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
+                                                case.k_scale, case.v_scale), num_splits=splits)
+            _check(out, want)
+
+
+def test_larger_block_size_and_group_of_8(kv, workloads):
+    shape = workloads.LayerShape(64, 8, 128, 32)  # 72B-style GQA 8:1, 32-token blocks
+    lens = [31, 32, 33, 700]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=8)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    for splits in (None, 1, 4):
+        out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
+                                            case.k_scale, case.v_scale), num_splits=splits)
+        _check(out, want)
+    assert kv.device_status() == 0
+
+
+def test_quantize_q_matches_its_definition(kv, workloads):
+    from conftest import package
+
+    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
+    lens = [200, 45]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=10)
+    want = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
+    out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
+                                        case.k_scale, case.v_scale), quantize_q=True)
+    assert cosine(out.float().cpu(), want.float()) >= MIN_COS
+    assert max_abs(out.float().cpu(), want.float()) <= MAX_ABS
+
+
+def test_max_seq_len_hint_skips_validation_and_zero_length_is_safe(kv, workloads):
+    lens = [40, 0, 17]
+    case = workloads.make_decode_case([40, 1, 17], seed=12)
+    sh = case.shape
+    kc = torch.zeros(case.num_blocks, 16, sh.num_kv_heads, sh.head_dim, dtype=torch.int8)
+    vc = torch.zeros_like(kc)
+    oracle.cache_write(case.key, case.value, kc, vc, case.slot_mapping, case.k_scale, case.v_scale)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, sl, case.k_scale, case.v_scale),
+                                  max_seq_len=48)
+    out = out.float().cpu()
+    assert torch.isfinite(out).all() and float(out[1].abs().max()) == 0.0
+    want = oracle.int8_paged_attention_oracle(case.query[[0, 2]], kc, vc, case.block_tables[[0, 2]], [40, 17],
+                                              case.k_scale, case.v_scale)
+    assert cosine(out[[0, 2]], want) >= MIN_COS
+    with pytest.raises(AssertionError):  # the reference's host check: every seq_len > 0
+        kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, sl, case.k_scale, case.v_scale))
+
+
+def test_partial_rows_and_merge_reproduce_a_sequence_split(kv, workloads):
+    """Each 'rank' holds a contiguous range of every sequence's blocks in its own local cache; partial rows
+    merged on one device must equal attention over the whole sequence."""
+    lens = [1000, 333, 64]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=14)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    R = 4
+    per_rank_blocks = 16  # rank r owns logical blocks [16r, 16r+16)
+    parts = []
+    for r in range(R):
+        lo = r * per_rank_blocks
+        local_bt = case.block_tables[:, lo : lo + per_rank_blocks].contiguous()
+        local_len = torch.tensor([max(0, min(T - lo * 16, per_rank_blocks * 16)) for T in lens], dtype=torch.int32)
+        if local_bt.shape[1] == 0:
+            local_bt = torch.zeros(len(lens), 1, dtype=torch.int32)
+        parts.append(kv.int8_paged_attention_partial(*_dev(case.query, kc, vc, local_bt, local_len,
+                                                           case.k_scale, case.v_scale)))
+    merged = kv.merge_partials(torch.stack(parts).contiguous(), 128, dtype=torch.bfloat16)
+    _check(merged, want)
+    assert kv.device_status() == 0
