@@ -711,7 +711,7 @@ constexpr int kF16Stages = 3;
 
 // The dynamic shared-memory limit is raised once per (kernel, device); later calls, which may sit inside a
 // stream capture, launch without touching function attributes.
-template <typename K>
+template <int KERNEL_TAG, typename K>  // the tag keeps one flag array per kernel: the kernels share a signature
 static int set_smem(K kernel, int bytes) {
   static std::atomic<bool> done[64];
   int dev = 0;
@@ -731,7 +731,7 @@ static int64_t tiled_ctas(const AttnParams& p) {
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
   constexpr int smem = kTiledWarpsPerCta * kInt8Stages * 4096 + kTiledWarpsPerCta * kInt8Stages * 8 + 1024;
   auto kernel = paged_attn_int8_kernel<kInt8Stages>;
-  if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+  if (set_smem<0>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
   const int64_t ctas = tiled_ctas(p);
   if (ctas <= 0) return INT8KV_OK;
   kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
@@ -744,11 +744,11 @@ int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUt
   if (ctas <= 0) return INT8KV_OK;
   if (p.cache_kind == kCacheBf16) {
     auto kernel = paged_attn_f16_kernel<kF16Stages, true>;
-    if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+    if (set_smem<1>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
     kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
   } else {
     auto kernel = paged_attn_f16_kernel<kF16Stages, false>;
-    if (set_smem(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+    if (set_smem<2>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
     kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
   }
   return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;

@@ -1,0 +1,107 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol the header declares, and its
+host-only functions and argument validation behave (no kernel is launched here)."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from conftest import REPO, package
+
+HEADER = REPO / "include" / "int8kv_b200.h"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return package("_lib").load()
+
+
+def declared_symbols():
+    return sorted(set(re.findall(r"\b(int8kv_[a-z0-9_]+)\s*\(", HEADER.read_text())))
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    names = declared_symbols()
+    assert len(names) >= 12
+    bound = set(package("_lib").EXPORTED_SYMBOLS)
+    for n in names:
+        assert hasattr(lib, n), n
+        assert n in bound, f"{n} is declared in the header but has no ctypes signature"
+    assert bound <= set(names)
+
+
+def test_abi_version_and_status_strings(lib):
+    text = HEADER.read_text()
+    assert lib.int8kv_abi_version() == int(re.search(r"#define INT8KV_ABI_VERSION (\d+)", text).group(1))
+    codes = {n: int(v) for n, v in re.findall(r"#define (INT8KV_E_[A-Z_]+) \((-\d+)\)", text)}
+    assert len(codes) == 6
+    seen = set()
+    for name, code in codes.items():
+        s = lib.int8kv_status_str(code).decode()
+        assert s and s != "unknown status" and s not in seen
+        seen.add(s)
+    assert lib.int8kv_status_str(0).decode() == "ok"
+    assert lib.int8kv_status_str(-99).decode() == "unknown status"
+
+
+def test_workspace_sizing(lib):
+    rf = lib.int8kv_partial_row_floats(128)
+    assert rf == 132 and rf % 4 == 0
+    assert lib.int8kv_partial_row_floats(64) == 68
+    assert lib.int8kv_workspace_bytes(8, 28, 128, 1) == 16
+    assert lib.int8kv_workspace_bytes(8, 28, 128, 4) == 4 * 8 * 28 * 132 * 4 + 16
+    assert lib.int8kv_workspace_bytes(-1, 28, 128, 4) == -1
+    n = lib.int8kv_workspace_bytes(8, 28, 128, 4)
+    off = lib.int8kv_workspace_status_offset(n)
+    assert off % 16 == 0 and n - 16 <= off + 16 <= n
+    assert lib.int8kv_workspace_status_offset((1 << 20)) == (1 << 20) - 16
+
+
+def test_split_heuristic(lib):
+    cap = lib.int8kv_max_splits()
+    assert cap >= 16
+    # enough (sequence, head) pairs to fill 148 SMs: no split
+    assert lib.int8kv_choose_splits(1024, 4, 8192, 16, 148) == 1
+    # short sequences are never split below 128 tokens per part
+    assert lib.int8kv_choose_splits(1, 4, 100, 16, 148) == 1
+    assert lib.int8kv_choose_splits(1, 4, 512, 16, 148) == 4
+    # long single sequence: many splits, bounded by the cap
+    s = lib.int8kv_choose_splits(1, 4, 65536, 16, 148)
+    assert 32 <= s <= cap
+    for B in (1, 2, 4, 8):
+        for seq in (512, 1024, 2048, 4096):
+            s = lib.int8kv_choose_splits(B, 4, seq, 16, 148)
+            assert 1 <= s <= max(1, seq // 128)
+    # monotone: more sequences never ask for more splits
+    assert lib.int8kv_choose_splits(8, 4, 4096, 16, 148) <= lib.int8kv_choose_splits(1, 4, 4096, 16, 148)
+
+
+def test_argument_validation_returns_codes_before_any_launch(lib):
+    _lib = package("_lib")
+    st3, st4, st2 = _lib.i64([1, 1, 1]), _lib.i64([1, 1, 1, 1]), _lib.i64([1, 1])
+    # cache write: negative sizes, bad dtype, null pointers
+    assert lib.int8kv_cache_write(None, None, 0, -1, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.E_BAD_SHAPE
+    assert lib.int8kv_cache_write(None, None, 7, 1, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.E_BAD_DTYPE
+    assert lib.int8kv_cache_write(None, None, 0, 1, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.E_NULLPTR
+    assert lib.int8kv_cache_write(None, None, 0, 0, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.OK
+    # attention: Hq not a multiple of Hkv, bad dtype, null pointers, too many splits
+    def attn(q_dtype=0, B=1, Hq=28, Hkv=4, splits=0):
+        return lib.int8kv_paged_attn_int8(None, q_dtype, st3, B, Hq, Hkv, 128, None, None, st4, st4, 4, 16, None, 0, st2, 4,
+                                          None, 0, 64, None, None, None, 0, st3, splits, None, 0, 0, None)
+    assert attn(Hq=30) == _lib.E_BAD_SHAPE
+    assert attn(q_dtype=5) == _lib.E_BAD_DTYPE
+    assert attn() == _lib.E_NULLPTR
+    assert attn(B=0) == _lib.OK
+    assert attn(splits=10 ** 6) == _lib.E_BAD_SHAPE
+    assert lib.int8kv_merge_partials(None, 0, 1, 28, 128, None, 0, st3, None) == _lib.E_BAD_SHAPE
+    assert lib.int8kv_merge_partials(None, 2, 1, 28, 128, None, 0, st3, None) == _lib.E_NULLPTR
+    assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 2, st4, st4, 4, 16, None, 0, st2, 4,
+                                      None, 0, 64, None, 0, st3, 0, None, 0, None) == _lib.E_BAD_DTYPE
+
+
+def test_error_type_carries_the_status(lib):
+    _lib = package("_lib")
+    with pytest.raises(_lib.Int8KVError) as e:
+        _lib.check("int8kv_cache_write", _lib.E_WORKSPACE)
+    assert e.value.code == _lib.E_WORKSPACE and "workspace" in str(e.value)
