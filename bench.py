@@ -25,7 +25,6 @@ import importlib
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path
@@ -108,47 +107,73 @@ def build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed, with_bf16=Fals
 # clocks
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and clock-event reasons of one GPU every few milliseconds while a region runs
+    (NVML reads only; nothing is set)."""
 
-    def __init__(self, gpu_index: int):
+    REASONS = {
+        "hw_slowdown": 0x8,
+        "sw_thermal_slowdown": 0x20,
+        "hw_thermal_slowdown": 0x40,
+        "sw_power_cap": 0x4,
+    }
+
+    def __init__(self, gpu_index: int, period_s: float = 0.004):
         self.idx = gpu_index
-        self.proc = None
+        self.period = period_s
+        self.samples, self.reason_bits = [], 0
+        self.max_mhz = None
+        self._stop = None
+        self._thread = None
+        self._err = None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.idx < len(ids) and ids[self.idx].isdigit():
+                return int(ids[self.idx])
+        return self.idx
 
     def start(self):
+        import threading
+
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:  # the CUDA device's own UUID is unambiguous under any CUDA_VISIBLE_DEVICES remapping
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.idx).uuid)
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self._err = f"nvml unavailable: {type(e).__name__}"
+            return
+        self._stop = threading.Event()
+
+        def loop():
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop.is_set():
+                try:
+                    self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                    self.reason_bits |= int(get_reasons(h))
+                except Exception:
+                    pass
+                self._stop.wait(self.period)
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            text, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            text, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in text.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for n, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self._thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [self._err or "not sampled"]}
+        self._stop.set()
+        self._thread.join(2)
+        reasons = sorted(n for n, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(self.samples), "reasons": reasons}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -210,7 +235,11 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"])
     ap.add_argument("--num-splits", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
+    ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -218,6 +247,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     shape_kw, seq_lens, layers, desc = workload_spec(args.workload)
+    if args.batch:
+        seq_lens = seq_lens[: args.batch]
+        desc += f" (first {len(seq_lens)} sequences)"
+    if args.layers:
+        layers = args.layers
+        desc += f" ({layers} layer caches)"
     hq, hkv = shape_kw["hq"], shape_kw["hkv"]
     wl = importlib.import_module("int8-kvcache_b200.workloads")
     metric = "int8_paged_decode_attn_achieved_hbm_gbps"
@@ -274,9 +309,14 @@ def main():
         for _ in range(2):
             device_step()
         stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            device_step()
+        if args.no_graph:
+            class _Eager:
+                replay = staticmethod(device_step)
+            graph = _Eager()
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                device_step()
         for _ in range(args.warmup):
             graph.replay()
         stream.synchronize()
@@ -337,14 +377,16 @@ def main():
                 host_out[i].copy_(d_out, non_blocking=True)
             stream.synchronize()
 
-        for _ in range(args.warmup):
-            e2e_step()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_step()
-        barrier()
-        e2e_s = time.perf_counter() - t0
+        e2e_s = float("nan")
+        if not args.no_e2e:
+            for _ in range(args.warmup):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                e2e_step()
+            barrier()
+            e2e_s = time.perf_counter() - t0
         clocks = sampler.stop() if rank == 0 else None
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)

@@ -309,7 +309,8 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
 
 int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_q_heads, int head_dim, void* out,
                           int out_dtype, const int64_t out_strides[3], void* stream) {
-  if (num_parts <= 0 || batch < 0 || num_q_heads <= 0 || head_dim <= 0) return INT8KV_E_BAD_SHAPE;
+  if (num_parts <= 0 || num_parts > kMaxSplits || batch < 0 || num_q_heads <= 0 || head_dim <= 0)
+    return INT8KV_E_BAD_SHAPE;
   if (!valid_float_dtype(out_dtype)) return INT8KV_E_BAD_DTYPE;
   if (batch == 0) return INT8KV_OK;
   if (!parts || !out || !out_strides) return INT8KV_E_NULLPTR;

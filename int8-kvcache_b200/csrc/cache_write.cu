@@ -4,7 +4,7 @@
 // Arithmetic (bit-exact target): q = clamp(rint(float(x) / max(scale, 1e-6)), -127, 127) with an IEEE
 // fp32 division and round-half-to-even, i.e. the result of the reference's torch oracle
 // (src/quant.py:37-40) with the scale floor of its Triton kernel (src/triton_ops/int8_cache_write.py:50-51).
-// No fast-math: a reciprocal multiply is not bit-identical to the division.
+// No fast-math: a reciprocal multiply alone is not bit-identical to the division (see quant1).
 //
 // The kernel is a pure HBM stream (per token and KV head: 2*D*sizeof(in) bytes read, 2*D bytes written).
 // Vector path: each thread owns 16 consecutive elements of one (token, head) row of K and of V: it
@@ -14,10 +14,20 @@
 
 namespace int8kv {
 
-__device__ __forceinline__ int quant1(float x, float scale) {
-  float q = rintf(x / scale);          // div.rn.f32 then round-half-even
-  q = fminf(fmaxf(q, -127.f), 127.f);  // NaN -> -127 by fmaxf/fminf semantics is avoided below
-  return (x != x) ? 0 : static_cast<int>(q);
+// rint(x / scale) clamped to [-127, 127], bit-identical to IEEE division followed by round-half-even, at
+// the cost of one multiply in the common case.  x * (1/scale) is within 2 ulp of the true quotient; its
+// rounding to an integer can only differ from that of the correctly rounded quotient when the quotient is
+// within a few ulp of a tie k + 0.5 (ulp <= 2^-17 below 128), so exactly those elements — and anything
+// huge, infinite or NaN — take the real division.
+__device__ __forceinline__ int quant1(float x, float scale, float rscale) {
+  float q = x * rscale;
+  float n = rintf(q);
+  if (!(fabsf(q - n) < 0.5f - 6.2e-5f)) {
+    q = x / scale;  // div.rn.f32
+    n = rintf(q);
+  }
+  n = fminf(fmaxf(n, -127.f), 127.f);
+  return (x != x) ? 0 : static_cast<int>(n);
 }
 
 template <typename T>
@@ -38,14 +48,14 @@ __device__ __forceinline__ void load16(const T* p, float (&x)[16]) {
   for (int i = 0; i < 16; ++i) x[i] = to_f32<T>(e[i]);
 }
 
-__device__ __forceinline__ uint4 quant16(const float (&x)[16], float scale) {
+__device__ __forceinline__ uint4 quant16(const float (&x)[16], float scale, float rscale) {
   uint32_t w[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint32_t b0 = static_cast<uint32_t>(quant1(x[4 * i + 0], scale)) & 0xffu;
-    uint32_t b1 = static_cast<uint32_t>(quant1(x[4 * i + 1], scale)) & 0xffu;
-    uint32_t b2 = static_cast<uint32_t>(quant1(x[4 * i + 2], scale)) & 0xffu;
-    uint32_t b3 = static_cast<uint32_t>(quant1(x[4 * i + 3], scale)) & 0xffu;
+    uint32_t b0 = static_cast<uint32_t>(quant1(x[4 * i + 0], scale, rscale)) & 0xffu;
+    uint32_t b1 = static_cast<uint32_t>(quant1(x[4 * i + 1], scale, rscale)) & 0xffu;
+    uint32_t b2 = static_cast<uint32_t>(quant1(x[4 * i + 2], scale, rscale)) & 0xffu;
+    uint32_t b3 = static_cast<uint32_t>(quant1(x[4 * i + 3], scale, rscale)) & 0xffu;
     w[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
   }
   return make_uint4(w[0], w[1], w[2], w[3]);
@@ -76,8 +86,8 @@ __global__ void __launch_bounds__(256) cache_write_vec_kernel(const WriteParams 
     const int64_t off = slot - blk * p.block_size;
     int8_t* kd = p.kc + blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + c * 16;
     int8_t* vd = p.vc + blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + c * 16;
-    *reinterpret_cast<uint4*>(kd) = quant16(kx, ks);
-    *reinterpret_cast<uint4*>(vd) = quant16(vx, vs);
+    *reinterpret_cast<uint4*>(kd) = quant16(kx, ks, __frcp_rn(ks));
+    *reinterpret_cast<uint4*>(vd) = quant16(vx, vs, __frcp_rn(vs));
   }
 }
 
@@ -99,8 +109,8 @@ __global__ void __launch_bounds__(256) cache_write_elem_kernel(const WriteParams
     const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
     const int64_t blk = slot / p.block_size;
     const int64_t off = slot - blk * p.block_size;
-    p.kc[blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + d * p.kc_st[3]] = static_cast<int8_t>(quant1(kx, ks));
-    p.vc[blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + d * p.vc_st[3]] = static_cast<int8_t>(quant1(vx, vs));
+    p.kc[blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + d * p.kc_st[3]] = static_cast<int8_t>(quant1(kx, ks, __frcp_rn(ks)));
+    p.vc[blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + d * p.vc_st[3]] = static_cast<int8_t>(quant1(vx, vs, __frcp_rn(vs)));
   }
 }
 

@@ -22,6 +22,7 @@
 // O^T = V^T . P^T puts dims on M: the V^T A fragment needs pairs of tokens at one dim, produced by byte
 // interleaving (prmt) of 16-byte row pieces on the way to fp16.  v_scale and 1/l are applied once in the epilogue.
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -658,38 +659,75 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
 }
 
 // ---------------------------------------------------------------------------------------------
-// Merge of partial rows [R, rows, row_floats] (out | lse | pad): one warp per row
+// Merge of partial rows [R, rows, row_floats] (out | lse | pad): one CTA of four warps per row.
+// The weights exp(lse_r - max) are computed once, in parallel over r, into shared memory; then warp w
+// accumulates the parts r = w, w+4, ... with four independent 16-byte loads in flight per lane, and the four
+// warp sums are combined through shared memory.  Parts with lse = -inf have weight 0 and are not read (their
+// rows were never written).
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) merge_partials_kernel(const MergeParams p) {
+constexpr int kMergeWarps = 4;
+
+__global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(const MergeParams p) {
+  __shared__ float w_s[kMaxSplits];
+  __shared__ float red_s[kMergeWarps][4 * kWarp];
+  __shared__ float top_s[kMergeWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + warp;
-  if (row >= p.rows) return;
+  const int64_t row = blockIdx.x;
   const int64_t stride_r = p.rows * p.row_floats;
   const float* base = p.parts + row * p.row_floats;
-  float top = -INFINITY;
-  for (int r = lane; r < p.R; r += kWarp) top = fmaxf(top, base[r * stride_r + p.D]);
+
+  float lse = -INFINITY;
+  if (static_cast<int>(threadIdx.x) < p.R) lse = base[threadIdx.x * stride_r + p.D];  // R <= kMaxSplits = blockDim
+  float top = lse;
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
-  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row % p.Hq);
+  if (lane == 0) top_s[warp] = top;
+  __syncthreads();
+  top = fmaxf(fmaxf(top_s[0], top_s[1]), fmaxf(top_s[2], top_s[3]));
+  if (static_cast<int>(threadIdx.x) < p.R) w_s[threadIdx.x] = lse == -INFINITY ? 0.f : __expf(lse - top);
+  __syncthreads();
   float den = 0.f;
+  for (int r = lane; r < p.R; r += kWarp) den += w_s[r];
+  for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(kFull, den, o);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row % p.Hq);
+
   for (int d0 = 0; d0 < p.D; d0 += 4 * kWarp) {
     const int d = d0 + 4 * lane;
+    const bool live = d < p.D;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    den = 0.f;
-    for (int r = 0; r < p.R; ++r) {
-      const float lse = base[r * stride_r + p.D];
-      if (lse == -INFINITY) continue;  // empty part: its out row was never written
-      const float w = __expf(lse - top);
-      den += w;
-      if (d < p.D) {
-        const float4 o = *reinterpret_cast<const float4*>(base + r * stride_r + d);
-        a.x += w * o.x; a.y += w * o.y; a.z += w * o.z; a.w += w * o.w;
+    for (int r0 = warp; r0 < p.R; r0 += 4 * kMergeWarps) {
+      float w[4];
+      float4 o[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * kMergeWarps;
+        w[u] = r < p.R ? w_s[r] : 0.f;
+        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a.x += w[u] * o[u].x; a.y += w[u] * o[u].y; a.z += w[u] * o[u].z; a.w += w[u] * o[u].w;
       }
     }
-    if (d < p.D) {
-      const float inv = den > 0.f ? 1.f / den : 0.f;
-      a.x *= inv; a.y *= inv; a.z *= inv; a.w *= inv;
+    *reinterpret_cast<float4*>(&red_s[warp][4 * lane]) = a;
+    __syncthreads();
+    if (warp == 0 && live) {
+      const float4 x1 = *reinterpret_cast<const float4*>(&red_s[1][4 * lane]);
+      const float4 x2 = *reinterpret_cast<const float4*>(&red_s[2][4 * lane]);
+      const float4 x3 = *reinterpret_cast<const float4*>(&red_s[3][4 * lane]);
+      a.x = (a.x + x1.x + x2.x + x3.x) * inv;
+      a.y = (a.y + x1.y + x2.y + x3.y) * inv;
+      a.z = (a.z + x1.z + x2.z + x3.z) * inv;
+      a.w = (a.w + x1.w + x2.w + x3.w) * inv;
       if (p.part_out != nullptr) {
         *reinterpret_cast<float4*>(p.part_out + row * p.row_floats + d) = a;
+      } else if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
+                 ((reinterpret_cast<uintptr_t>(p.out) + 2 * (b * p.o_st[0] + hq * p.o_st[1] + d)) & 7u) == 0) {
+        uint2 v;
+        v.x = pack_bf162(a.x, a.y);
+        v.y = pack_bf162(a.z, a.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + b * p.o_st[0] + hq * p.o_st[1] + d) = v;
       } else {
         const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
         store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
@@ -698,8 +736,9 @@ __global__ void __launch_bounds__(128) merge_partials_kernel(const MergeParams p
         if (d + 3 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
       }
     }
+    __syncthreads();
   }
-  if (p.part_out != nullptr && lane == 0)
+  if (p.part_out != nullptr && threadIdx.x == 0)
     p.part_out[row * p.row_floats + p.D] = den > 0.f ? top + __logf(den) : -INFINITY;
 }
 
@@ -728,14 +767,35 @@ static int64_t tiled_ctas(const AttnParams& p) {
   return (items + kTiledWarpsPerCta - 1) / kTiledWarpsPerCta;
 }
 
-int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
-  constexpr int smem = kTiledWarpsPerCta * kInt8Stages * 4096 + kTiledWarpsPerCta * kInt8Stages * 8 + 1024;
-  auto kernel = paged_attn_int8_kernel<kInt8Stages>;
-  if (set_smem<0>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
+template <int NST>
+static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
+  constexpr int smem = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
+  auto kernel = paged_attn_int8_kernel<NST>;
+  if (set_smem<10 + NST>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
   const int64_t ctas = tiled_ctas(p);
   if (ctas <= 0) return INT8KV_OK;
   kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+// Ring depth: INT8KV_STAGES in the environment (read once) overrides the default, for tuning runs.
+static int int8_stage_choice() {
+  static const int choice = []() {
+    const char* e = std::getenv("INT8KV_STAGES");
+    const int v = e ? std::atoi(e) : kInt8Stages;
+    return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8) ? v : kInt8Stages;
+  }();
+  return choice;
+}
+
+int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
+  switch (int8_stage_choice()) {
+    case 2: return launch_int8_stages<2>(p, tmK, tmV, stream);
+    case 3: return launch_int8_stages<3>(p, tmK, tmV, stream);
+    case 6: return launch_int8_stages<6>(p, tmK, tmV, stream);
+    case 8: return launch_int8_stages<8>(p, tmK, tmV, stream);
+    default: return launch_int8_stages<4>(p, tmK, tmV, stream);
+  }
 }
 
 int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
@@ -764,7 +824,7 @@ int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
 
 int launch_merge(const MergeParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return INT8KV_OK;
-  merge_partials_kernel<<<static_cast<unsigned>((p.rows + 3) / 4), 128, 0, stream>>>(p);
+  merge_partials_kernel<<<static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
 
