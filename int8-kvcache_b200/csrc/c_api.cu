@@ -83,11 +83,11 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   if (B <= 0 || Hkv <= 0 || max_seq <= 0) return 1;
   const int64_t tiles = (max_seq + 15) / 16;
   const int64_t items = static_cast<int64_t>(B) * Hkv;
-  // One warp serves one (sequence, kv head, split).  Aim at about 12 warps per SM, never fewer than
-  // 8 tiles (128 tokens, 32 KB of INT8 K+V) per split so that the partial rows stay a small fraction of the
-  // traffic, and leave unsplit whatever already fills the machine.
-  const int64_t want = static_cast<int64_t>(sm_count) * 12;
-  if (items >= want) return 1;
+  // One warp serves one (sequence, kv head, split) and 12 warps are resident per SM.  Measured on B200: ragged
+  // batches balance best, and the tail of the last wave costs least, with about four waves of warps; short
+  // problems are latency-bound and want every SM busy even at 8 tiles (128 tokens) per split, below which the
+  // partial rows and their merge outweigh the gain.
+  const int64_t want = static_cast<int64_t>(sm_count) * 12 * 4;
   int64_t s = (want + items - 1) / items;
   const int64_t by_len = tiles / 8;
   if (s > by_len) s = by_len;
@@ -152,6 +152,7 @@ int run_attention(const AttnCall& a) {
   for (int i = 0; i < 4; ++i) { p.kc_st[i] = a.kc_st[i]; p.vc_st[i] = a.vc_st[i]; }
   p.num_blocks = a.num_blocks; p.block_size = a.block_size;
   p.tiles_per_block = a.block_size / 16;
+  p.hint_tiles = static_cast<int>(tiles);
   p.bt = a.bt; p.bt_is_i64 = a.bt_is_i64; p.bt_st[0] = a.bt_st[0]; p.bt_st[1] = a.bt_st[1]; p.bt_width = a.bt_width;
   p.sl = a.sl; p.sl_is_i64 = a.sl_is_i64;
   p.k_scale = a.k_scale; p.v_scale = a.v_scale;
@@ -175,8 +176,8 @@ int run_attention(const AttnCall& a) {
     if (!make_cache_map(&tmK, a.kc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.kc_st) ||
         !make_cache_map(&tmV, a.vc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.vc_st))
       return INT8KV_E_LAUNCH;
-    rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, a.stream)
-                                    : launch_attn_tiled_f16(p, tmK, tmV, a.stream);
+    rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, sm, a.stream)
+                                    : launch_attn_tiled_f16(p, tmK, tmV, sm, a.stream);
   } else {
     if (a.cache_kind != kCacheInt8 && a.quantize_q) return INT8KV_E_UNSUPPORTED;
     rc = launch_attn_generic(p, a.stream);

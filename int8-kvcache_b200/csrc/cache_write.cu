@@ -36,17 +36,22 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 
-// Load 16 consecutive elements (16-byte vector loads) and return them as floats.
+// 16 consecutive elements as raw 16-byte vectors (issued before anything depends on them) ...
 template <typename T>
-__device__ __forceinline__ void load16(const T* p, float (&x)[16]) {
-  constexpr int kVecs = 16 * sizeof(T) / 16;
-  uint4 raw[kVecs];
+struct Raw16 {
+  static constexpr int kVecs = 16 * sizeof(T) / 16;
+  uint4 v[kVecs];
+  __device__ __forceinline__ void load(const T* p) {
 #pragma unroll
-  for (int i = 0; i < kVecs; ++i) raw[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
-  const T* e = reinterpret_cast<const T*>(raw);
+    for (int i = 0; i < kVecs; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  }
+  // ... and their float values
+  __device__ __forceinline__ void to_float(float (&x)[16]) const {
+    const T* e = reinterpret_cast<const T*>(v);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) x[i] = to_f32<T>(e[i]);
-}
+    for (int i = 0; i < 16; ++i) x[i] = to_f32<T>(e[i]);
+  }
+};
 
 __device__ __forceinline__ uint4 quant16(const float (&x)[16], float scale, float rscale) {
   uint32_t w[4];
@@ -73,15 +78,19 @@ __global__ void __launch_bounds__(256) cache_write_vec_kernel(const WriteParams 
     const int rem = static_cast<int>(idx - t * per_token);
     const int h = rem / chunks;
     const int c = rem - h * chunks;
+    // the slot and the K/V vectors are independent loads: all are in flight before the first use
     const int64_t slot = load_index(p.slots, p.slot_is_i64, t);
-    if (slot < 0 || slot >= p.num_slots) continue;
     const T* kp = reinterpret_cast<const T*>(p.key) + t * p.k_st[0] + h * p.k_st[1] + c * 16;
     const T* vp = reinterpret_cast<const T*>(p.value) + t * p.v_st[0] + h * p.v_st[1] + c * 16;
-    float kx[16], vx[16];
-    load16<T>(kp, kx);
-    load16<T>(vp, vx);
+    Raw16<T> kr, vr;
+    kr.load(kp);
+    vr.load(vp);
     const float ks = fmaxf(__ldg(p.k_scale + h), 1e-6f);
     const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
+    if (slot < 0 || slot >= p.num_slots) continue;
+    float kx[16], vx[16];
+    kr.to_float(kx);
+    vr.to_float(vx);
     const int64_t blk = slot / p.block_size;
     const int64_t off = slot - blk * p.block_size;
     int8_t* kd = p.kc + blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + c * 16;

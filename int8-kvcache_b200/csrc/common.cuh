@@ -36,6 +36,75 @@ __device__ __forceinline__ int64_t load_index(const void* base, int is_i64, int6
                 : static_cast<int64_t>(reinterpret_cast<const int32_t*>(base)[idx]);
 }
 
+// 32 consecutive elements of a float tensor starting at element `off` (element stride `stride`) -> floats;
+// 16-byte vector loads when the run is contiguous and aligned.
+__device__ __forceinline__ void load32_as_float(const void* base, int dtype, int64_t off, int64_t stride, float (&x)[32]) {
+  const int esz = dtype == INT8KV_FP32 ? 4 : 2;
+  const char* ptr = reinterpret_cast<const char*>(base) + off * esz;
+  if (stride == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) {
+    if (dtype == INT8KV_FP32) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(ptr) + i);
+        x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(ptr) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f;
+          if (dtype == INT8KV_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+          else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+          x[8 * i + 2 * j] = f.x;
+          x[8 * i + 2 * j + 1] = f.y;
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) x[i] = load_as_float(base, dtype, off + i * stride);
+  }
+}
+
+// 16 consecutive output elements from floats; 16-byte vector stores when contiguous and aligned.
+__device__ __forceinline__ void store16_from_float(void* base, int dtype, int64_t off, int64_t stride, const float (&x)[16]) {
+  const int esz = dtype == INT8KV_FP32 ? 4 : 2;
+  char* ptr = reinterpret_cast<char*>(base) + off * esz;
+  if (stride == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) {
+    if (dtype == INT8KV_FP32) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        reinterpret_cast<float4*>(ptr)[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+    } else {
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (dtype == INT8KV_BF16) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __half2 h = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      reinterpret_cast<uint4*>(ptr)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(ptr)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) store_from_float(base, dtype, off + i * stride, x[i]);
+  }
+}
+
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start while
+// its predecessor drains; it must pass grid_dependency_wait() before touching memory the predecessor wrote.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __host__ __device__ __forceinline__ int dtype_bytes(int dtype) { return dtype == INT8KV_FP32 ? 4 : 2; }
 
 // ---------------------------------------------------------------------------------------------
@@ -59,25 +128,27 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+// One attempt to observe the completion of a phase: the hardware may suspend the thread for up to
+// `hint_ns` nanoseconds while the phase is pending, then returns whether it completed.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
       : "memory");
   return done != 0;
 }
 
-// Wait for a phase of `bar` with an iteration limit (a wait that cannot finish must not hang the GPU).
+// Wait for a phase of `bar` with an attempt limit (a wait that cannot finish must not hang the GPU): each
+// attempt suspends for at most about a microsecond, so the default limit gives up after roughly a second.
 // Returns false when the limit ran out.
-constexpr uint32_t kWaitSpinLimit = 1u << 22;
+constexpr uint32_t kWaitSpinLimit = 1u << 20;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit = kWaitSpinLimit) {
   for (uint32_t it = 0; it < limit; ++it) {
-    if (mbar_test(bar, parity)) return true;
-    if (it > 64) __nanosleep(it > 4096 ? 256 : 32);
+    if (mbar_try_wait(bar, parity, 1000u)) return true;
   }
   return false;
 }
@@ -124,6 +195,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// INT8 tensor-core MMA m16n8k32, int32 accumulate: A rows x 32 signed bytes, B 32 signed bytes x 8 columns.
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 

@@ -41,6 +41,7 @@ struct AttnParams {
   int64_t num_blocks;
   int block_size;
   int tiles_per_block;  // block_size / 16 (tiled kernels)
+  int hint_tiles;       // ceil(max_seq_len hint / 16): sizes the grid and seeds the block-table prefetch
   const void* bt;
   int bt_is_i64;
   int64_t bt_st[2];
@@ -73,8 +74,10 @@ struct MergeParams {
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
-int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream);
-int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream);
+int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                           cudaStream_t stream);
+int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                          cudaStream_t stream);
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
 

@@ -23,6 +23,8 @@
 // interleaving (prmt) of 16-byte row pieces on the way to fp16.  v_scale and 1/l are applied once in the epilogue.
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
+#include <utility>
 
 #include "common.cuh"
 
@@ -57,17 +59,31 @@ struct TileRing {
     return static_cast<int>(load_index(bt_row, bt_is_i64, lb * bt_stride));
   }
 
-  __device__ __forceinline__ void init(int lane_) {
+  // Barrier set-up plus a speculative load of the first two block-id windows at `guess_lb0`, so that the
+  // block-table read overlaps the seq_lens read that the true range depends on.
+  __device__ __forceinline__ void init(int lane_, int guess_lb0) {
     lane = lane_;
     if (lane == 0) {
 #pragma unroll
       for (int s = 0; s < NST; ++s) mbar_init(bar0 + 8 * s, 1);
       mbar_fence_init();
     }
+    lb0 = guess_lb0;
     cur_win = 0;
     bt_cur = load_window(0);
     bt_next = load_window(1);
     __syncwarp();
+  }
+
+  // Fix the range once it is known; the windows are reloaded only when the guess was wrong.
+  __device__ __forceinline__ void set_range(int t0_, int tpb_) {
+    t0 = t0_;
+    const int real_lb0 = t0_ / tpb_;
+    if (real_lb0 != lb0) {
+      lb0 = real_lb0;
+      bt_cur = load_window(0);
+      bt_next = load_window(1);
+    }
   }
 
   // Issue the loads of tile ordinal i (tile t0 + i) into stage i % NST.  Called by all lanes, in order of i.
@@ -112,13 +128,26 @@ struct ItemCoord {
   int t0, t1;        // tile range of this split
 };
 
-__device__ __forceinline__ bool decode_item(const AttnParams& p, int64_t item, ItemCoord& it) {
+// Which (sequence, kv head, split) a work item is: arithmetic only.
+__device__ __forceinline__ bool item_coords(const AttnParams& p, int64_t item, ItemCoord& it) {
   const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
   if (item >= total) return false;
   it.h = static_cast<int>(item % p.Hkv);
   const int64_t r = item / p.Hkv;
   it.c = static_cast<int>(r % p.num_splits);
   it.b = static_cast<int>(r / p.num_splits);
+  return true;
+}
+
+// First logical block of split c if the sequence had the hinted maximum length (the guess used to start the
+// block-table read early; exact for batches of full-length sequences).
+__device__ __forceinline__ int guessed_first_block(const AttnParams& p, int c) {
+  const int per = (p.hint_tiles + p.num_splits - 1) / p.num_splits;
+  return (c * per) / p.tiles_per_block;
+}
+
+// The tile range of the item: reads seq_lens[b]; every sequence splits its own tiles evenly.
+__device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   int64_t sl = load_index(p.sl, p.sl_is_i64, it.b);
   const int64_t cap = p.bt_width * p.block_size;
   if (sl > cap) sl = cap;
@@ -128,7 +157,6 @@ __device__ __forceinline__ bool decode_item(const AttnParams& p, int64_t item, I
   const int per = (ntiles + p.num_splits - 1) / p.num_splits;
   it.t0 = it.c * per;
   it.t1 = min(it.t0 + per, ntiles);
-  return true;
 }
 
 // Result of an empty tile range: zeros to `out` (direct mode) or lse = -inf (partial mode).
@@ -148,26 +176,67 @@ __device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord
 // ---------------------------------------------------------------------------------------------
 // INT8 cache, D = 128, group <= 8
 // ---------------------------------------------------------------------------------------------
+// One V tile (16 tokens x 128 dims of one head, swizzled in shared memory) times P^T (two B registers):
+// acc[j] += V^T[dims 16g+2j, 16g+2j+1 | tokens] . P^T.  `vx` are the lane's four 16-byte row pieces
+// (tokens 2t, 2t+1, 2t+8, 2t+9; dims 16g..16g+15).
+__device__ __forceinline__ void pv_tile(float (&acc)[8][4], const uint4 (&vx)[4], uint32_t pb0, uint32_t pb1) {
+  const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&vx[0]);
+  const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&vx[1]);
+  const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&vx[2]);
+  const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&vx[3]);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t x0 = w0[c] ^ 0x80808080u, x1 = w1[c] ^ 0x80808080u;
+    const uint32_t x2 = w2[c] ^ 0x80808080u, x3 = w3[c] ^ 0x80808080u;
+    const uint32_t lo01 = prmt(x0, x1, 0x5140u), hi01 = prmt(x0, x1, 0x7362u);
+    const uint32_t lo23 = prmt(x2, x3, 0x5140u), hi23 = prmt(x2, x3, 0x7362u);
+    mma_f16(acc[2 * c], u8pair_to_half2(lo01, 0x4140u), u8pair_to_half2(lo01, 0x4342u),
+            u8pair_to_half2(lo23, 0x4140u), u8pair_to_half2(lo23, 0x4342u), pb0, pb1);
+    mma_f16(acc[2 * c + 1], u8pair_to_half2(hi01, 0x4140u), u8pair_to_half2(hi01, 0x4342u),
+            u8pair_to_half2(hi23, 0x4140u), u8pair_to_half2(hi23, 0x4342u), pb0, pb1);
+  }
+}
+
+// Raw integer scores of one K tile: s[0..3] = 256 * (K . Qhi^T) + (K . Qlo^T) on the C fragment
+// (rows = tokens g / g+8, cols = heads 2t / 2t+1).  The K bytes go to the tensor core as they are.
+__device__ __forceinline__ void qk_tile(int (&s)[4], uint32_t kbase, const uint32_t (&koff)[4], const uint32_t (&qh)[8],
+                                        const uint32_t (&ql)[8], bool two_limbs) {
+  const uint4 a0 = lds128(kbase + koff[0]), a1 = lds128(kbase + koff[1]);
+  const uint4 c0 = lds128(kbase + koff[2]), c1 = lds128(kbase + koff[3]);
+  const uint32_t ka[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  const uint32_t kc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int st = 0; st < 4; ++st) mma_s8(lo, ka[2 * st], kc[2 * st], ka[2 * st + 1], kc[2 * st + 1], ql[2 * st], ql[2 * st + 1]);
+  if (two_limbs) {
+#pragma unroll
+    for (int st = 0; st < 4; ++st) mma_s8(hi, ka[2 * st], kc[2 * st], ka[2 * st + 1], kc[2 * st + 1], qh[2 * st], qh[2 * st + 1]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s[i] = (hi[i] << 8) + lo[i];
+}
+
 template <int NST>
-__global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp)
+__global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
+  static_assert(NST % 2 == 0, "tiles are consumed in pairs");
   constexpr int kStage = 4096;  // 16x128 K bytes + 16x128 V bytes
   extern __shared__ uint8_t smem_raw[];
+  const int wpc = blockDim.x >> 5;  // warps per CTA: 1 for small grids (spread over all SMs), 4 otherwise
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
 
+  grid_dependency_wait();  // inputs may come from the kernel launched just before this one
+
   ItemCoord it;
-  if (!decode_item(p, static_cast<int64_t>(blockIdx.x) * kTiledWarpsPerCta + warp, it)) return;
-  if (it.t0 >= it.t1) {
-    write_empty(p, it, lane);
-    return;
-  }
+  if (!item_coords(p, static_cast<int64_t>(blockIdx.x) * wpc + warp, it)) return;
+  grid_launch_dependents();
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   TileRing<NST, kStage, 1> ring;
   ring.stage0 = smem_base + warp * (NST * kStage);
-  ring.bar0 = smem_base + kTiledWarpsPerCta * NST * kStage + warp * (NST * 8);
+  ring.bar0 = smem_base + wpc * NST * kStage + warp * (NST * 8);
   ring.tmK = &tmK;
   ring.tmV = &tmV;
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
@@ -176,102 +245,127 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   ring.bt_limit = p.bt_width;
   ring.tpb = p.tiles_per_block;
   ring.head = it.h;
-  ring.t0 = it.t0;
-  ring.lb0 = it.t0 / p.tiles_per_block;
   if (lane == 0) {
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
   }
-  ring.init(lane);
+  ring.init(lane, guessed_first_block(p, it.c));
+  item_range(p, it);
+  if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
+    write_empty(p, it, lane);
+    return;
+  }
+  ring.set_range(it.t0, p.tiles_per_block);
 
   const int n = it.t1 - it.t0;
   const int pre = n < NST ? n : NST;
   for (int i = 0; i < pre; ++i) ring.issue(i);
 
-  // ---- Q fragments: lane (g, t) holds head g of the group, dims [32t, 32t+32) as 16 half2 -------------
-  uint32_t qf[16];
-  float q_mul = 1.f;  // per-head multiplier of the raw dot product (query quantisation scale)
+  // ---- Q as two INT8 limbs: lane (g, t) holds head g of the group, dims [32t, 32t+32), 4 dims per word ----
+  // q ~= q_mul * (256 * hi + lo) with |256 hi + lo| <= 32000: 16-bit fixed point per head, finer than the bf16
+  // the query arrives in for every element that matters to the dot product.  With quantize_q the reference's
+  // INT8 query (absmax/127, half away from zero) sits in the low limb alone.
+  uint32_t qh[8], ql[8];
+  float q_mul;
+  const bool two_limbs = !p.quantize_q;
   {
     float qv[32];
     const int hq = it.h * p.G + g;
     if (g < p.G) {
-      const int64_t base = it.b * p.q_st[0] + hq * p.q_st[1];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) qv[i] = load_as_float(p.q, p.q_dtype, base + (32 * t + i) * p.q_st[2]);
+      load32_as_float(p.q, p.q_dtype, it.b * p.q_st[0] + hq * p.q_st[1] + 32 * t * p.q_st[2], p.q_st[2], qv);
     } else {
 #pragma unroll
       for (int i = 0; i < 32; ++i) qv[i] = 0.f;
     }
-    if (p.quantize_q) {
-      float amax = 0.f;
+    float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
-      amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
+    int qi[32];
+    if (p.quantize_q) {
       const float qs = fmaxf(amax / 127.f, 1e-6f);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float s = qv[i] / qs;
-        const float r = s >= 0.f ? floorf(s + 0.5f) : -floorf(-s + 0.5f);  // half away from zero
-        qv[i] = fminf(fmaxf(r, -127.f), 127.f);
+        const float x = qv[i] / qs;
+        const float r = x >= 0.f ? floorf(x + 0.5f) : -floorf(-x + 0.5f);  // half away from zero
+        qi[i] = static_cast<int>(fminf(fmaxf(r, -127.f), 127.f));
       }
       q_mul = qs;
+    } else {
+      const float inv = amax > 0.f ? 32000.f / amax : 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) qi[i] = __float2int_rn(qv[i] * inv);
+      q_mul = amax > 0.f ? amax / 32000.f : 0.f;
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) qf[i] = pack_half2(qv[2 * i], qv[2 * i + 1]);
+    for (int w = 0; w < 8; ++w) {
+      uint32_t hw = 0, lw = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int v = qi[4 * w + e];
+        const int h = two_limbs ? ((v + 128) >> 8) : 0;
+        const int l = v - (h << 8);
+        hw |= (static_cast<uint32_t>(h) & 0xffu) << (8 * e);
+        lw |= (static_cast<uint32_t>(l) & 0xffu) << (8 * e);
+      }
+      qh[w] = hw;
+      ql[w] = lw;
+    }
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
   const float kmul = fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
   const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
   const float sc1 = kmul * __shfl_sync(kFull, q_mul, (2 * t + 1) * 4);
 
+  // swizzled offsets of this lane's row pieces inside a K tile and a V tile (constant over the loop)
+  const uint32_t koff[4] = {swz128(g, 2 * t), swz128(g, 2 * t + 1), swz128(g + 8, 2 * t), swz128(g + 8, 2 * t + 1)};
+  const uint32_t voff[4] = {swz128(2 * t, g), swz128(2 * t + 1, g), swz128(2 * t + 8, g), swz128(2 * t + 9, g)};
+
   float acc[8][4];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
+  // Two tiles (32 tokens) per iteration: two independent score chains, one max reduction, one rescale test.
+  // When the range holds an odd number of tiles the last pair's second tile is all-masked; its stage holds
+  // stale bytes, which are finite integers and meet p = 0.
   bool timed_out = false;
   int i = 0;
-  for (; i < n; ++i) {
-    if (!ring.wait(i)) {
+  for (; i < n; i += 2) {
+    const bool second = i + 1 < n;
+    bool ok = ring.wait(i);
+    if (ok && second) ok = ring.wait(i + 1);
+    if (!ok) {
       timed_out = true;
       break;
     }
-    const uint32_t kb = ring.stage(i);
-    const uint32_t vb = kb + 2048;
+    const uint32_t sA = ring.stage(i), sB = ring.stage(i + 1);
 
-    // ---- S^T = K . Q^T ------------------------------------------------------------------------------
-    uint32_t ka[8], kc[8];
-    {
-      const uint4 a0 = lds128(kb + swz128(g, 2 * t)), a1 = lds128(kb + swz128(g, 2 * t + 1));
-      const uint4 c0 = lds128(kb + swz128(g + 8, 2 * t)), c1 = lds128(kb + swz128(g + 8, 2 * t + 1));
-      ka[0] = a0.x; ka[1] = a0.y; ka[2] = a0.z; ka[3] = a0.w; ka[4] = a1.x; ka[5] = a1.y; ka[6] = a1.z; ka[7] = a1.w;
-      kc[0] = c0.x; kc[1] = c0.y; kc[2] = c0.z; kc[3] = c0.w; kc[4] = c1.x; kc[5] = c1.y; kc[6] = c1.z; kc[7] = c1.w;
-    }
-    // V pieces are requested now so that their latency hides under the score phase
-    uint4 vx[4];
-    vx[0] = lds128(vb + swz128(2 * t, g));
-    vx[1] = lds128(vb + swz128(2 * t + 1, g));
-    vx[2] = lds128(vb + swz128(2 * t + 8, g));
-    vx[3] = lds128(vb + swz128(2 * t + 9, g));
-
-    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    int ia[4], ib[4];
+    qk_tile(ia, sA, koff, qh, ql, two_limbs);
+    qk_tile(ib, sB, koff, qh, ql, two_limbs);
+    uint4 va[4], vb[4];
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      const uint32_t wa = ka[s] ^ 0x80808080u, wc = kc[s] ^ 0x80808080u;
-      const uint32_t a0 = u8pair_to_half2(wa, 0x4140u), a2 = u8pair_to_half2(wa, 0x4342u);
-      const uint32_t a1 = u8pair_to_half2(wc, 0x4140u), a3 = u8pair_to_half2(wc, 0x4342u);
-      if (s & 1) mma_f16(sb, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
-      else mma_f16(sa, a0, a1, a2, a3, qf[2 * s], qf[2 * s + 1]);
+    for (int r = 0; r < 4; ++r) {
+      va[r] = lds128(sA + 2048 + voff[r]);
+      vb[r] = lds128(sB + 2048 + voff[r]);
     }
 
-    // ---- online softmax on the C fragment: rows = tokens g / g+8, cols = heads 2t / 2t+1 ---------------
+    // ---- online softmax on the C fragments: rows = tokens g, g+8 (tile A) and 16+g, 24+g (tile B) ----------
     const int tok0 = (it.t0 + i) * kTile + g;
-    float v0 = (sa[0] + sb[0]) * sc0, v1 = (sa[1] + sb[1]) * sc1;
-    float v2 = (sa[2] + sb[2]) * sc0, v3 = (sa[3] + sb[3]) * sc1;
-    if (tok0 >= it.seq_len) v0 = v1 = -INFINITY;
-    if (tok0 + 8 >= it.seq_len) v2 = v3 = -INFINITY;
-    float mx0 = fmaxf(v0, v2), mx1 = fmaxf(v1, v3);
+    float v[8];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      v[r] = static_cast<float>(ia[r]) * ((r & 1) ? sc1 : sc0);
+      v[4 + r] = static_cast<float>(ib[r]) * ((r & 1) ? sc1 : sc0);
+    }
+    if (tok0 >= it.seq_len) v[0] = v[1] = -INFINITY;
+    if (tok0 + 8 >= it.seq_len) v[2] = v[3] = -INFINITY;
+    if (!second || tok0 + 16 >= it.seq_len) v[4] = v[5] = -INFINITY;
+    if (!second || tok0 + 24 >= it.seq_len) v[6] = v[7] = -INFINITY;
+    float mx0 = fmaxf(fmaxf(v[0], v[2]), fmaxf(v[4], v[6]));
+    float mx1 = fmaxf(fmaxf(v[1], v[3]), fmaxf(v[5], v[7]));
     mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 4));
     mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 4));
     mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 8));
@@ -290,40 +384,31 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       m0 = mn0;
       m1 = mn1;
     }
-    const float p0 = exp2_fast(v0 - m0), p1 = exp2_fast(v1 - m1);
-    const float p2 = exp2_fast(v2 - m0), p3 = exp2_fast(v3 - m1);
-    l0 += p0 + p2;
-    l1 += p1 + p3;
-    // P^T as the B operand: (tokens 2t,2t+1 | head g) and (tokens 2t+8,2t+9 | head g)
-    const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
-    const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
-
-    // ---- O^T += V^T . P^T : rows = dims (16g+2j, 16g+2j+1), k = tokens, cols = heads ----------------------
-    const uint32_t* w0 = reinterpret_cast<const uint32_t*>(&vx[0]);
-    const uint32_t* w1 = reinterpret_cast<const uint32_t*>(&vx[1]);
-    const uint32_t* w2 = reinterpret_cast<const uint32_t*>(&vx[2]);
-    const uint32_t* w3 = reinterpret_cast<const uint32_t*>(&vx[3]);
+    float pr[8];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t x0 = w0[c] ^ 0x80808080u, x1 = w1[c] ^ 0x80808080u;
-      const uint32_t x2 = w2[c] ^ 0x80808080u, x3 = w3[c] ^ 0x80808080u;
-      const uint32_t lo01 = prmt(x0, x1, 0x5140u), hi01 = prmt(x0, x1, 0x7362u);
-      const uint32_t lo23 = prmt(x2, x3, 0x5140u), hi23 = prmt(x2, x3, 0x7362u);
-      mma_f16(acc[2 * c], u8pair_to_half2(lo01, 0x4140u), u8pair_to_half2(lo01, 0x4342u),
-              u8pair_to_half2(lo23, 0x4140u), u8pair_to_half2(lo23, 0x4342u), pb0, pb1);
-      mma_f16(acc[2 * c + 1], u8pair_to_half2(hi01, 0x4140u), u8pair_to_half2(hi01, 0x4342u),
-              u8pair_to_half2(hi23, 0x4140u), u8pair_to_half2(hi23, 0x4342u), pb0, pb1);
-    }
+    for (int r = 0; r < 8; ++r) pr[r] = exp2_fast(v[r] - ((r & 1) ? m1 : m0));
+    l0 += (pr[0] + pr[2]) + (pr[4] + pr[6]);
+    l1 += (pr[1] + pr[3]) + (pr[5] + pr[7]);
+    // P^T as B operands: (tokens 2t,2t+1 | head g), (tokens 2t+8,2t+9 | head g) for each tile
+    const uint32_t pa0 = movmatrix_trans(pack_half2(pr[0], pr[1]));
+    const uint32_t pa1 = movmatrix_trans(pack_half2(pr[2], pr[3]));
+    const uint32_t pb0 = movmatrix_trans(pack_half2(pr[4], pr[5]));
+    const uint32_t pb1 = movmatrix_trans(pack_half2(pr[6], pr[7]));
 
-    __syncwarp();  // every lane has consumed the stage before lane 0 refills it
+    // ---- O^T += V^T . P^T ------------------------------------------------------------------------------
+    pv_tile(acc, va, pa0, pa1);
+    pv_tile(acc, vb, pb0, pb1);
+
+    __syncwarp();  // every lane has consumed both stages before lane 0 refills them
     if (i + NST < n) ring.issue(i + NST);
+    if (i + 1 + NST < n) ring.issue(i + 1 + NST);
   }
 
   if (timed_out) {
     if (lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
     // drain the loads that were already issued, again with a limit, so that none lands after this warp left
     const int issued = (i + NST < n) ? i + NST : n;
-    for (int j = i + 1; j < issued; ++j) ring.wait(j, 1u << 16);
+    for (int j = i; j < issued; ++j) ring.wait(j, 1u << 12);
     return;
   }
 
@@ -350,9 +435,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       o[2 * j + 1] = acc[j][e + 2] * inv;
     }
     if (p.part == nullptr) {
-      const int64_t base = it.b * p.o_st[0] + hq * p.o_st[1];
-#pragma unroll
-      for (int d = 0; d < 16; ++d) store_from_float(p.out, p.out_dtype, base + (16 * g + d) * p.o_st[2], o[d]);
+      store16_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + 16 * g * p.o_st[2], p.o_st[2], o);
     } else {
       const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + hq;
       float4* dst = reinterpret_cast<float4*>(p.part + row * p.row_floats + 16 * g);
@@ -382,20 +465,19 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
                       const AttnParams p) {
   constexpr int kStage = 8192;  // K: two 16x128-byte halves (dims 0-63, 64-127), then V likewise
   extern __shared__ uint8_t smem_raw[];
+  const int wpc = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
 
+  grid_dependency_wait();
   ItemCoord it;
-  if (!decode_item(p, static_cast<int64_t>(blockIdx.x) * kTiledWarpsPerCta + warp, it)) return;
-  if (it.t0 >= it.t1) {
-    write_empty(p, it, lane);
-    return;
-  }
+  if (!item_coords(p, static_cast<int64_t>(blockIdx.x) * wpc + warp, it)) return;
+  grid_launch_dependents();
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   TileRing<NST, kStage, 2> ring;
   ring.stage0 = smem_base + warp * (NST * kStage);
-  ring.bar0 = smem_base + kTiledWarpsPerCta * NST * kStage + warp * (NST * 8);
+  ring.bar0 = smem_base + wpc * NST * kStage + warp * (NST * 8);
   ring.tmK = &tmK;
   ring.tmV = &tmV;
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
@@ -404,13 +486,17 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   ring.bt_limit = p.bt_width;
   ring.tpb = p.tiles_per_block;
   ring.head = it.h;
-  ring.t0 = it.t0;
-  ring.lb0 = it.t0 / p.tiles_per_block;
   if (lane == 0) {
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
   }
-  ring.init(lane);
+  ring.init(lane, guessed_first_block(p, it.c));
+  item_range(p, it);
+  if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
+    write_empty(p, it, lane);
+    return;
+  }
+  ring.set_range(it.t0, p.tiles_per_block);
 
   const int n = it.t1 - it.t0;
   const int pre = n < NST ? n : NST;
@@ -522,7 +608,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   if (timed_out) {
     if (lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
     const int issued = (i + NST < n) ? i + NST : n;
-    for (int j = i + 1; j < issued; ++j) ring.wait(j, 1u << 16);
+    for (int j = i + 1; j < issued; ++j) ring.wait(j, 1u << 12);
     return;
   }
 
@@ -574,6 +660,7 @@ __device__ __forceinline__ float cache_elem(const void* base, int kind, int64_t 
 }
 
 __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParams p) {
+  grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hq;
@@ -676,8 +763,18 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   const int64_t stride_r = p.rows * p.row_floats;
   const float* base = p.parts + row * p.row_floats;
 
+  grid_dependency_wait();  // the partial rows come from the attention kernel launched just before
   float lse = -INFINITY;
   if (static_cast<int>(threadIdx.x) < p.R) lse = base[threadIdx.x * stride_r + p.D];  // R <= kMaxSplits = blockDim
+  // The first batch of rows is requested before the weights exist, so that both reads share one latency.
+  // Rows of empty parts were never written: whatever they hold is discarded by the weight test below.
+  float4 pre[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int r = warp + u * kMergeWarps;
+    pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < p.R && 4 * lane < p.D) pre[u] = *reinterpret_cast<const float4*>(base + r * stride_r + 4 * lane);
+  }
   float top = lse;
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
   if (lane == 0) top_s[warp] = top;
@@ -698,16 +795,19 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
     for (int r0 = warp; r0 < p.R; r0 += 4 * kMergeWarps) {
       float w[4];
       float4 o[4];
+      const bool have = d0 == 0 && r0 == warp;  // this batch was prefetched
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int r = r0 + u * kMergeWarps;
         w[u] = r < p.R ? w_s[r] : 0.f;
-        o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (live && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
+        o[u] = pre[u];
+        if (!have && live && r < p.R && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        a.x += w[u] * o[u].x; a.y += w[u] * o[u].y; a.z += w[u] * o[u].z; a.w += w[u] * o[u].w;
+        if (w[u] > 0.f) {
+          a.x += w[u] * o[u].x; a.y += w[u] * o[u].y; a.z += w[u] * o[u].z; a.w += w[u] * o[u].w;
+        }
       }
     }
     *reinterpret_cast<float4*>(&red_s[warp][4 * lane]) = a;
@@ -748,6 +848,30 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 constexpr int kInt8Stages = 4;
 constexpr int kF16Stages = 3;
 
+static int env_int(const char* name, int fallback) {
+  const char* e = std::getenv(name);
+  return e ? std::atoi(e) : fallback;
+}
+
+// Tuning switches, read once from the environment: INT8KV_STAGES (ring depth of the INT8 kernel),
+// INT8KV_WPC (warps per CTA: 1 or 4, 0 = choose from the grid size), INT8KV_PDL (0 disables programmatic
+// dependent launch).
+struct Tuning {
+  int stages, wpc, pdl;
+};
+static const Tuning& tuning() {
+  static const Tuning t = []() {
+    Tuning x;
+    x.stages = env_int("INT8KV_STAGES", kInt8Stages);
+    if (x.stages != 2 && x.stages != 4 && x.stages != 6 && x.stages != 8) x.stages = kInt8Stages;
+    x.wpc = env_int("INT8KV_WPC", 0);
+    if (x.wpc != 1 && x.wpc != 4) x.wpc = 0;
+    x.pdl = env_int("INT8KV_PDL", 1) != 0;
+    return x;
+  }();
+  return t;
+}
+
 // The dynamic shared-memory limit is raised once per (kernel, device); later calls, which may sit inside a
 // stream capture, launch without touching function attributes.
 template <int KERNEL_TAG, typename K>  // the tag keeps one flag array per kernel: the kernels share a signature
@@ -762,70 +886,84 @@ static int set_smem(K kernel, int bytes) {
   return 0;
 }
 
-static int64_t tiled_ctas(const AttnParams& p) {
-  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
-  return (items + kTiledWarpsPerCta - 1) / kTiledWarpsPerCta;
+// Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while the previous
+// kernel in the stream drains; every kernel here calls grid_dependency_wait() before its first global access.
+template <typename... KArgs, typename... Args>
+static int launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tuning().pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+// Warps per CTA: a grid that cannot fill the machine with 4-warp CTAs is launched as 1-warp CTAs so that its
+// warps spread over all SMs instead of stacking four to an SM.
+static int pick_wpc(int64_t items, int sm_count) {
+  if (tuning().wpc) return tuning().wpc;
+  return items <= static_cast<int64_t>(sm_count) * 12 ? 1 : kTiledWarpsPerCta;
 }
 
 template <int NST>
-static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
-  constexpr int smem = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
+static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                              cudaStream_t stream) {
+  constexpr int smem_max = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
   auto kernel = paged_attn_int8_kernel<NST>;
-  if (set_smem<10 + NST>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
-  const int64_t ctas = tiled_ctas(p);
-  if (ctas <= 0) return INT8KV_OK;
-  kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
-  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+  if (set_smem<10 + NST>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
+  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  if (items <= 0) return INT8KV_OK;
+  const int wpc = pick_wpc(items, sm_count);
+  const size_t smem = static_cast<size_t>(wpc) * NST * 4096 + wpc * NST * 8 + 1024;
+  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
 }
 
-// Ring depth: INT8KV_STAGES in the environment (read once) overrides the default, for tuning runs.
-static int int8_stage_choice() {
-  static const int choice = []() {
-    const char* e = std::getenv("INT8KV_STAGES");
-    const int v = e ? std::atoi(e) : kInt8Stages;
-    return (v == 2 || v == 3 || v == 4 || v == 6 || v == 8) ? v : kInt8Stages;
-  }();
-  return choice;
-}
-
-int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
-  switch (int8_stage_choice()) {
-    case 2: return launch_int8_stages<2>(p, tmK, tmV, stream);
-    case 3: return launch_int8_stages<3>(p, tmK, tmV, stream);
-    case 6: return launch_int8_stages<6>(p, tmK, tmV, stream);
-    case 8: return launch_int8_stages<8>(p, tmK, tmV, stream);
-    default: return launch_int8_stages<4>(p, tmK, tmV, stream);
+int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                           cudaStream_t stream) {
+  switch (tuning().stages) {
+    case 2: return launch_int8_stages<2>(p, tmK, tmV, sm_count, stream);
+    case 6: return launch_int8_stages<6>(p, tmK, tmV, sm_count, stream);
+    case 8: return launch_int8_stages<8>(p, tmK, tmV, sm_count, stream);
+    default: return launch_int8_stages<4>(p, tmK, tmV, sm_count, stream);
   }
 }
 
-int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, cudaStream_t stream) {
-  constexpr int smem = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
-  const int64_t ctas = tiled_ctas(p);
-  if (ctas <= 0) return INT8KV_OK;
-  if (p.cache_kind == kCacheBf16) {
-    auto kernel = paged_attn_f16_kernel<kF16Stages, true>;
-    if (set_smem<1>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
-    kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
-  } else {
-    auto kernel = paged_attn_f16_kernel<kF16Stages, false>;
-    if (set_smem<2>(kernel, smem) != 0) return INT8KV_E_LAUNCH;
-    kernel<<<static_cast<unsigned>(ctas), kTiledWarpsPerCta * kWarp, smem, stream>>>(tmK, tmV, p);
-  }
-  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+template <bool IS_BF16>
+static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                      cudaStream_t stream) {
+  constexpr int smem_max = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
+  auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16>;
+  if (set_smem<IS_BF16 ? 1 : 2>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
+  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  if (items <= 0) return INT8KV_OK;
+  const int wpc = pick_wpc(items, sm_count);
+  const size_t smem = static_cast<size_t>(wpc) * kF16Stages * 8192 + wpc * kF16Stages * 8 + 1024;
+  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
+}
+
+int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                          cudaStream_t stream) {
+  return p.cache_kind == kCacheBf16 ? launch_f16<true>(p, tmK, tmV, sm_count, stream)
+                                    : launch_f16<false>(p, tmK, tmV, sm_count, stream);
 }
 
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
   if (p.D > kGenericMaxD) return INT8KV_E_UNSUPPORTED;
   const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hq;
   if (items <= 0) return INT8KV_OK;
-  paged_attn_generic_kernel<<<static_cast<unsigned>((items + 3) / 4), 128, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+  return launch_pdl(paged_attn_generic_kernel, static_cast<unsigned>((items + 3) / 4), 128, 0, stream, p);
 }
 
 int launch_merge(const MergeParams& p, cudaStream_t stream) {
   if (p.rows <= 0) return INT8KV_OK;
-  merge_partials_kernel<<<static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+  return launch_pdl(merge_partials_kernel, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p);
 }
 
 }  // namespace int8kv

@@ -61,8 +61,10 @@ def test_workspace_sizing(lib):
 def test_split_heuristic(lib):
     cap = lib.int8kv_max_splits()
     assert cap >= 16
-    # enough (sequence, head) pairs to fill 148 SMs: no split
-    assert lib.int8kv_choose_splits(1024, 4, 8192, 16, 148) == 1
+    # enough (sequence, head) pairs for four waves of warps on 148 SMs: no split
+    assert lib.int8kv_choose_splits(4096, 4, 8192, 16, 148) == 1
+    # a large ragged batch is still cut into a few parts per sequence for balance
+    assert 4 <= lib.int8kv_choose_splits(256, 4, 8192, 16, 148) <= 16
     # short sequences are never split below 128 tokens per part
     assert lib.int8kv_choose_splits(1, 4, 100, 16, 148) == 1
     assert lib.int8kv_choose_splits(1, 4, 512, 16, 148) == 4
@@ -75,6 +77,7 @@ def test_split_heuristic(lib):
             assert 1 <= s <= max(1, seq // 128)
     # monotone: more sequences never ask for more splits
     assert lib.int8kv_choose_splits(8, 4, 4096, 16, 148) <= lib.int8kv_choose_splits(1, 4, 4096, 16, 148)
+    assert lib.int8kv_choose_splits(0, 4, 4096, 16, 148) == 1
 
 
 def test_argument_validation_returns_codes_before_any_launch(lib):
