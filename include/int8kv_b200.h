@@ -5,8 +5,9 @@
  * types cross this boundary.  All calls are asynchronous on `stream` (a cudaStream_t passed
  * as void*), never synchronise the device, never allocate device memory and never throw:
  * they return 0 or a negative INT8KV_E_* code.  The caller owns every buffer, including the
- * split-KV workspace.  The library keeps no mutable state apart from a per-device "kernel
- * attributes configured" flag, so it may be called from several host threads and streams.
+ * split-KV workspace (int8kv_paged_attn_int8_static_ws, which brings its own, is the one
+ * exception and says so).  The library keeps no mutable state apart from per-device "set up
+ * once" flags, so it may be called from several host threads and streams.
  *
  * Tensor conventions (the reference prototype cjsmt/Int8-kvcache uses the same ones):
  *   key/value (new tokens)  [T, Hkv, D]                bf16 / fp16 / fp32, any strides
@@ -121,6 +122,40 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
                            float* partial,
                            int num_splits, void* workspace, int64_t workspace_bytes,
                            int quantize_q, void* stream);
+
+/*
+ * INT8 paged decode attention for callers that must not allocate device memory.  No counterpart in the
+ * reference: there every call allocates its split-KV buffers with torch.empty.
+ *
+ * Who needs it: a serving engine that has already handed every free byte of HBM to its KV-cache pool (a late
+ * cudaMalloc can fail, or fragment the pool), and request loops that may not call cudaMalloc at all because it
+ * synchronises the whole device at an unpredictable moment.  Such a caller passes only inputs and the output;
+ * the split-KV partial rows go to a buffer that is part of the library image itself: INT8KV_STATIC_WS_BYTES
+ * bytes of device memory, held by every GPU that loads the library until the process exits.
+ *
+ * Limits and rules:
+ *   - the call is rejected with INT8KV_E_WORKSPACE, before anything is launched, when the split-KV rows of this
+ *     shape (int8kv_workspace_bytes) do not fit in INT8KV_STATIC_WS_BYTES; pass a smaller num_splits (1 needs
+ *     almost nothing) or use int8kv_paged_attn_int8 with a workspace of your own;
+ *   - the first call on each device looks up the device address of the buffer (with that device current);
+ *     make that first call outside any stream capture;
+ *   - all calls on a device share the one buffer, which keeps whatever the previous call left in it.  Nothing in
+ *     it has to start at zero (every row is written before it is read), but two calls of one process whose
+ *     kernels overlap on the GPU (different streams or host threads) race on it: serialise them;
+ *   - it never calls cudaMalloc, cudaFree or any allocating library routine.
+ * Arguments and result are those of int8kv_paged_attn_int8 without the workspace pair.
+ */
+#define INT8KV_STATIC_WS_BYTES (8 * 1024 * 1024)
+int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64_t q_strides[3],
+                           int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                           const int8_t* key_cache, const int8_t* value_cache,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                           const float* k_scale, const float* v_scale,
+                           void* out, int out_dtype, const int64_t out_strides[3],
+                           int num_splits, int quantize_q, void* stream);
 
 /*
  * Merge `num_parts` partial results.  Replaces _merge_split_kv_kernel (reference

@@ -21,6 +21,7 @@ ABI_VERSION = 1
 OK = 0
 E_NULLPTR, E_BAD_SHAPE, E_BAD_DTYPE, E_UNSUPPORTED, E_LAUNCH, E_WORKSPACE = -1, -2, -3, -4, -5, -6
 DEV_WAIT_TIMEOUT = 1
+STATIC_WS_BYTES = 8 * 1024 * 1024
 
 BF16, FP16, FP32 = 0, 1, 2
 
@@ -57,6 +58,12 @@ _SIGNATURES = {
         [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP,
          C.c_int, _VP, C.c_int64, C.c_int, _VP],
+    ),
+    "int8kv_paged_attn_int8_static_ws": (
+        C.c_int,
+        [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
+         C.c_int, C.c_int, _VP],
     ),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),
 }

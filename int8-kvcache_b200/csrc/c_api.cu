@@ -326,4 +326,66 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant: the split-KV workspace is a buffer inside the library image.
+// ---------------------------------------------------------------------------------------------------------
+}  // extern "C"
+
+// The workspace itself, at file scope.  In host code this name is only a handle for the runtime: it is NOT a
+// device address and must never be handed to a kernel; the address the kernels use comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_ws[INT8KV_STATIC_WS_BYTES];
+
+namespace {
+
+// Device address of g_static_ws on each device, looked up on the first call made with that device current.
+std::atomic<void*> g_static_ws_addr[kMaxDevices];
+
+int static_ws_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return INT8KV_E_LAUNCH;
+  void* p = g_static_ws_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_static_ws) != cudaSuccess || p == nullptr) return INT8KV_E_LAUNCH;
+    g_static_ws_addr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return INT8KV_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64_t q_strides[3], int batch,
+                                     int num_q_heads, int num_kv_heads, int head_dim, const int8_t* key_cache,
+                                     const int8_t* value_cache, const int64_t key_cache_strides[4],
+                                     const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                                     const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                                     int64_t bt_width, const void* seq_lens, int sl_is_i64,
+                                     int64_t max_seq_len_hint, const float* k_scale, const float* v_scale,
+                                     void* out, int out_dtype, const int64_t out_strides[3], int num_splits,
+                                     int quantize_q, void* stream) {
+  if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || block_size <= 0 || bt_width < 0 ||
+      num_splits < 0 || num_splits > kMaxSplits)
+    return INT8KV_E_BAD_SHAPE;
+  // Size check first, with the same split count the launch would use, so that an oversized request is refused
+  // before any CUDA call is made.
+  int64_t max_seq = max_seq_len_hint > 0 ? max_seq_len_hint : bt_width * block_size;
+  if (max_seq > bt_width * block_size) max_seq = bt_width * block_size;
+  int splits = num_splits > 0 ? num_splits : choose_splits(batch, num_kv_heads, max_seq, block_size, device_sm_count());
+  const int64_t tiles = (max_seq + 15) / 16;
+  if (splits > tiles) splits = tiles > 0 ? static_cast<int>(tiles) : 1;
+  if (ws_bytes(batch, num_q_heads, head_dim, splits) > INT8KV_STATIC_WS_BYTES) return INT8KV_E_WORKSPACE;
+  void* ws = nullptr;
+  const int rc = static_ws_address(&ws);
+  if (rc != INT8KV_OK) return rc;
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             k_scale, v_scale, out, out_dtype, out_strides, nullptr,
+             splits, ws, INT8KV_STATIC_WS_BYTES, quantize_q, static_cast<cudaStream_t>(stream)};
+  return run_attention(a);
+}
+
 }  // extern "C"
