@@ -15,19 +15,35 @@
 namespace int8kv {
 
 // rint(x / scale) clamped to [-127, 127], bit-identical to IEEE division followed by round-half-even, at
-// the cost of one multiply in the common case.  x * (1/scale) is within 2 ulp of the true quotient; its
-// rounding to an integer can only differ from that of the correctly rounded quotient when the quotient is
-// within a few ulp of a tie k + 0.5 (ulp <= 2^-17 below 128), so exactly those elements — and anything
-// huge, infinite or NaN — take the real division.
+// the cost of a few full-rate FP32 instructions in the common case:
+//  * x * (1/scale) is within 2 ulp of the true quotient; its rounding to an integer can differ from that of
+//    the correctly rounded quotient only when the quotient is within a few ulp of a tie k + 0.5 (ulp <= 2^-17
+//    below 128), so exactly those elements — and anything huge, infinite or NaN — take the real division;
+//  * rounding uses the 1.5 * 2^23 trick (adding and subtracting it rounds to nearest-even in the FP32 adder,
+//    and the integer sits in the low mantissa bits), which keeps the work off the quarter-rate conversion unit.
+// Returns the integer still unclamped for |n| < 2^22; the caller saturates when packing.
+constexpr float kRoundMagic = 12582912.f;           // 1.5 * 2^23
+constexpr int kRoundMagicBits = 0x4B400000;
+
 __device__ __forceinline__ int quant1(float x, float scale, float rscale) {
   float q = x * rscale;
-  float n = rintf(q);
-  if (!(fabsf(q - n) < 0.5f - 6.2e-5f)) {
-    q = x / scale;  // div.rn.f32
-    n = rintf(q);
+  float t = q + kRoundMagic;
+  const float n = t - kRoundMagic;
+  if (!(fabsf(q - n) < 0.5f - 6.2e-5f) || !(fabsf(q) < 4.0e6f)) {  // near a tie, beyond 2^22, infinite or NaN
+    q = x / scale;                          // div.rn.f32
+    q = fminf(fmaxf(q, -127.f), 127.f);     // also maps +-inf; NaN is handled below
+    t = q + kRoundMagic;
+    if (x != x) t = kRoundMagic;            // NaN -> 0, as a float-to-int8 cast of NaN gives on the CPU
   }
-  n = fminf(fmaxf(n, -127.f), 127.f);
-  return (x != x) ? 0 : static_cast<int>(n);
+  return __float_as_int(t) - kRoundMagicBits;
+}
+
+// Four such integers saturated to int8 and packed little-endian; -128 is raised to -127.
+__device__ __forceinline__ uint32_t pack4_sat(int n0, int n1, int n2, int n3) {
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(n3), "r"(n2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(n1), "r"(n0), "r"(hi));
+  return __vmaxs4(w, 0x81818181u);
 }
 
 template <typename T>
@@ -36,7 +52,7 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 
-// 16 consecutive elements as raw 16-byte vectors (issued before anything depends on them) ...
+// Sixteen consecutive elements as raw 16-byte vectors (requested before anything depends on them) ...
 template <typename T>
 struct Raw16 {
   static constexpr int kVecs = 16 * sizeof(T) / 16;
@@ -45,59 +61,46 @@ struct Raw16 {
 #pragma unroll
     for (int i = 0; i < kVecs; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
   }
-  // ... and their float values
-  __device__ __forceinline__ void to_float(float (&x)[16]) const {
+  // ... and their quantised bytes
+  __device__ __forceinline__ uint4 quantise(float scale, float rscale) const {
     const T* e = reinterpret_cast<const T*>(v);
+    uint32_t w[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) x[i] = to_f32<T>(e[i]);
+    for (int i = 0; i < 4; ++i)
+      w[i] = pack4_sat(quant1(to_f32<T>(e[4 * i]), scale, rscale), quant1(to_f32<T>(e[4 * i + 1]), scale, rscale),
+                       quant1(to_f32<T>(e[4 * i + 2]), scale, rscale), quant1(to_f32<T>(e[4 * i + 3]), scale, rscale));
+    return make_uint4(w[0], w[1], w[2], w[3]);
   }
 };
 
-__device__ __forceinline__ uint4 quant16(const float (&x)[16], float scale, float rscale) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t b0 = static_cast<uint32_t>(quant1(x[4 * i + 0], scale, rscale)) & 0xffu;
-    uint32_t b1 = static_cast<uint32_t>(quant1(x[4 * i + 1], scale, rscale)) & 0xffu;
-    uint32_t b2 = static_cast<uint32_t>(quant1(x[4 * i + 2], scale, rscale)) & 0xffu;
-    uint32_t b3 = static_cast<uint32_t>(quant1(x[4 * i + 3], scale, rscale)) & 0xffu;
-    w[i] = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
-// Vector path: D % 16 == 0, unit innermost strides, 16-byte aligned rows on both sides.
+// Vector path: D % 16 == 0, unit innermost strides, 16-byte aligned rows on both sides.  One thread per 16
+// elements of one (token, head) row of K and of V; index arithmetic in 32 bits (the launcher guarantees the
+// unit count fits) and by shift where the block size is a power of two.
 template <typename T>
-__global__ void __launch_bounds__(256) cache_write_vec_kernel(const WriteParams p) {
-  const int chunks = p.D >> 4;
-  const int64_t per_token = static_cast<int64_t>(p.Hkv) * chunks;
-  const int64_t total = p.T * per_token;
-  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t t = idx / per_token;
-    const int rem = static_cast<int>(idx - t * per_token);
-    const int h = rem / chunks;
-    const int c = rem - h * chunks;
-    // the slot and the K/V vectors are independent loads: all are in flight before the first use
-    const int64_t slot = load_index(p.slots, p.slot_is_i64, t);
-    const T* kp = reinterpret_cast<const T*>(p.key) + t * p.k_st[0] + h * p.k_st[1] + c * 16;
-    const T* vp = reinterpret_cast<const T*>(p.value) + t * p.v_st[0] + h * p.v_st[1] + c * 16;
-    Raw16<T> kr, vr;
-    kr.load(kp);
-    vr.load(vp);
-    const float ks = fmaxf(__ldg(p.k_scale + h), 1e-6f);
-    const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
-    if (slot < 0 || slot >= p.num_slots) continue;
-    float kx[16], vx[16];
-    kr.to_float(kx);
-    vr.to_float(vx);
-    const int64_t blk = slot / p.block_size;
-    const int64_t off = slot - blk * p.block_size;
-    int8_t* kd = p.kc + blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + c * 16;
-    int8_t* vd = p.vc + blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + c * 16;
-    *reinterpret_cast<uint4*>(kd) = quant16(kx, ks, __frcp_rn(ks));
-    *reinterpret_cast<uint4*>(vd) = quant16(vx, vs, __frcp_rn(vs));
-  }
+__global__ void __launch_bounds__(256) cache_write_vec_kernel(const WriteParams p, const uint32_t total,
+                                                              const int bs_shift) {
+  const uint32_t chunks = static_cast<uint32_t>(p.D) >> 4;
+  const uint32_t per_token = static_cast<uint32_t>(p.Hkv) * chunks;
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const uint32_t t = idx / per_token;
+  const uint32_t rem = idx - t * per_token;
+  const uint32_t h = rem / chunks;
+  const uint32_t c = rem - h * chunks;
+  // the slot and the K/V vectors are independent loads: all are in flight before the first use
+  const int64_t slot = load_index(p.slots, p.slot_is_i64, t);
+  Raw16<T> kr, vr;
+  kr.load(reinterpret_cast<const T*>(p.key) + static_cast<int64_t>(t) * p.k_st[0] + h * p.k_st[1] + c * 16);
+  vr.load(reinterpret_cast<const T*>(p.value) + static_cast<int64_t>(t) * p.v_st[0] + h * p.v_st[1] + c * 16);
+  const float ks = fmaxf(__ldg(p.k_scale + h), 1e-6f);
+  const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
+  if (slot < 0 || slot >= p.num_slots) return;
+  const int64_t blk = bs_shift >= 0 ? (slot >> bs_shift) : slot / p.block_size;
+  const int64_t off = slot - blk * p.block_size;
+  int8_t* kd = p.kc + blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + c * 16;
+  int8_t* vd = p.vc + blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + c * 16;
+  *reinterpret_cast<uint4*>(kd) = kr.quantise(ks, __frcp_rn(ks));
+  *reinterpret_cast<uint4*>(vd) = vr.quantise(vs, __frcp_rn(vs));
 }
 
 // Element path: any D, any strides, any alignment.
@@ -118,8 +121,8 @@ __global__ void __launch_bounds__(256) cache_write_elem_kernel(const WriteParams
     const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
     const int64_t blk = slot / p.block_size;
     const int64_t off = slot - blk * p.block_size;
-    p.kc[blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + d * p.kc_st[3]] = static_cast<int8_t>(quant1(kx, ks, __frcp_rn(ks)));
-    p.vc[blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + d * p.vc_st[3]] = static_cast<int8_t>(quant1(vx, vs, __frcp_rn(vs)));
+    p.kc[blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + d * p.kc_st[3]] = static_cast<int8_t>(max(-127, min(127, quant1(kx, ks, __frcp_rn(ks)))));
+    p.vc[blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + d * p.vc_st[3]] = static_cast<int8_t>(max(-127, min(127, quant1(vx, vs, __frcp_rn(vs)))));
   }
 }
 
@@ -129,21 +132,28 @@ int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream) 
   if (p.T == 0) return INT8KV_OK;
   const int esz = dtype_bytes(p.in_dtype);
   const int per16 = 16 / esz;  // elements per 16 bytes
+  const int64_t units = p.T * p.Hkv * (p.D / 16);
   bool vec = (p.D % 16 == 0) && p.k_st[2] == 1 && p.v_st[2] == 1 && p.kc_st[3] == 1 && p.vc_st[3] == 1 &&
-             aligned16(p.key) && aligned16(p.value) && aligned16(p.kc) && aligned16(p.vc);
+             aligned16(p.key) && aligned16(p.value) && aligned16(p.kc) && aligned16(p.vc) &&
+             units < (int64_t(1) << 31) && p.T < (int64_t(1) << 31);
   for (int i = 0; i < 2 && vec; ++i) vec = (p.k_st[i] % per16 == 0) && (p.v_st[i] % per16 == 0);
   for (int i = 0; i < 3 && vec; ++i) vec = (p.kc_st[i] % 16 == 0) && (p.vc_st[i] % 16 == 0);
   const int threads = 256;
-  const int64_t work = vec ? p.T * p.Hkv * (p.D / 16) : p.T * p.Hkv * static_cast<int64_t>(p.D);
-  int64_t blocks = (work + threads - 1) / threads;
-  const int64_t cap = static_cast<int64_t>(sm_count) * 32;  // grid-stride beyond 32 CTAs per SM
-  if (blocks > cap) blocks = cap;
   if (vec) {
-    if (p.in_dtype == INT8KV_BF16) cache_write_vec_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(p);
-    else if (p.in_dtype == INT8KV_FP16) cache_write_vec_kernel<__half><<<blocks, threads, 0, stream>>>(p);
-    else cache_write_vec_kernel<float><<<blocks, threads, 0, stream>>>(p);
+    int bs_shift = -1;
+    if ((p.block_size & (p.block_size - 1)) == 0)
+      for (bs_shift = 0; (1 << bs_shift) < p.block_size; ++bs_shift) {}
+    const unsigned blocks = static_cast<unsigned>((units + threads - 1) / threads);
+    const uint32_t total = static_cast<uint32_t>(units);
+    if (p.in_dtype == INT8KV_BF16) cache_write_vec_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
+    else if (p.in_dtype == INT8KV_FP16) cache_write_vec_kernel<__half><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
+    else cache_write_vec_kernel<float><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
   } else {
-    cache_write_elem_kernel<<<blocks, threads, 0, stream>>>(p);
+    const int64_t work = p.T * p.Hkv * static_cast<int64_t>(p.D);
+    int64_t blocks = (work + threads - 1) / threads;
+    const int64_t cap = static_cast<int64_t>(sm_count) * 32;  // grid-stride beyond 32 CTAs per SM
+    if (blocks > cap) blocks = cap;
+    cache_write_elem_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
