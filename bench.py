@@ -237,6 +237,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
+    ap.add_argument("--no-bf16", dest="bf16_baseline", action="store_false", help="skip the same-run BF16 baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
     ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
@@ -339,60 +340,136 @@ def main():
         barrier()
         dev_ms = e0.elapsed_time(e1)
 
-        # ---- e2e: Python operators, pinned host inputs in, result out, every step -------------------
+        # ---- same-run BF16 baseline on identical block tables (one step = the same 28 calls) --------------
+        bf16_ms = float("nan")
+        if args.bf16_baseline:
+            shape = wl.LayerShape(hq, hkv, 128, 16)
+            gen = torch.Generator(device=device)
+            for li, L in enumerate(layers_data):
+                L.kb = torch.zeros(L.kc.shape, dtype=torch.bfloat16, device=device)
+                L.vb = torch.zeros_like(L.kb)
+                gen.manual_seed(9000 + li)
+                gain = wl.channel_gain(shape, 100 + rank, device)
+                for b in range(B):
+                    T = seq_lens[b]
+                    k, v = wl.draw_kv(T, shape, gen, gain)
+                    tok = torch.arange(T, device=device)
+                    slots = L.block_tables[b, tok // 16].long() * 16 + tok % 16
+                    L.kb.view(-1, hkv, 128)[slots] = k
+                    L.vb.view(-1, hkv, 128)[slots] = v
+
+            def bf16_step():
+                for L in layers_data:
+                    kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens,
+                                            max_seq_len=max_seq, out=L.out)
+
+            for _ in range(2):
+                bf16_step()
+            stream.synchronize()
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=stream):
+                bf16_step()
+            for _ in range(args.warmup):
+                g2.replay()
+            barrier()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record(stream)
+            for _ in range(args.steps):
+                g2.replay()
+            b1.record(stream)
+            barrier()
+            bf16_ms = b0.elapsed_time(b1) / args.steps
+            for L in layers_data:
+                del L.kb, L.vb
+
+        # ---- e2e: the decode step a serving engine runs, from host buffers to host buffers ---------------
+        # Inputs of one step (every layer's new query / key / value rows, the block tables, sequence lengths and
+        # write slots) sit in ONE pinned host buffer; a step copies it to the device, runs cache write +
+        # attention for every layer through the Python operators, and copies every layer's output back to a
+        # pinned host buffer.  Measured twice: launched eagerly from Python, and with the same calls captured
+        # once into a CUDA graph (how decode loops are run in production) and replayed per step.
         shape = wl.LayerShape(hq, hkv, 128, 16)
         g = torch.Generator().manual_seed(7)
-        host_q = [wl.draw_query(B, shape, g).pin_memory() for _ in range(layers)]
-        host_kv = [tuple(t.pin_memory() for t in wl.draw_kv(B, shape, g, wl.channel_gain(shape, 0))) for _ in range(layers)]
-        host_out = [torch.empty(B, hq, 128, dtype=torch.bfloat16).pin_memory() for _ in range(layers)]
-        last_slots, host_bt, host_sl = [], [], []
-        for L in layers_data:
-            last = torch.tensor([s - 1 for s in seq_lens], device=device)
-            slots = L.block_tables[torch.arange(B, device=device), last // 16].long() * 16 + last % 16
-            last_slots.append(slots.cpu().pin_memory())
-            host_bt.append(L.block_tables.cpu().pin_memory())
-            host_sl.append(L.seq_lens.cpu().pin_memory())
-        d_q = torch.empty(B, hq, 128, dtype=torch.bfloat16, device=device)
-        d_k = torch.empty(B, hkv, 128, dtype=torch.bfloat16, device=device)
-        d_v = torch.empty_like(d_k)
-        d_slots = torch.empty(B, dtype=torch.int64, device=device)
-        d_bt = torch.empty_like(layers_data[0].block_tables)
-        d_sl = torch.empty(B, dtype=torch.int32, device=device)
-        d_out = torch.empty(B, hq, 128, dtype=torch.bfloat16, device=device)
-        h2d = layers * (host_q[0].numel() * 2 + 2 * host_kv[0][0].numel() * 2 + last_slots[0].numel() * 8
-                        + host_bt[0].numel() * 4 + host_sl[0].numel() * 4)
-        d2h = layers * host_out[0].numel() * 2
+        n_q, n_kv = B * hq * 128, B * hkv * 128
+        width = layers_data[0].block_tables.shape[1]
+        per_layer = (n_q + 2 * n_kv) * 2
+        meta_bytes = B * width * 4 + B * 4 + B * 8
+        meta_bytes = (meta_bytes + 15) // 16 * 16
+        h_in = torch.empty(layers * per_layer + meta_bytes, dtype=torch.uint8).pin_memory()
+        d_in = torch.empty_like(h_in, device=device)
+        h_out = torch.empty(layers, B, hq, 128, dtype=torch.bfloat16).pin_memory()
+        d_out = torch.empty(layers, B, hq, 128, dtype=torch.bfloat16, device=device)
 
-        def e2e_step():
+        def views(buf):
+            per = []
+            for i in range(layers):
+                base = buf[i * per_layer:(i + 1) * per_layer].view(torch.bfloat16)
+                per.append((base[:n_q].view(B, hq, 128), base[n_q:n_q + n_kv].view(B, hkv, 128),
+                            base[n_q + n_kv:].view(B, hkv, 128)))
+            m = buf[layers * per_layer:]
+            bt = m[:B * width * 4].view(torch.int32).view(B, width)
+            sl = m[B * width * 4:B * width * 4 + B * 4].view(torch.int32)
+            so = B * width * 4 + B * 4
+            so = (so + 7) // 8 * 8
+            slots = m[so:so + B * 8].view(torch.int64)
+            return per, bt, sl, slots
+
+        hv, h_bt, h_sl, h_slots = views(h_in)
+        for i in range(layers):
+            hv[i][0].copy_(wl.draw_query(B, shape, g))
+            k, v = wl.draw_kv(B, shape, g, wl.channel_gain(shape, 0))
+            hv[i][1].copy_(k)
+            hv[i][2].copy_(v)
+        # all layers share the step's metadata, as in a serving engine (layer 0's tables are used for every layer)
+        L0 = layers_data[0]
+        h_bt.copy_(L0.block_tables.cpu())
+        h_sl.copy_(L0.seq_lens.cpu())
+        last = torch.tensor([s - 1 for s in seq_lens])
+        h_slots.copy_(L0.block_tables.cpu()[torch.arange(B), last // 16].long() * 16 + last % 16)
+        dv, d_bt, d_sl, d_slots = views(d_in)
+        h2d, d2h = h_in.numel(), h_out.numel() * 2
+
+        def e2e_enqueue():
+            d_in.copy_(h_in, non_blocking=True)
             for i, L in enumerate(layers_data):
-                d_q.copy_(host_q[i], non_blocking=True)
-                d_k.copy_(host_kv[i][0], non_blocking=True)
-                d_v.copy_(host_kv[i][1], non_blocking=True)
-                d_slots.copy_(last_slots[i], non_blocking=True)
-                d_bt.copy_(host_bt[i], non_blocking=True)
-                d_sl.copy_(host_sl[i], non_blocking=True)
-                kv.int8_kv_cache_write(d_k, d_v, L.kc, L.vc, d_slots, L.k_scale, L.v_scale)
-                kv.int8_paged_attention(d_q, L.kc, L.vc, d_bt, d_sl, L.k_scale, L.v_scale,
-                                        num_splits=args.num_splits, max_seq_len=max_seq, out=d_out)
-                host_out[i].copy_(d_out, non_blocking=True)
-            stream.synchronize()
+                q, k, v = dv[i]
+                kv.int8_kv_cache_write(k, v, L.kc, L.vc, d_slots, L.k_scale, L.v_scale)
+                kv.int8_paged_attention(q, L.kc, L.vc, d_bt, d_sl, L.k_scale, L.v_scale,
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i])
+            h_out.copy_(d_out, non_blocking=True)
 
-        e2e_s = float("nan")
-        if not args.no_e2e:
+        def time_steps(step):
             for _ in range(args.warmup):
-                e2e_step()
+                step()
             barrier()
             t0 = time.perf_counter()
             for _ in range(args.steps):
-                e2e_step()
+                step()
             barrier()
-            e2e_s = time.perf_counter() - t0
+            return time.perf_counter() - t0
+
+        e2e_s = e2e_eager_s = float("nan")
+        if not args.no_e2e:
+            def eager_step():
+                e2e_enqueue()
+                stream.synchronize()
+
+            e2e_eager_s = time_steps(eager_step)
+            g3 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g3, stream=stream):
+                e2e_enqueue()
+
+            def graph_step():
+                g3.replay()
+                stream.synchronize()
+
+            e2e_s = time_steps(graph_step)
         clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    times = torch.tensor([dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = [float(x) for x in times.tolist()]
+    dev_ms, e2e_ms, e2e_eager_ms, bf16_ms = [float(x) for x in times.tolist()]
     status = kv.device_status(device)
 
     if rank == 0:
@@ -420,8 +497,15 @@ def main():
             "device_status": status,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
-                    "what": "pinned-host q/k/v/slots/tables/seq_lens -> device, cache write + attention through the "
-                            "Python operators, output -> pinned host, per layer, synchronised per step"},
+                    "eager_ms_per_step": e2e_eager_ms / args.steps,
+                    "eager_value": world * nbytes_step / (e2e_eager_ms / args.steps * 1e-3) / 1e9,
+                    "what": "per step: one pinned-host buffer (all layers' new q/k/v rows, block tables, seq_lens, "
+                            "slots) -> device, cache write + attention per layer through the Python operators, all "
+                            "outputs -> pinned host, stream synchronised; `value` replays those calls as one CUDA "
+                            "graph, `eager_value` launches them from Python every step"},
+            "bf16_baseline": {"us_per_call": bf16_ms * 1e3 / layers, "int8_speedup": bf16_ms / ms_per_step,
+                              "what": "bf16_paged_attention on un-quantised caches, same block tables, same graph "
+                                      "replay timing"} if args.bf16_baseline else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src,
                          "kernel": "paged_attn_int8_kernel (+ merge_partials_kernel when split), per call inside the graph",

@@ -146,7 +146,7 @@ __device__ __forceinline__ int guessed_first_block(const AttnParams& p, int c) {
   return (c * per) / p.tiles_per_block;
 }
 
-// The tile range of the item: reads seq_lens[b]; every sequence splits its own tiles evenly.
+// The tile range of the item: reads seq_lens[b]; every sequence splits its own tiles evenly over the parts it uses.
 __device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   int64_t sl = load_index(p.sl, p.sl_is_i64, it.b);
   const int64_t cap = p.bt_width * p.block_size;
@@ -154,9 +154,14 @@ __device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   if (sl < 0) sl = 0;
   it.seq_len = static_cast<int>(sl);
   const int ntiles = (it.seq_len + kTile - 1) / kTile;
-  const int per = (ntiles + p.num_splits - 1) / p.num_splits;
+  // A sequence uses as many of the num_splits parts as it takes to give each about the tile count that the
+  // longest sequence's parts have, and leaves the rest empty: in a ragged batch every working warp then has
+  // a similar amount to read, and short sequences write few partial rows.
+  const int per_longest = max(1, (p.hint_tiles + p.num_splits - 1) / p.num_splits);
+  const int used = min(p.num_splits, max(1, (ntiles + per_longest - 1) / per_longest));
+  const int per = (ntiles + used - 1) / used;
   it.t0 = it.c * per;
-  it.t1 = min(it.t0 + per, ntiles);
+  it.t1 = it.c < used ? min(it.t0 + per, ntiles) : it.t0;
 }
 
 // Result of an empty tile range: zeros to `out` (direct mode) or lse = -inf (partial mode).

@@ -1,0 +1,92 @@
+"""Sequence-parallel INT8 attention on two GPUs: every rank holds a contiguous block range of every sequence
+in its own cache, computes partial rows, NCCL all-gathers them into local memory and merges locally.  The
+result must equal single-GPU attention over the whole sequence.  Skipped when fewer than two GPUs are visible.
+Also checks the collective-free KV-head x batch sharding on each rank against the oracle."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from conftest import cosine, max_abs, package
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        kv, sh, wl = package(), package("sharding"), package("workloads")
+        lens = [2000, 333, 64, 1]
+        case = wl.make_decode_case(lens, wl.QWEN25_7B, seed=77)
+        kc = torch.zeros(case.num_blocks, 16, 4, 128, dtype=torch.int8)
+        vc = torch.zeros_like(kc)
+        oracle.cache_write(case.key, case.value, kc, vc, case.slot_mapping, case.k_scale, case.v_scale)
+        want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+
+        # --- sequence split: this rank's local cache holds only its block range, with local block ids
+        lo, hi, local_lens = sh.sequence_split(lens, rank, world, 16)
+        width = case.block_tables.shape[1]
+        hi = min(hi, width)
+        local_tables = torch.zeros(len(lens), max(hi - lo, 1), dtype=torch.int32)
+        local_kc = torch.zeros(len(lens) * max(hi - lo, 1) + 1, 16, 4, 128, dtype=torch.int8)
+        local_vc = torch.zeros_like(local_kc)
+        nxt = 1
+        for b, n in enumerate(local_lens):
+            for j in range((n + 15) // 16):
+                src = int(case.block_tables[b, lo + j])
+                local_kc[nxt], local_vc[nxt] = kc[src], vc[src]
+                local_tables[b, j] = nxt
+                nxt += 1
+        out = sh.sequence_parallel_int8_attention(
+            case.query.to(dev), local_kc.to(dev), local_vc.to(dev), local_tables.to(dev),
+            torch.tensor(local_lens, dtype=torch.int32, device=dev), case.k_scale.to(dev), case.v_scale.to(dev))
+        torch.cuda.synchronize()
+        got = out.float().cpu()
+        seq_err, seq_cos = max_abs(got, want.to(torch.bfloat16).float()), cosine(got, want)
+
+        # --- head x batch shard of this rank, no collective
+        shard = sh.head_batch_partition(world, 28, 4, len(lens))[rank]
+        args = sh.shard_decode_inputs(shard, case.query.to(dev), kc.to(dev), vc.to(dev), case.block_tables.to(dev),
+                                      case.seq_lens.to(dev), case.k_scale.to(dev), case.v_scale.to(dev))
+        part = kv.int8_paged_attention(*args).float().cpu()
+        q0, q1 = shard.q_heads
+        b0, b1 = shard.batch
+        ref = want[b0:b1, q0:q1]
+        ret[rank] = (seq_err, seq_cos, max_abs(part, ref.to(torch.bfloat16).float()), cosine(part, ref),
+                     int(kv.device_status(dev)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_sequence_split_and_head_shards_match_the_oracle():
+    world = 2
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(240)
+            assert p.exitcode == 0
+        assert len(ret) == world
+        for seq_err, seq_cos, shard_err, shard_cos, status in ret.values():
+            assert seq_err <= 2e-2 and seq_cos >= 0.9999
+            assert shard_err <= 2e-2 and shard_cos >= 0.9999
+            assert status == 0
