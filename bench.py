@@ -35,6 +35,9 @@ REPO = Path(__file__).resolve().parent
 if str(REPO) not in sys.path:
     sys.path.insert(0, str(REPO))
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch, from the one-pass ncu capture
+# summarised in profiles/bench_default__launch_list.md (default workload only)
+NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33691648}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
@@ -47,6 +50,8 @@ def workload_spec(name: str):
     gen = torch.Generator().manual_seed(1234)
     if name == "c2":
         return dict(hq=28, hkv=4), [4096] * 8, 28, "sweep cell B=8 seq=4096, 28 distinct layer caches"
+    if name == "c3":  # cache-write workload; handled by bench_cache_write
+        return dict(hq=28, hkv=4), [2048] * 8, 1, "prefill cache write, 8 x 2048 tokens"
     if name == "c4":
         lens = torch.randint(1024, 8193, (256,), generator=gen).tolist()
         return dict(hq=28, hkv=4), lens, 4, "B=256 seq~U[1024,8192], 4 distinct layer caches"
@@ -226,13 +231,64 @@ def time_cpu(wl, hq, hkv, seq_lens, budget_s, min_reps=3, warm=1):
 
 
 # ---------------------------------------------------------------------------------------------------
+def bench_cache_write(kv, wl, device, args):
+    """Prefill-style INT8 cache write (BASELINE config 3): 8 x 2048 tokens, ~3% padding slots, rotated over
+    8 distinct input/cache sets (400 MB, larger than L2); one step = 8 writes replayed as a CUDA graph."""
+    sets = []
+    for i in range(8):
+        key, value, slots, ks, vs, nb = wl.prefill_write_case(8, 2048, seed=i, device=device)
+        kc = torch.zeros(nb, 16, 4, 128, dtype=torch.int8, device=device)
+        sets.append((key, value, slots, ks, vs, kc, torch.zeros_like(kc)))
+    valid = sum(int((s[2] >= 0).sum()) for s in sets) / len(sets)
+    nbytes = 16384 * 4 * 128 * 4 + valid * 4 * 128 * 2 + 8 * 16384 + 32
+
+    def step():
+        for key, value, slots, ks, vs, kc, vc in sets:
+            kv.int8_kv_cache_write(key, value, kc, vc, slots, ks, vs)
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        if args.no_graph:
+            replay = step
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            replay = graph.replay
+        for _ in range(max(args.warmup, 3)):
+            replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            replay()
+        e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps / len(sets)
+    peaks_path = REPO / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else FALLBACK_PEAK_GBS
+    gbs = nbytes / us / 1e3
+    print(json.dumps({
+        "metric": "int8_kv_cache_write_achieved_hbm_gbps", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us * len(sets) / 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 -> int8 (fp32 quotient)",
+        "data": "synthetic", "us_per_call": us, "gpu_launches": len(sets) * args.steps,
+        "config": {"workload": "c3: prefill cache write, 16384 tokens x 4 heads x 128, permuted 1024-block pool, "
+                               "~3% slots = -1, 8 rotated sets (larger than L2)"},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                     "traffic": None, "kernel": "cache_write_vec_kernel<bf16>", "algorithmic_bytes_per_call": nbytes},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--num-splits", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -284,6 +340,8 @@ def main():
     kv = importlib.import_module("int8-kvcache_b200")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.workload == "c3":
+        return bench_cache_write(kv, wl, device, args)
     if world > 1:
         import torch.distributed as dist
 
@@ -507,7 +565,8 @@ def main():
                               "what": "bf16_paged_attention on un-quantised caches, same block tables, same graph "
                                       "replay timing"} if args.bf16_baseline else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src,
+                         "traffic": NCU_DRAM_TRAFFIC_PER_LAUNCH.get(args.workload) if not (args.batch or args.layers) else None,
+                         "peak_source": peak_src,
                          "kernel": "paged_attn_int8_kernel (+ merge_partials_kernel when split), per call inside the graph",
                          "algorithmic_bytes_per_call": nbytes_call},
         }
