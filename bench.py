@@ -491,9 +491,8 @@ def main():
             d_in.copy_(h_in, non_blocking=True)
             for i, L in enumerate(layers_data):
                 q, k, v = dv[i]
-                kv.int8_kv_cache_write(k, v, L.kc, L.vc, d_slots, L.k_scale, L.v_scale)
-                kv.int8_paged_attention(q, L.kc, L.vc, d_bt, d_sl, L.k_scale, L.v_scale,
-                                        num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i])
+                kv.int8_decode_step(q, k, v, L.kc, L.vc, d_slots, d_bt, d_sl, L.k_scale, L.v_scale,
+                                    num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i])
             h_out.copy_(d_out, non_blocking=True)
 
         def time_steps(step):
@@ -558,7 +557,7 @@ def main():
                     "eager_ms_per_step": e2e_eager_ms / args.steps,
                     "eager_value": world * nbytes_step / (e2e_eager_ms / args.steps * 1e-3) / 1e9,
                     "what": "per step: one pinned-host buffer (all layers' new q/k/v rows, block tables, seq_lens, "
-                            "slots) -> device, cache write + attention per layer through the Python operators, all "
+                            "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python operators, all "
                             "outputs -> pinned host, stream synchronised; `value` replays those calls as one CUDA "
                             "graph, `eager_value` launches them from Python every step"},
             "bf16_baseline": {"us_per_call": bf16_ms * 1e3 / layers, "int8_speedup": bf16_ms / ms_per_step,

@@ -124,6 +124,44 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
                            int quantize_q, void* stream);
 
 /*
+ * Dynamic per-(token, head) INT8 cache write.  Replaces reshape_and_cache_int8 and its Triton kernel (reference
+ * vllm_int8/vllm_int8_cache_ops.py:13-210), the reference's alternative quantisation scheme: for every token and
+ * KV head, scale = max(absmax / 127, 1e-6) over the D elements, q = clamp(x / scale, +-127) rounded half away from
+ * zero; the INT8 row goes to cache[slot / BS, slot % BS, head, :] and the fp32 scale to scale_cache[slot / BS,
+ * slot % BS, head] ([num_blocks, BS, Hkv], strides in elements).  slot < 0 skips the token.
+ */
+int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype,
+                               int64_t num_tokens, int num_kv_heads, int head_dim,
+                               const int64_t key_strides[3], const int64_t value_strides[3],
+                               int8_t* key_cache, int8_t* value_cache,
+                               const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                               float* k_scale_cache, float* v_scale_cache,
+                               const int64_t k_scale_strides[3], const int64_t v_scale_strides[3],
+                               int64_t num_blocks, int block_size,
+                               const void* slot_mapping, int slot_is_i64, void* stream);
+
+/*
+ * One decode step of one layer in a single call: int8kv_cache_write of the step's `batch` new K/V rows (one per
+ * sequence, at slot_mapping), then int8kv_paged_attn_int8 over the updated cache, stream-ordered.  This is the pair
+ * of calls that the reference's vLLM hooks make back to back for every layer (do_kv_cache_update then forward,
+ * vllm_int8/vllm_shadow_cache_patch.py:154-166 and vllm_int8/vllm_int8_attention_patch.py:117-137); seq_lens
+ * already count the new token.
+ */
+int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
+                       const int64_t key_strides[3], const int64_t value_strides[3],
+                       const void* slot_mapping, int slot_is_i64,
+                       const void* query, int q_dtype, const int64_t q_strides[3],
+                       int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                       int8_t* key_cache, int8_t* value_cache,
+                       const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                       int64_t num_blocks, int block_size,
+                       const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                       const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                       const float* k_scale, const float* v_scale,
+                       void* out, int out_dtype, const int64_t out_strides[3],
+                       int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * INT8 paged decode attention for callers that must not allocate device memory.  No counterpart in the
  * reference: there every call allocates its split-KV buffers with torch.empty.
  *

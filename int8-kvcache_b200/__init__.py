@@ -16,12 +16,14 @@ from . import _lib  # noqa: F401
 from .ops import (  # noqa: F401
     bf16_paged_attention,
     device_status,
+    int8_decode_step,
     int8_kv_cache_write,
     int8_paged_attention,
     int8_paged_attention_partial,
     merge_partials,
     partial_row_floats,
     release_workspaces,
+    reshape_and_cache_int8,
 )
 
 __all__ = [
@@ -29,6 +31,8 @@ __all__ = [
     "int8_paged_attention",
     "bf16_paged_attention",
     "int8_paged_attention_partial",
+    "int8_decode_step",
+    "reshape_and_cache_int8",
     "merge_partials",
     "partial_row_floats",
     "device_status",

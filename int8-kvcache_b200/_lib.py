@@ -65,6 +65,18 @@ _SIGNATURES = {
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
          C.c_int, C.c_int, _VP],
     ),
+    "int8kv_cache_write_dynamic": (
+        C.c_int,
+        [_VP, _VP, C.c_int, C.c_int64, C.c_int, C.c_int, _I64P, _I64P, _VP, _VP, _I64P, _I64P, _VP, _VP, _I64P, _I64P,
+         C.c_int64, C.c_int, _VP, C.c_int, _VP],
+    ),
+    "int8kv_decode_step": (
+        C.c_int,
+        [_VP, _VP, C.c_int, _I64P, _I64P, _VP, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
+         C.c_int, _VP, C.c_int64, _VP],
+    ),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),
 }
 

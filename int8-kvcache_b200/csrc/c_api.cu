@@ -329,6 +329,57 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 
+int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype, int64_t num_tokens, int num_kv_heads,
+                               int head_dim, const int64_t key_strides[3], const int64_t value_strides[3],
+                               int8_t* key_cache, int8_t* value_cache, const int64_t key_cache_strides[4],
+                               const int64_t value_cache_strides[4], float* k_scale_cache, float* v_scale_cache,
+                               const int64_t k_scale_strides[3], const int64_t v_scale_strides[3], int64_t num_blocks,
+                               int block_size, const void* slot_mapping, int slot_is_i64, void* stream) {
+  if (num_tokens < 0 || num_kv_heads <= 0 || head_dim <= 0 || num_blocks < 0 || block_size <= 0)
+    return INT8KV_E_BAD_SHAPE;
+  if (!valid_float_dtype(in_dtype)) return INT8KV_E_BAD_DTYPE;
+  if (num_tokens == 0) return INT8KV_OK;
+  if (!key || !value || !key_cache || !value_cache || !k_scale_cache || !v_scale_cache || !slot_mapping ||
+      !key_strides || !value_strides || !key_cache_strides || !value_cache_strides || !k_scale_strides ||
+      !v_scale_strides)
+    return INT8KV_E_NULLPTR;
+  DynWriteParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.key = key; p.value = value; p.in_dtype = in_dtype;
+  p.T = num_tokens; p.Hkv = num_kv_heads; p.D = head_dim;
+  for (int i = 0; i < 3; ++i) {
+    p.k_st[i] = key_strides[i]; p.v_st[i] = value_strides[i];
+    p.ks_st[i] = k_scale_strides[i]; p.vs_st[i] = v_scale_strides[i];
+  }
+  p.kc = key_cache; p.vc = value_cache; p.ks = k_scale_cache; p.vs = v_scale_cache;
+  for (int i = 0; i < 4; ++i) { p.kc_st[i] = key_cache_strides[i]; p.vc_st[i] = value_cache_strides[i]; }
+  p.num_slots = num_blocks * block_size;
+  p.block_size = block_size;
+  p.slots = slot_mapping; p.slot_is_i64 = slot_is_i64;
+  return launch_cache_write_dynamic(p, static_cast<cudaStream_t>(stream));
+}
+
+int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const int64_t key_strides[3],
+                       const int64_t value_strides[3], const void* slot_mapping, int slot_is_i64,
+                       const void* query, int q_dtype, const int64_t q_strides[3], int batch, int num_q_heads,
+                       int num_kv_heads, int head_dim, int8_t* key_cache, int8_t* value_cache,
+                       const int64_t key_cache_strides[4], const int64_t value_cache_strides[4], int64_t num_blocks,
+                       int block_size, const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                       int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                       const float* k_scale, const float* v_scale, void* out, int out_dtype,
+                       const int64_t out_strides[3], int num_splits, void* workspace, int64_t workspace_bytes,
+                       void* stream) {
+  const int rc = int8kv_cache_write(key, value, kv_dtype, batch, num_kv_heads, head_dim, key_strides, value_strides,
+                                    key_cache, value_cache, key_cache_strides, value_cache_strides, num_blocks,
+                                    block_size, slot_mapping, slot_is_i64, k_scale, v_scale, stream);
+  if (rc != INT8KV_OK) return rc;
+  return int8kv_paged_attn_int8(query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, key_cache,
+                                value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
+                                block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+                                k_scale, v_scale, out, out_dtype, out_strides, num_splits, workspace, workspace_bytes,
+                                0, stream);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Allocation-free variant: the split-KV workspace is a buffer inside the library image.
 // ---------------------------------------------------------------------------------------------------------

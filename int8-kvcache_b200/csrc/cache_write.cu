@@ -126,6 +126,66 @@ __global__ void __launch_bounds__(256) cache_write_elem_kernel(const WriteParams
   }
 }
 
+// Dynamic per-(token, head) quantisation (the reference's alternative scheme, vllm_int8/vllm_int8_cache_ops.py:13-131):
+// scale = max(absmax / 127, 1e-6) over the head's D elements, q = round_half_away(clamp(x / scale, +-127)), INT8 row
+// and fp32 scale are stored at the token's slot.  One warp per (token, head); rows up to 16 elements per lane are kept
+// in registers, longer ones are read a second time.
+__global__ void __launch_bounds__(256) cache_write_dynamic_kernel(const DynWriteParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= p.T * p.Hkv) return;
+  const int64_t t = row / p.Hkv;
+  const int h = static_cast<int>(row - t * p.Hkv);
+  const int64_t slot = load_index(p.slots, p.slot_is_i64, t);
+  if (slot < 0 || slot >= p.num_slots) return;
+  const int64_t blk = slot / p.block_size;
+  const int64_t off = slot - blk * p.block_size;
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {
+    const void* src = which ? p.value : p.key;
+    const int64_t* st = which ? p.v_st : p.k_st;
+    int8_t* cache = which ? p.vc : p.kc;
+    const int64_t* cst = which ? p.vc_st : p.kc_st;
+    float* scales = which ? p.vs : p.ks;
+    const int64_t* sst = which ? p.vs_st : p.ks_st;
+    const int64_t base = t * st[0] + h * st[1];
+    constexpr int kKeep = 16;
+    float x[kKeep];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int d = lane + 32 * i;
+      x[i] = d < p.D ? load_as_float(src, p.in_dtype, base + d * st[2]) : 0.f;
+      amax = fmaxf(amax, fabsf(x[i]));
+    }
+    for (int d = lane + 32 * kKeep; d < p.D; d += 32) amax = fmaxf(amax, fabsf(load_as_float(src, p.in_dtype, base + d * st[2])));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax / 127.f, 1e-6f);
+    const int64_t cbase = blk * cst[0] + off * cst[1] + h * cst[2];
+    auto quant = [scale](float v) {
+      float q = fminf(fmaxf(v / scale, -127.f), 127.f);
+      q = q >= 0.f ? floorf(q + 0.5f) : ceilf(q - 0.5f);
+      return static_cast<int8_t>(static_cast<int>(q));
+    };
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const int d = lane + 32 * i;
+      if (d < p.D) cache[cbase + d * cst[3]] = quant(x[i]);
+    }
+    for (int d = lane + 32 * kKeep; d < p.D; d += 32)
+      cache[cbase + d * cst[3]] = quant(load_as_float(src, p.in_dtype, base + d * st[2]));
+    if (lane == 0) scales[blk * sst[0] + off * sst[1] + h * sst[2]] = scale;
+  }
+}
+
+int launch_cache_write_dynamic(const DynWriteParams& p, cudaStream_t stream) {
+  const int64_t rows = p.T * p.Hkv;
+  if (rows <= 0) return INT8KV_OK;
+  const int64_t blocks = (rows + 7) / 8;  // 8 warps per CTA
+  cache_write_dynamic_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream) {

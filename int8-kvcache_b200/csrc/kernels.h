@@ -25,6 +25,25 @@ struct WriteParams {
   const float* v_scale;
 };
 
+struct DynWriteParams {
+  const void* key;
+  const void* value;
+  int in_dtype;
+  int64_t T;
+  int Hkv, D;
+  int64_t k_st[3], v_st[3];
+  int8_t* kc;
+  int8_t* vc;
+  int64_t kc_st[4], vc_st[4];
+  float* ks;  // per-(slot, head) scale caches [num_blocks, BS, Hkv]
+  float* vs;
+  int64_t ks_st[3], vs_st[3];
+  int64_t num_slots;
+  int block_size;
+  const void* slots;
+  int slot_is_i64;
+};
+
 // cache element kinds
 enum CacheKind { kCacheInt8 = 0, kCacheBf16 = 1, kCacheFp16 = 2 };
 
@@ -74,6 +93,7 @@ struct MergeParams {
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
+int launch_cache_write_dynamic(const DynWriteParams& p, cudaStream_t stream);
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                            cudaStream_t stream);
 int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,

@@ -132,6 +132,51 @@ def int8_kv_cache_write(
     _lib.check("int8kv_cache_write", rc)
 
 
+def reshape_and_cache_int8(
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    k_scale_cache: torch.Tensor,
+    v_scale_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> None:
+    """Dynamic INT8 quantisation with one scale per (token, KV head): writes the INT8 rows into the paged
+    caches and the fp32 scales into [num_blocks, BS, Hkv] scale caches at slot_mapping.  Signature and
+    checks of the reference's vllm_int8/vllm_int8_cache_ops.py:134-210."""
+    assert key.is_cuda and value.is_cuda and key_cache.is_cuda and value_cache.is_cuda and slot_mapping.is_cuda
+    assert key.ndim == 3 and value.ndim == 3 and key.shape == value.shape
+    num_tokens, num_kv_heads, head_dim = key.shape
+    assert key_cache.ndim == 4 and value_cache.ndim == 4
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    assert k_scale_cache.dtype == torch.float32 and v_scale_cache.dtype == torch.float32
+    assert slot_mapping.numel() == num_tokens
+    num_blocks, block_size, cache_heads, cache_dim = key_cache.shape
+    assert cache_heads == num_kv_heads and cache_dim == head_dim
+    assert value_cache.shape == key_cache.shape
+    assert tuple(k_scale_cache.shape) == (num_blocks, block_size, num_kv_heads)
+    assert tuple(v_scale_cache.shape) == (num_blocks, block_size, num_kv_heads)
+    assert key.dtype in _FLOAT_CODES and value.dtype == key.dtype
+    assert slot_mapping.dtype in (torch.int32, torch.int64)
+    lib = _require_lib()
+    slot_mapping = slot_mapping.reshape(-1)
+    if slot_mapping.stride(0) != 1:
+        slot_mapping = slot_mapping.contiguous()
+    rc = lib.int8kv_cache_write_dynamic(
+        key.data_ptr(), value.data_ptr(), _FLOAT_CODES[key.dtype],
+        num_tokens, num_kv_heads, head_dim,
+        _lib.i64(key.stride()), _lib.i64(value.stride()),
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        k_scale_cache.data_ptr(), v_scale_cache.data_ptr(),
+        _lib.i64(k_scale_cache.stride()), _lib.i64(v_scale_cache.stride()),
+        num_blocks, block_size,
+        slot_mapping.data_ptr(), int(slot_mapping.dtype == torch.int64),
+        _stream_ptr(key.device),
+    )
+    _lib.check("int8kv_cache_write_dynamic", rc)
+
+
 # ---------------------------------------------------------------------------------------------------
 # paged decode attention
 # ---------------------------------------------------------------------------------------------------
@@ -285,6 +330,67 @@ def bf16_paged_attention(
         _stream_ptr(query.device),
     )
     _lib.check("int8kv_paged_attn_bf16", rc)
+    return out
+
+
+def int8_decode_step(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    *,
+    max_seq_len: int,
+    num_splits: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One layer's decode step in one library call: write the step's new K/V rows [B, Hkv, D] at slot_mapping,
+    then attend with query [B, Hq, D] over the updated cache (seq_lens already count the new tokens).  Equivalent
+    to int8_kv_cache_write followed by int8_paged_attention; `max_seq_len` is required, so the call never
+    synchronises and can be captured in a CUDA graph."""
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    assert key.is_cuda and value.is_cuda and slot_mapping.is_cuda
+    assert key.shape == (B, Hkv, D) and value.shape == key.shape
+    assert key.dtype in _FLOAT_CODES and value.dtype == key.dtype
+    assert slot_mapping.ndim == 1 and slot_mapping.numel() == B and slot_mapping.dtype in (torch.int32, torch.int64)
+    assert k_scale.numel() == Hkv and v_scale.numel() == Hkv
+    lib = _require_lib()
+    k_scale = _as_f32_scale(k_scale)
+    v_scale = _as_f32_scale(v_scale)
+    if out is None:
+        out = torch.empty((B, Hq, D), device=query.device, dtype=query.dtype)
+    else:
+        assert out.shape == (B, Hq, D) and out.dtype in _FLOAT_CODES and out.is_cuda
+    if B == 0:
+        return out
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    if slot_mapping.stride(0) != 1:
+        slot_mapping = slot_mapping.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, int(max_seq_len), num_splits)
+    rc = lib.int8kv_decode_step(
+        key.data_ptr(), value.data_ptr(), _FLOAT_CODES[key.dtype], _lib.i64(key.stride()), _lib.i64(value.stride()),
+        slot_mapping.data_ptr(), int(slot_mapping.dtype == torch.int64),
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), int(max_seq_len),
+        k_scale.data_ptr(), v_scale.data_ptr(),
+        out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
+        splits, ws.data_ptr(), ws.numel(),
+        _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_decode_step", rc)
     return out
 
 

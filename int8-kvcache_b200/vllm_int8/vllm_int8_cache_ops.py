@@ -1,11 +1,13 @@
-"""Drop-in for `runtime_int8_cache_write` of the reference module vllm_int8/vllm_int8_cache_ops.py:281-306:
-the shape checks vLLM's runtime tensors must pass, then the INT8 cache write."""
+"""Drop-in for the reference module vllm_int8/vllm_int8_cache_ops.py: `runtime_int8_cache_write` (:281-306, the
+static-scale write used by the attention path) and the dynamic per-(token, head) scheme with its helpers
+(`reshape_and_cache_int8` :134-210, `allocate_int8_kv_cache` :213-247, `dequantize_int8_cache` :250-256,
+`print_int8_cache_memory` :263-277)."""
 
 from __future__ import annotations
 
 import torch
 
-from ..ops import int8_kv_cache_write
+from ..ops import int8_kv_cache_write, reshape_and_cache_int8  # noqa: F401
 
 
 def runtime_int8_cache_write(
@@ -26,3 +28,29 @@ def runtime_int8_cache_write(
     assert k_scale.shape == (key.shape[1],)
     assert v_scale.shape == (key.shape[1],)
     int8_kv_cache_write(key, value, key_cache, value_cache, slot_mapping, k_scale, v_scale)
+
+
+def allocate_int8_kv_cache(num_blocks: int, block_size: int, num_kv_heads: int, head_dim: int, device="cuda"):
+    """(key_cache, value_cache int8 [num_blocks, BS, Hkv, D], k_scale_cache, v_scale_cache fp32 [num_blocks, BS, Hkv])."""
+    key_cache = torch.empty((num_blocks, block_size, num_kv_heads, head_dim), device=device, dtype=torch.int8)
+    k_scale_cache = torch.empty((num_blocks, block_size, num_kv_heads), device=device, dtype=torch.float32)
+    return key_cache, torch.empty_like(key_cache), k_scale_cache, torch.empty_like(k_scale_cache)
+
+
+def dequantize_int8_cache(cache: torch.Tensor, scale_cache: torch.Tensor) -> torch.Tensor:
+    """Debug helper: INT8 cache times its per-(slot, head) scale -> fp32."""
+    assert cache.dtype == torch.int8
+    return cache.float() * scale_cache[..., None]
+
+
+def int8_cache_memory_bytes(key_cache, value_cache, k_scale_cache, v_scale_cache):
+    """(INT8 payload bytes, scale bytes)."""
+    nbytes = lambda x: x.numel() * x.element_size()
+    return nbytes(key_cache) + nbytes(value_cache), nbytes(k_scale_cache) + nbytes(v_scale_cache)
+
+
+def print_int8_cache_memory(key_cache, value_cache, k_scale_cache, v_scale_cache) -> None:
+    kv_bytes, scale_bytes = int8_cache_memory_bytes(key_cache, value_cache, k_scale_cache, v_scale_cache)
+    print(f"K/V INT8 : {kv_bytes / 1024**2:.3f} MB")
+    print(f"Scales    : {scale_bytes / 1024**2:.3f} MB")
+    print(f"Total     : {(kv_bytes + scale_bytes) / 1024**2:.3f} MB")

@@ -22,6 +22,7 @@ own Python code, generated in a container where the reference is importable
 
 from .quant import (  # noqa: F401
     static_quant_per_head,
+    dynamic_quant_per_token_head,
     dequant_per_head,
     SCALE_FLOOR,
 )

@@ -43,3 +43,17 @@ def dequant_per_head(
     """int8 -> float: q * scale[head] (src/quant.py:33-34)."""
     s = scale.detach().to(dtype).reshape(-1)
     return q.to(dtype) * _as_head_broadcast(s, q.ndim, head_axis)
+
+
+def dynamic_quant_per_token_head(x: torch.Tensor):
+    """x [T, Hkv, D] -> (int8 [T, Hkv, D], fp32 scale [T, Hkv]): one scale per (token, head),
+    scale = max(absmax / 127, 1e-6), q = clamp(x / scale, +-127) rounded half away from zero in fp32.
+
+    Follows the arithmetic of the reference's dynamic write kernel
+    (vllm_int8/vllm_int8_cache_ops.py:70-93), which is its only definition of this scheme; the reference pins it
+    only through a dequantisation-error bound (tests/test_vllm_int8_cache_ops.py: mean abs error < 0.02)."""
+    xf = x.to(torch.float32)
+    scale = torch.clamp_min(xf.abs().amax(dim=-1) / 127.0, SCALE_FLOOR)
+    q = torch.clamp(xf / scale.unsqueeze(-1), -127.0, 127.0)
+    q = torch.where(q >= 0, torch.floor(q + 0.5), torch.ceil(q - 0.5))
+    return q.to(torch.int8), scale

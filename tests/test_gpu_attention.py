@@ -239,3 +239,24 @@ def test_partial_rows_and_merge_reproduce_a_sequence_split(kv, workloads):
     merged = kv.merge_partials(torch.stack(parts).contiguous(), 128, dtype=torch.bfloat16)
     _check(merged, want)
     assert kv.device_status() == 0
+
+
+def test_decode_step_equals_write_then_attend(kv, workloads):
+    lens = [513, 97, 1030, 16]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=16)
+    dev = "cuda"
+    last = torch.tensor([sum(lens[: b + 1]) - 1 for b in range(len(lens))])
+    # caches hold everything but each sequence's last token
+    kc0, vc0 = torch.zeros_like(kc), torch.zeros_like(vc)
+    keep = torch.ones(sum(lens), dtype=torch.bool)
+    keep[last] = False
+    oracle.cache_write(case.key[keep], case.value[keep], kc0, vc0, case.slot_mapping[keep], case.k_scale, case.v_scale)
+    kcd, vcd = kc0.to(dev), vc0.to(dev)
+    out = kv.int8_decode_step(case.query.to(dev), case.key[last].to(dev), case.value[last].to(dev), kcd, vcd,
+                              case.slot_mapping[last].to(dev), case.block_tables.to(dev), case.seq_lens.to(dev),
+                              case.k_scale.to(dev), case.v_scale.to(dev), max_seq_len=max(lens))
+    assert torch.equal(kcd.cpu(), kc) and torch.equal(vcd.cpu(), vc)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    _check(out, want)
+    two = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale))
+    assert torch.equal(out, two)

@@ -154,3 +154,39 @@ def test_empty_and_argument_errors(kv):
         kv.int8_kv_cache_write(key, key, kc.float(), vc, torch.zeros(3, dtype=torch.int64, device=dev), s, s)
     with pytest.raises(AssertionError):
         kv.int8_kv_cache_write(key, key, kc, vc, torch.zeros(3, dtype=torch.float32, device=dev), s, s)
+
+
+def test_dynamic_per_token_head_write(kv):
+    """The reference's alternative scheme: bit-exact against the restated kernel arithmetic, and the
+    reference test's own bound (mean abs dequantisation error < 0.02; tests/test_vllm_int8_cache_ops.py)."""
+    from conftest import package
+
+    ops = package("vllm_int8.vllm_int8_cache_ops")
+    g = torch.Generator().manual_seed(0)
+    for dtype, D in ((torch.bfloat16, 128), (torch.float16, 80), (torch.float32, 576)):
+        T, H = 23, 4
+        key = torch.randn(T, H, D, generator=g).to(dtype)
+        value = (torch.randn(T, H, D, generator=g) * 3).to(dtype)
+        key[3, 1] = 0  # all-zero row: scale floors at 1e-6
+        slots = torch.arange(7, 7 + T, dtype=torch.int64)
+        slots[5] = -1
+        kc, vc, ksc, vsc = ops.allocate_int8_kv_cache(32, 16, H, D, device="cuda")
+        for t in (kc, vc):
+            t.fill_(CANARY)
+        ksc.fill_(-1.0)
+        vsc.fill_(-1.0)
+        ops.reshape_and_cache_int8(key.cuda(), value.cuda(), kc, vc, ksc, vsc, slots.cuda())
+        kq, ks = oracle.dynamic_quant_per_token_head(key)
+        vq, vs = oracle.dynamic_quant_per_token_head(value)
+        kc_o = torch.full((32 * 16, H, D), CANARY, dtype=torch.int8)
+        vc_o = torch.full_like(kc_o, CANARY)
+        ks_o = torch.full((32 * 16, H), -1.0)
+        vs_o = torch.full_like(ks_o, -1.0)
+        live = slots >= 0
+        kc_o[slots[live]], vc_o[slots[live]] = kq[live], vq[live]
+        ks_o[slots[live]], vs_o[slots[live]] = ks[live], vs[live]
+        assert torch.equal(kc.cpu().reshape(-1, H, D), kc_o) and torch.equal(vc.cpu().reshape(-1, H, D), vc_o)
+        assert torch.equal(ksc.cpu().reshape(-1, H), ks_o) and torch.equal(vsc.cpu().reshape(-1, H), vs_o)
+        deq = ops.dequantize_int8_cache(kc, ksc).cpu().reshape(-1, H, D)[slots[live]]
+        assert float((deq - key[live].float()).abs().mean()) < 0.02
+        assert ops.int8_cache_memory_bytes(kc, vc, ksc, vsc) == (2 * 32 * 16 * H * D, 2 * 32 * 16 * H * 4)

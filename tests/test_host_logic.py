@@ -41,6 +41,11 @@ REFERENCE_SIGNATURES = {
         ["query", "key_cache", "value_cache", "block_tables", "seq_lens"],
     ("vllm_int8.vllm_int8_cache_ops", "runtime_int8_cache_write"):
         ["key", "value", "key_cache", "value_cache", "slot_mapping", "k_scale", "v_scale"],
+    ("vllm_int8.vllm_int8_cache_ops", "reshape_and_cache_int8"):
+        ["key", "value", "key_cache", "value_cache", "k_scale_cache", "v_scale_cache", "slot_mapping"],
+    ("vllm_int8.vllm_int8_cache_ops", "allocate_int8_kv_cache"):
+        ["num_blocks", "block_size", "num_kv_heads", "head_dim", "device"],
+    ("vllm_int8.vllm_int8_cache_ops", "dequantize_int8_cache"): ["cache", "scale_cache"],
     ("vllm_int8.vllm_int8_attention_patch", "_run_int8_attention"): ["layer", "query", "attn_metadata"],
     ("vllm_int8.vllm_int8_attention_patch", "_is_supported_decode"): ["query", "attn_metadata"],
 }
