@@ -1,11 +1,28 @@
-"""The decode call site of the reference's attention patch (vllm_int8/vllm_int8_attention_patch.py:60-137):
-the gate that recognises a pure decode step and the call that serves it from the layer's INT8 cache.
-The monkey-patching of vLLM itself is outside this package."""
+"""The attention call site of the reference's patch (vllm_int8/vllm_int8_attention_patch.py:60-334): the gate that
+recognises a pure decode step, the call that serves it from the layer's INT8 cache, and the wrapper of an
+attention implementation's `forward` in the reference's three modes:
+
+  shadow     run the original, run INT8 beside it, record cosine / relative L2 / MAE, return the original
+  takeover   same comparison, but the INT8 result overwrites the output
+  int8_only  INT8 alone (no comparison, no extra synchronisation), counted in ATTN_INT8_HITS
+
+Anything that is not a decode step, or a layer without an INT8 cache, goes to the original forward.
+"""
 
 from __future__ import annotations
 
+from typing import Dict, List
+
+import torch
+
 from ..ops import int8_paged_attention
-from .cache_manager import get_layer_cache
+from .cache_manager import get_layer_cache, has_layer_cache
+
+ATTN_COMPARE_COUNT: Dict[str, int] = {}
+ATTN_METRICS: Dict[str, List[dict]] = {}
+ATTN_INT8_HITS: Dict[str, int] = {}
+ATTN_INT8_STATS: Dict[str, int] = {"last_batch": 0, "max_batch": 0}
+_PATCHED_CLASSES = set()
 
 
 def _get_block_table(attn_metadata):
@@ -45,3 +62,58 @@ def _run_int8_attention(layer, query, attn_metadata):
         shadow.v_scale,
         quantize_q=False,
     )
+
+
+def _compare(int8_out: torch.Tensor, ref_out: torch.Tensor) -> dict:
+    a, b = int8_out.float().reshape(-1), ref_out.float().reshape(-1)
+    return {
+        "cosine": float(torch.nn.functional.cosine_similarity(a, b, dim=0)),
+        "relative_l2": float((a - b).norm() / b.norm().clamp_min(1e-12)),
+        "mae": float((a - b).abs().mean()),
+    }
+
+
+def apply_int8_attention_patch(impl_cls=None, *, mode: str = "shadow", verbose_layer: int = 0, max_compare_calls: int = 8):
+    """Wrap impl_cls.forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
+    output_block_scale=None) in the given mode; vLLM's TritonAttentionImpl is patched when no class is given."""
+    del verbose_layer, max_compare_calls  # accepted for call compatibility; this module does not print
+    if mode not in ("shadow", "takeover", "int8_only"):
+        raise ValueError(f"Unknown mode: {mode}")
+    if impl_cls is None:
+        from vllm.v1.attention.backends.triton_attn import TritonAttentionImpl as impl_cls
+    if impl_cls in _PATCHED_CLASSES:
+        raise RuntimeError("Attention has already been patched in this Python process.")
+    original_forward = impl_cls.forward
+
+    def patched_forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
+                        output_block_scale=None):
+        name = getattr(layer, "layer_name", None)
+        if name is None or not has_layer_cache(name) or not _is_supported_decode(query, attn_metadata):
+            return original_forward(self, layer, query, key, value, kv_cache, attn_metadata, output,
+                                    output_scale=output_scale, output_block_scale=output_block_scale)
+        if mode == "int8_only":
+            int8_out = _run_int8_attention(layer, query, attn_metadata)
+            ATTN_INT8_HITS[name] = ATTN_INT8_HITS.get(name, 0) + 1
+            batch = int(attn_metadata.seq_lens.numel())
+            ATTN_INT8_STATS["last_batch"] = batch
+            ATTN_INT8_STATS["max_batch"] = max(ATTN_INT8_STATS.get("max_batch", 0), batch)
+            n = int8_out.shape[0]
+            output[:n].copy_(int8_out.reshape_as(output[:n]))
+            return output
+        result = original_forward(self, layer, query, key, value, kv_cache, attn_metadata, output,
+                                  output_scale=output_scale, output_block_scale=output_block_scale)
+        int8_out = _run_int8_attention(layer, query, attn_metadata)
+        n = int8_out.shape[0]
+        ref_out = output[:n].detach().reshape(int8_out.shape)
+        ATTN_COMPARE_COUNT[name] = ATTN_COMPARE_COUNT.get(name, 0) + 1
+        ATTN_METRICS.setdefault(name, []).append(_compare(int8_out, ref_out))
+        if mode == "shadow":
+            return result
+        assert not torch.isnan(int8_out).any() and not torch.isinf(int8_out).any()
+        output[:n].copy_(int8_out.reshape_as(output[:n]))
+        ATTN_INT8_HITS[name] = ATTN_INT8_HITS.get(name, 0) + 1
+        return output
+
+    impl_cls.forward = patched_forward
+    _PATCHED_CLASSES.add(impl_cls)
+    return impl_cls

@@ -260,3 +260,60 @@ def test_decode_step_equals_write_then_attend(kv, workloads):
     _check(out, want)
     two = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale))
     assert torch.equal(out, two)
+
+
+def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
+    """do_kv_cache_update -> INT8 mirror write, forward -> INT8 attention, through the patched methods of a fake
+    attention-implementation class, in all three modes."""
+    from conftest import package
+
+    sc, sh = package("vllm_int8.static_scales"), package("vllm_int8.vllm_shadow_cache_patch")
+    ap, pool = package("vllm_int8.vllm_int8_attention_patch"), package("vllm_int8.cache_manager")
+    lens = [300, 77]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=18)
+    dev = "cuda"
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+
+    class Meta:
+        seq_lens = case.seq_lens.to(dev)
+        block_table = case.block_tables.to(dev)
+        num_actual_tokens = 2
+        max_query_len = 1
+
+    for mode in ("shadow", "takeover", "int8_only"):
+        pool.clear_cache_pool()
+        sc.set_static_scales(case.k_scale.repeat(28, 1), case.v_scale.repeat(28, 1))
+        for d in (ap.ATTN_INT8_HITS, ap.ATTN_METRICS, ap.ATTN_COMPARE_COUNT, sh.WRITE_CALL_COUNT):
+            d.clear()
+
+        class Impl:
+            def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
+                pass
+
+            def forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
+                        output_block_scale=None):
+                output[:2].copy_(want.to(output.dtype).to(output.device))  # stands in for the engine's bf16 attention
+                return output
+
+        class Layer:
+            layer_name = "model.layers.5.self_attn.attn"
+
+        sh.apply_shadow_cache_patch(Impl)
+        ap.apply_int8_attention_patch(Impl, mode=mode)
+        impl = Impl()
+        native = torch.empty(case.num_blocks, 4, 16, 256, dtype=torch.bfloat16, device=dev)
+        impl.do_kv_cache_update(Layer(), case.key.to(dev), case.value.to(dev), native, case.slot_mapping.to(dev))
+        shadow = pool.get_layer_cache(Layer.layer_name)
+        assert torch.equal(shadow.key_cache.cpu(), kc) and torch.equal(shadow.value_cache.cpu(), vc)
+        padded_q = torch.zeros(4, 28, 128, dtype=torch.bfloat16, device=dev)
+        padded_q[:2] = case.query.to(dev)
+        out = torch.zeros(4, 28, 128, dtype=torch.bfloat16, device=dev)
+        res = impl.forward(Layer(), padded_q, None, None, native, Meta(), out)
+        _check(res[:2], want)
+        if mode == "int8_only":
+            assert ap.ATTN_INT8_HITS[Layer.layer_name] == 1 and ap.ATTN_INT8_STATS["last_batch"] == 2
+        else:
+            m = ap.ATTN_METRICS[Layer.layer_name][0]
+            assert m["cosine"] > 0.9999 and m["relative_l2"] < 0.02
+    pool.clear_cache_pool()
+    sc.clear_static_scales()

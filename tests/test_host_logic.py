@@ -174,3 +174,118 @@ def test_sequence_split_lengths(kv):
             assert local[2] == 0 and local[3] == 0
     assert total == lens
     assert sh.sequence_split([100], 1, 2, 16, blocks_per_rank=2) == (2, 4, [32])
+
+
+def test_static_scales_lookup_and_native_page_dims(tmp_path):
+    sc = package("vllm_int8.static_scales")
+    sh = package("vllm_int8.vllm_shadow_cache_patch")
+    k = torch.arange(28 * 4, dtype=torch.float32).reshape(28, 4) / 100 + 0.01
+    path = tmp_path / "scales.pt"
+    torch.save({"k_scale": k, "v_scale": k * 2, "k_amax": k * 127, "v_amax": k * 254}, path)
+    sc.clear_static_scales()
+    with pytest.raises(RuntimeError):
+        sc.get_layer_scales("model.layers.3.self_attn.attn", "cpu")
+    sc.load_static_scales(str(path))
+    ks, vs = sc.get_layer_scales("model.layers.12.self_attn.attn", "cpu")
+    assert torch.equal(ks, k[12]) and torch.equal(vs, 2 * k[12]) and ks.is_contiguous() and ks.dtype == torch.float32
+    assert sc.extract_layer_idx("language_model.model.layers.27.self_attn.attn") == 27
+    with pytest.raises(RuntimeError):
+        sc.extract_layer_idx("lm_head")
+    # the three native cache layouts of the engine
+    assert sh._infer_native_page_dims(torch.empty(9, 4, 16, 256), 4) == (9, 16)
+    assert sh._infer_native_page_dims(torch.empty(9, 2, 16, 4, 128), 4) == (9, 16)
+    assert sh._infer_native_page_dims(torch.empty(2, 9, 32, 4, 128), 4) == (9, 32)
+    with pytest.raises(ValueError):
+        sh._infer_native_page_dims(torch.empty(9, 16), 4)
+    sc.clear_static_scales()
+
+
+def test_shadow_cache_patch_wiring_with_a_fake_engine_class():
+    """The patched method runs the original first, allocates the layer's INT8 cache once from the native page
+    geometry and the layer's scales, and hands the flattened slots to the write operator."""
+    sc = package("vllm_int8.static_scales")
+    sh = package("vllm_int8.vllm_shadow_cache_patch")
+    pool = package("vllm_int8.cache_manager")
+    pool.clear_cache_pool()
+    sh.WRITE_CALL_COUNT.clear()
+    sc.set_static_scales(torch.full((4, 2), 0.05), torch.full((4, 2), 0.07))
+    calls = []
+
+    class FakeImpl:
+        def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
+            calls.append("native")
+
+    class Layer:
+        layer_name = "model.layers.2.self_attn.attn"
+
+    def fake_writer(key, value, kc, vc, slots, ks, vs):
+        calls.append(("int8", tuple(kc.shape), slots.tolist(), float(ks[0]), float(vs[0])))
+
+    key = torch.zeros(3, 2, 8)
+    native = torch.zeros(5, 2, 16, 16)  # fused layout [blocks, Hkv, BS, 2D]
+    sh.shadow_cache_update(Layer(), key, key, native, torch.tensor([[4], [5], [-1]]), writer=fake_writer)
+    assert calls[-1] == ("int8", (5, 16, 2, 8), [4, 5, -1], pytest.approx(0.05), pytest.approx(0.07))
+    assert sh.WRITE_CALL_COUNT[Layer.layer_name] == 1 and sh.NATIVE_CACHE_BYTES_BY_LAYER[Layer.layer_name] == native.numel() * 4
+    first = pool.get_layer_cache(Layer.layer_name)
+    sh.shadow_cache_update(Layer(), key, key, native, torch.tensor([6, 7, 8]), writer=fake_writer)
+    assert pool.get_layer_cache(Layer.layer_name) is first and sh.WRITE_CALL_COUNT[Layer.layer_name] == 2
+    with pytest.raises(AssertionError):
+        sh.shadow_cache_update(Layer(), key, key, native, torch.tensor([6, 7]), writer=fake_writer)
+    # class wrapping is idempotent and keeps the original call first (the INT8 write itself needs a GPU)
+    assert sh.apply_shadow_cache_patch(FakeImpl) is FakeImpl
+    patched = FakeImpl.do_kv_cache_update
+    sh.apply_shadow_cache_patch(FakeImpl)
+    assert FakeImpl.do_kv_cache_update is patched
+    pool.clear_cache_pool()
+    sc.clear_static_scales()
+
+
+def test_attention_patch_falls_back_outside_decode_and_rejects_unknown_modes():
+    ap = package("vllm_int8.vllm_int8_attention_patch")
+    pool = package("vllm_int8.cache_manager")
+    pool.clear_cache_pool()
+
+    class FakeImpl:
+        def forward(self, layer, query, key, value, kv_cache, attn_metadata, output, output_scale=None,
+                    output_block_scale=None):
+            output.fill_(3.0)
+            return output
+
+    with pytest.raises(ValueError):
+        ap.apply_int8_attention_patch(FakeImpl, mode="fast")
+    ap.apply_int8_attention_patch(FakeImpl, mode="int8_only")
+    with pytest.raises(RuntimeError):
+        ap.apply_int8_attention_patch(FakeImpl, mode="shadow")
+
+    class Layer:
+        layer_name = "model.layers.0.self_attn.attn"
+
+    out = torch.zeros(2, 28, 128)
+    # no INT8 cache for the layer -> original forward
+    res = FakeImpl().forward(Layer(), torch.zeros(2, 28, 128), None, None, None, None, out)
+    assert res is out and float(out.min()) == 3.0 and ap.ATTN_INT8_HITS.get(Layer.layer_name, 0) == 0
+
+
+def test_scale_calibration_accumulates_running_maxima(tmp_path):
+    cal_mod = package("calibration")
+    sc = package("vllm_int8.static_scales")
+    g = torch.Generator().manual_seed(1)
+    cal = cal_mod.ScaleCalibrator(num_layers=3, num_kv_heads=4)
+    dumps = [{l: {"k": torch.randn(2, 4, 10, 128, generator=g).half() * (l + 1),
+                  "v": torch.randn(2, 4, 10, 128, generator=g).half()} for l in (0, 2)} for _ in range(3)]
+    for d in dumps:
+        cal.observe_dump(d)
+    out = cal.scales()
+    for l in (0, 2):
+        k_all = torch.cat([d[l]["k"] for d in dumps]).float()
+        assert torch.equal(out["k_amax"][l], k_all.abs().amax(dim=(0, 2, 3)))
+        assert torch.equal(out["k_scale"][l], (out["k_amax"][l] / 127.0).clamp_min(1e-6))
+    assert torch.equal(out["k_scale"][1], torch.full((4,), 1e-6))  # a layer never observed floors at 1e-6
+    # token-major observation ([T, Hkv, D], head axis 1) and the file round trip into the scale lookup
+    cal.observe(1, torch.ones(5, 4, 8) * 2.54, torch.ones(5, 4, 8), head_axis=1)
+    path = tmp_path / "scales.pt"
+    cal.save(str(path))
+    sc.load_static_scales(str(path))
+    ks, vs = sc.get_layer_scales("model.layers.1.self_attn.attn", "cpu")
+    assert torch.allclose(ks, torch.full((4,), 0.02)) and torch.allclose(vs, torch.full((4,), 1 / 127.0))
+    sc.clear_static_scales()
