@@ -78,8 +78,6 @@ int64_t ws_bytes(int B, int Hq, int D, int S) {
   return rows + 16;  // trailing 16 bytes hold the status word
 }
 
-int min_splits_for(int64_t max_seq) { return static_cast<int>((max_seq + 32767) / 32768 > 0 ? (max_seq + 32767) / 32768 : 1); }
-
 int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
   (void)block_size;
   if (B <= 0 || Hkv <= 0 || max_seq <= 0) return 1;
@@ -97,7 +95,6 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   while (pow2 < s) pow2 *= 2;
   s = pow2;
   while (s > 1 && (s > by_len || s > kMaxSplits)) s /= 2;
-  if (s < min_splits_for(max_seq)) s = min_splits_for(max_seq);
   if (s < 1) s = 1;
   return static_cast<int>(s);
 }
@@ -138,9 +135,6 @@ int run_attention(const AttnCall& a) {
   // more splits than 16-token tiles only produces empty parts
   const int64_t tiles = (max_seq + 15) / 16;
   if (S > tiles) S = tiles > 0 ? static_cast<int>(tiles) : 1;
-  // the INT8 kernel accumulates P.V in 32-bit integers: at most 32768 tokens per part keeps them in range
-  // whatever the data (255 * 127 per token and limb)
-  if (a.cache_kind == kCacheInt8 && S < min_splits_for(max_seq)) S = min_splits_for(max_seq);
 
   const int rf = partial_row_floats(a.D);
   const int64_t need = ws_bytes(a.B, a.Hq, a.D, S);
@@ -436,7 +430,6 @@ int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64
   int splits = num_splits > 0 ? num_splits : choose_splits(batch, num_kv_heads, max_seq, block_size, device_sm_count());
   const int64_t tiles = (max_seq + 15) / 16;
   if (splits > tiles) splits = tiles > 0 ? static_cast<int>(tiles) : 1;
-  if (splits < min_splits_for(max_seq)) splits = min_splits_for(max_seq);
   if (ws_bytes(batch, num_q_heads, head_dim, splits) > INT8KV_STATIC_WS_BYTES) return INT8KV_E_WORKSPACE;
   void* ws = nullptr;
   const int rc = static_ws_address(&ws);

@@ -221,51 +221,7 @@ __device__ __forceinline__ void qk_tile(int (&s)[4], uint32_t kbase, const uint3
   for (int i = 0; i < 4; ++i) s[i] = (hi[i] << 8) + lo[i];
 }
 
-// ---- integer PV path ---------------------------------------------------------------------------------------
-// O^T += V^T . P^T on the INT8 tensor cores, with the V bytes as they are and P as 16-bit fixed point split into
-// two unsigned byte limbs.  A pair of tiles (32 tokens) is one k = 32 MMA step: k-slots 4t..4t+3 carry tile A's
-// tokens 2t, 2t+1, 2t+8, 2t+9 and k-slots 16+4t.. the same tokens of tile B (the rows this lane holds anyway).
-// The A operand needs four tokens of one dim in a register: a 4x4 byte transpose of the lane's row pieces.
-__device__ __forceinline__ void transpose4x4(uint32_t (&o)[4], uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3) {
-  const uint32_t x01l = prmt(w0, w1, 0x5140u), x01h = prmt(w0, w1, 0x7362u);
-  const uint32_t x23l = prmt(w2, w3, 0x5140u), x23h = prmt(w2, w3, 0x7362u);
-  o[0] = prmt(x01l, x23l, 0x5410u);
-  o[1] = prmt(x01l, x23l, 0x7632u);
-  o[2] = prmt(x01h, x23h, 0x5410u);
-  o[3] = prmt(x01h, x23h, 0x7632u);
-}
-
-__device__ __forceinline__ void pv_pair_int(int (&ah)[8][4], int (&al)[8][4], const uint4 (&va)[4], const uint4 (&vb)[4],
-                                            uint32_t b0_hi, uint32_t b1_hi, uint32_t b0_lo, uint32_t b1_lo) {
-  const uint32_t* a0 = reinterpret_cast<const uint32_t*>(&va[0]);
-  const uint32_t* a1 = reinterpret_cast<const uint32_t*>(&va[1]);
-  const uint32_t* a2 = reinterpret_cast<const uint32_t*>(&va[2]);
-  const uint32_t* a3 = reinterpret_cast<const uint32_t*>(&va[3]);
-  const uint32_t* c0 = reinterpret_cast<const uint32_t*>(&vb[0]);
-  const uint32_t* c1 = reinterpret_cast<const uint32_t*>(&vb[1]);
-  const uint32_t* c2 = reinterpret_cast<const uint32_t*>(&vb[2]);
-  const uint32_t* c3 = reinterpret_cast<const uint32_t*>(&vb[3]);
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t ta[4], tb[4];  // [d'] = the four tokens at dim 16g + 4c + d'
-    transpose4x4(ta, a0[c], a1[c], a2[c], a3[c]);
-    transpose4x4(tb, c0[c], c1[c], c2[c], c3[c]);
-    mma_s8u8(ah[2 * c], ta[0], ta[1], tb[0], tb[1], b0_hi, b1_hi);
-    mma_s8u8(al[2 * c], ta[0], ta[1], tb[0], tb[1], b0_lo, b1_lo);
-    mma_s8u8(ah[2 * c + 1], ta[2], ta[3], tb[2], tb[3], b0_hi, b1_hi);
-    mma_s8u8(al[2 * c + 1], ta[2], ta[3], tb[2], tb[3], b0_lo, b1_lo);
-  }
-}
-
-// Rounded arithmetic shift right by k (0 <= k; 31 or more clears).
-__device__ __forceinline__ int shr_round(int x, int k) {
-  return k >= 31 ? 0 : ((x + ((1 << k) >> 1)) >> k);
-}
-
-constexpr int kPBits = 12;       // P = 2^(score - ref) is stored as round(P * 2^12) in 16 bits ...
-constexpr float kPHeadroom = 3.99f;  // ... so scores may exceed the reference exponent by just under 4
-
-template <int NST, bool INT_PV>
+template <int NST>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
@@ -375,15 +331,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  // integer PV path: two-limb integer accumulators, integer row sums, integer-valued reference exponents
-  int ah[8][4], al[8][4];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    ah[j][0] = ah[j][1] = ah[j][2] = ah[j][3] = 0;
-    al[j][0] = al[j][1] = al[j][2] = al[j][3] = 0;
-  }
-  int li0 = 0, li1 = 0;
-  float r0 = -1.0e30f, r1 = -1.0e30f;
 
   // Two tiles (32 tokens) per iteration: two independent score chains, one max reduction, one rescale test.
   // When the range holds an odd number of tiles the last pair's second tile is all-masked; its stage holds
@@ -430,42 +377,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 8));
     mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 16));
     mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 16));
-    if constexpr (INT_PV) {
-      // The reference exponent of a head moves only when a score would overflow the 16-bit P; then everything
-      // accumulated so far is shifted down by the (integer) difference.  After the first pair this is rare.
-      if (__any_sync(kFull, (mx0 > r0 + kPHeadroom) || (mx1 > r1 + kPHeadroom))) {
-        const float n0 = mx0 > r0 + kPHeadroom ? ceilf(mx0) : r0;
-        const float n1 = mx1 > r1 + kPHeadroom ? ceilf(mx1) : r1;
-        const int k0 = static_cast<int>(fminf(n0 - r0, 31.f)), k1 = static_cast<int>(fminf(n1 - r1, 31.f));
-        li0 = shr_round(li0, k0);
-        li1 = shr_round(li1, k1);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          ah[j][0] = shr_round(ah[j][0], k0); ah[j][1] = shr_round(ah[j][1], k1);
-          ah[j][2] = shr_round(ah[j][2], k0); ah[j][3] = shr_round(ah[j][3], k1);
-          al[j][0] = shr_round(al[j][0], k0); al[j][1] = shr_round(al[j][1], k1);
-          al[j][2] = shr_round(al[j][2], k0); al[j][3] = shr_round(al[j][3], k1);
-        }
-        r0 = n0;
-        r1 = n1;
-      }
-      // P as integers: adding 2^23 rounds 2^(score - ref + 12) to nearest-even in the low mantissa bits
-      uint32_t pq[8];
-      const float o0 = static_cast<float>(kPBits) - r0, o1 = static_cast<float>(kPBits) - r1;
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        pq[r] = __float_as_uint(exp2_fast(v[r] + ((r & 1) ? o1 : o0)) + 8388608.f) & 0xffffu;
-      li0 += static_cast<int>((pq[0] + pq[2]) + (pq[4] + pq[6]));
-      li1 += static_cast<int>((pq[1] + pq[3]) + (pq[5] + pq[7]));
-      // (token row | heads 2t, 2t+1) pairs of 16-bit P, transposed to (head g | tokens 2t, 2t+1) per 8 tokens
-      const uint32_t xa0 = movmatrix_trans(pq[0] | (pq[1] << 16));
-      const uint32_t xa1 = movmatrix_trans(pq[2] | (pq[3] << 16));
-      const uint32_t xb0 = movmatrix_trans(pq[4] | (pq[5] << 16));
-      const uint32_t xb1 = movmatrix_trans(pq[6] | (pq[7] << 16));
-      // low and high bytes of the four tokens of each tile: the two unsigned limbs of P^T
-      pv_pair_int(ah, al, va, vb, prmt(xa0, xa1, 0x7531u), prmt(xb0, xb1, 0x7531u), prmt(xa0, xa1, 0x6420u),
-                  prmt(xb0, xb1, 0x6420u));
-    } else {
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
     if (__any_sync(kFull, (mn0 != m0) || (mn1 != m1))) {
       const float al0 = exp2_fast(m0 - mn0), al1 = exp2_fast(m1 - mn1);
@@ -492,7 +403,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     // ---- O^T += V^T . P^T ------------------------------------------------------------------------------
     pv_tile(acc, va, pa0, pa1);
     pv_tile(acc, vb, pb0, pb1);
-    }
 
     __syncwarp();  // every lane has consumed both stages before lane 0 refills them
     if (i + NST < n) ring.issue(i + NST);
@@ -507,18 +417,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     return;
   }
 
-  if constexpr (INT_PV) {
-    // back to the common form: acc = 256 * hi + lo, l = integer row sum, both scaled by 2^12 relative to 2^ref
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-#pragma unroll
-      for (int r = 0; r < 4; ++r) acc[j][r] = static_cast<float>(ah[j][r]) * 256.f + static_cast<float>(al[j][r]);
-    }
-    l0 = static_cast<float>(li0);
-    l1 = static_cast<float>(li1);
-    m0 = r0 - static_cast<float>(kPBits);
-    m1 = r1 - static_cast<float>(kPBits);
-  }
   // ---- epilogue: reduce the row sums over the token lanes, normalise, apply v_scale ----------------------
   l0 += __shfl_xor_sync(kFull, l0, 4);
   l1 += __shfl_xor_sync(kFull, l1, 4);
@@ -962,9 +860,9 @@ static int env_int(const char* name, int fallback) {
 
 // Tuning switches, read once from the environment: INT8KV_STAGES (ring depth of the INT8 kernel),
 // INT8KV_WPC (warps per CTA: 1 or 4, 0 = choose from the grid size), INT8KV_PDL (0 disables programmatic
-// dependent launch), INT8KV_INT_PV (0 selects the fp16 PV path of the INT8 kernel).
+// dependent launch).
 struct Tuning {
-  int stages, wpc, pdl, int_pv;
+  int stages, wpc, pdl;
 };
 static const Tuning& tuning() {
   static const Tuning t = []() {
@@ -974,7 +872,6 @@ static const Tuning& tuning() {
     x.wpc = env_int("INT8KV_WPC", 0);
     if (x.wpc != 1 && x.wpc != 4) x.wpc = 0;
     x.pdl = env_int("INT8KV_PDL", 1) != 0;
-    x.int_pv = env_int("INT8KV_INT_PV", -1);  // -1: by part length, 0 / 1: force the fp16 / integer PV path
     return x;
   }();
   return t;
@@ -1024,17 +921,8 @@ template <int NST>
 static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                               cudaStream_t stream) {
   constexpr int smem_max = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
-  // Long parts (>= 64 tiles = 1024 tokens each) run P.V on the INT8 tensor cores with 16-bit fixed-point P:
-  // fewer instructions per byte, worth about 1 % of HBM bandwidth at 65k-token contexts; short parts keep the
-  // fp16 P.V path, whose prologue and epilogue are a little shorter (measured on B200).
-  const int per_part = (p.hint_tiles + p.num_splits - 1) / p.num_splits;
-  const bool int_pv = tuning().int_pv < 0 ? per_part >= 64 : tuning().int_pv != 0;
-  auto kernel = int_pv ? paged_attn_int8_kernel<NST, true> : paged_attn_int8_kernel<NST, false>;
-  if (int_pv) {
-    if (set_smem<30 + NST>(paged_attn_int8_kernel<NST, true>, smem_max) != 0) return INT8KV_E_LAUNCH;
-  } else {
-    if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, false>, smem_max) != 0) return INT8KV_E_LAUNCH;
-  }
+  auto kernel = paged_attn_int8_kernel<NST>;
+  if (set_smem<10 + NST>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
   const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);

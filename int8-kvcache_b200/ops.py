@@ -219,8 +219,6 @@ def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits)
         splits = lib.int8kv_choose_splits(B, Hkv, max_seq, block_size, sm)
     else:
         splits = max(1, min(int(num_splits), lib.int8kv_max_splits()))
-    # the library never gives one part more than 32768 tokens (its integer accumulators are sized for that)
-    splits = max(splits, -(-int(max_seq) // 32768))
     nbytes = lib.int8kv_workspace_bytes(B, Hq, D, splits)
     ws = _workspace(device, nbytes)
     return splits, ws

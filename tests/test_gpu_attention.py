@@ -317,26 +317,3 @@ def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
             assert m["cosine"] > 0.9999 and m["relative_l2"] < 0.02
     pool.clear_cache_pool()
     sc.clear_static_scales()
-
-
-def test_long_parts_take_the_integer_pv_path(kv, workloads):
-    """Parts of 1024 tokens or more run P.V on the INT8 tensor cores with 16-bit fixed-point P and integer
-    accumulators; the result must meet the same bars, also when the reference exponent has to move (a late
-    token that dominates) and when early outliers leave most of the mass at the bottom of the 16-bit range."""
-    lens = [5000, 1100, 2048, 37]
-    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=20)
-    q = case.query.clone()
-    args = lambda qq: _dev(qq, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
-    for splits in (1, 2, None):
-        want = oracle.int8_paged_attention_oracle(q, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
-        _check(kv.int8_paged_attention(*args(q), num_splits=splits), want)
-    # make one early token and one late token of sequence 0 dominate: scale the query towards their keys
-    ks, _ = oracle.gather_paged_cache(kc, vc, case.block_tables, lens)
-    for tok in (3, 4321):
-        q2 = case.query.clone()
-        k_tok = oracle.dequant_per_head(ks[0][:, tok], case.k_scale, head_axis=0)  # [Hkv, D]
-        q2[0] = (k_tok.repeat_interleave(7, dim=0) * 0.6).to(q2.dtype)
-        want = oracle.int8_paged_attention_oracle(q2, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
-        out = kv.int8_paged_attention(*args(q2), num_splits=1)
-        _check(out, want)
-    assert kv.device_status() == 0
