@@ -317,3 +317,32 @@ def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
             assert m["cosine"] > 0.9999 and m["relative_l2"] < 0.02
     pool.clear_cache_pool()
     sc.clear_static_scales()
+
+
+def test_long_parts_and_sink_plus_crowd_distributions(kv, workloads):
+    """Parts of thousands of tokens, and the distribution real decoders produce: one 'sink' token far above a
+    broad crowd of tokens that are individually tiny but carry most of the probability mass together."""
+    lens = [8190, 1100, 2048, 37]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=20)
+    args = lambda qq: _dev(qq, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    for splits in (1, 2, None):
+        _check(kv.int8_paged_attention(*args(case.query), num_splits=splits), want)
+    ks, _ = oracle.gather_paged_cache(kc, vc, case.block_tables, lens)
+    for tok in (0, 4321):
+        k_tok = oracle.dequant_per_head(ks[0][:, tok], case.k_scale, head_axis=0).repeat_interleave(7, dim=0)  # [Hq, D]
+        base = case.query[0].float() * 0.05  # a flat crowd: all other scores within a fraction of a unit
+        lo, hi = 0.0, 1.0
+        for _ in range(20):  # bisect the sink strength so that the sink holds 5-15 % of the mass
+            beta = 0.5 * (lo + hi)
+            q_row = base + beta * k_tok
+            k_all = oracle.dequant_per_head(ks[0], case.k_scale, head_axis=0)  # [Hkv, T, D]
+            sc = torch.einsum("hgd,htd->hgt", q_row.reshape(4, 7, 128), k_all) / math.sqrt(128)
+            share = torch.softmax(sc, dim=-1)[..., tok].mean()
+            lo, hi = (beta, hi) if share < 0.10 else (lo, beta)
+        q2 = case.query.clone()
+        q2[0] = (base + beta * k_tok).to(q2.dtype)
+        want2 = oracle.int8_paged_attention_oracle(q2, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+        for splits in (1, None):
+            _check(kv.int8_paged_attention(*args(q2), num_splits=splits), want2)
+    assert kv.device_status() == 0
