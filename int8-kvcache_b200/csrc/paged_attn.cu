@@ -3,24 +3,29 @@
 // Work decomposition.  The unit of work is one WARP serving one (sequence, KV head, KV split): it reads every
 // 16-token tile of that head's K and V exactly once and serves all query heads of the GQA group from that single
 // read (group <= 8 heads sit on the N=8 side of the tensor-core tile, so 7 heads cost 8/7 padding, not 16/7).  A
-// CTA is four such warps working on consecutive items (with Hkv = 4: the four KV heads of the same pages, whose
-// rows interleave in memory, so one CTA consumes whole contiguous 8 KB pages).  Warps never synchronise with each
-// other; there is no __syncthreads in the kernel.
+// CTA is four such warps working on consecutive items (with Hkv = 4: the four KV heads of the same pages), or a
+// single warp when the grid is too small to fill the machine with 4-warp CTAs.  Warps never synchronise with
+// each other; there is no __syncthreads in the attention kernels.  A sequence uses as many of the num_splits
+// parts as it takes to give each about the tile count of the longest sequence's parts; partial results go to
+// a workspace and merge_partials_kernel, launched with programmatic dependent launch, combines them.
 //
 // Data movement.  Each warp runs its own NST-deep ring of shared-memory stages filled by TMA: one
 // cp.async.bulk.tensor tile load per 16x128-byte K tile and V tile, issued by lane 0, completion counted on an
 // mbarrier per stage.  The tensor map views the cache as (bytes-in-row, token-in-block, head, block) and applies
 // the 128-byte swizzle, which makes both access patterns below bank-conflict free.  Block ids come from
-// block_tables through a register window (32 ids per load, next window prefetched).  Waits are bounded: if a
-// stage never arrives the warp sets a status bit, drains what it issued and returns.
+// block_tables through a register window (32 ids per load, next window prefetched; the first windows are read
+// speculatively while seq_lens[b] is still in flight).  Waits are bounded: if a stage never arrives the warp
+// sets a status bit, drains what it issued and returns.
 //
-// Math (INT8 cache).  S^T = K . Q^T with tokens on M (16 per tile), heads on N (8), dims on K, as fp16 MMA
-// m16n8k16 with fp32 accumulation: int8 -> fp16 is exact (bytes are spliced into 0x64xx = 1024+u and 1152 is
-// subtracted), Q is held as fp16 B fragments whose k-order is permuted so that each lane's A operand is 32
-// consecutive bytes of a K row.  Online softmax runs in the log2 domain on the C fragment (max via three shuffles,
-// the row sum is reduced once at the end).  P^T is obtained from the C fragment with movmatrix (8x8 transpose) and
-// O^T = V^T . P^T puts dims on M: the V^T A fragment needs pairs of tokens at one dim, produced by byte
-// interleaving (prmt) of 16-byte row pieces on the way to fp16.  v_scale and 1/l are applied once in the epilogue.
+// Math (INT8 cache).  S^T = K . Q^T with tokens on M (16 per tile), heads on N (8), dims on K, on the INT8 tensor
+// cores (mma m16n8k32 s8 x s8 -> s32) with the K bytes exactly as they lie in the cache: the query is held as two
+// INT8 limbs (16-bit fixed point per head) in B fragments whose k-order is permuted so that each lane's A operand
+// is 32 consecutive bytes of a K row.  Two tiles are processed per loop iteration.  Online softmax runs in the
+// log2 domain on the C fragments (max via three shuffles, the row sum is reduced once at the end).  P^T is
+// obtained from the C fragments with movmatrix (8x8 transpose) and O^T = V^T . P^T runs as fp16 MMA m16n8k16 with
+// dims on M: int8 -> fp16 is exact (bytes are spliced into 0x64xx = 1024+u and 1152 is subtracted), and the V^T
+// A fragment needs pairs of tokens at one dim, produced by byte interleaving (prmt) of 16-byte row pieces on the
+// way to fp16.  v_scale and 1/l are applied once in the epilogue.
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
