@@ -46,6 +46,7 @@ extern "C" {
 
 /* Bits set by a kernel in the workspace's trailing status word (see int8kv_workspace_status_offset). */
 #define INT8KV_DEV_WAIT_TIMEOUT 1u /* a bounded wait for a staged page ran out; result invalid */
+#define INT8KV_DEV_SLOT_MISMATCH 2u /* int8kv_decode_step: a slot was not the slot of its sequence's last token */
 
 int int8kv_abi_version(void);
 const char* int8kv_status_str(int status);
@@ -141,11 +142,16 @@ int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype,
                                const void* slot_mapping, int slot_is_i64, void* stream);
 
 /*
- * One decode step of one layer in a single call: int8kv_cache_write of the step's `batch` new K/V rows (one per
- * sequence, at slot_mapping), then int8kv_paged_attn_int8 over the updated cache, stream-ordered.  This is the pair
- * of calls that the reference's vLLM hooks make back to back for every layer (do_kv_cache_update then forward,
- * vllm_int8/vllm_shadow_cache_patch.py:154-166 and vllm_int8/vllm_int8_attention_patch.py:117-137); seq_lens
- * already count the new token.
+ * One decode step of one layer in a single call: the step's `batch` new K/V rows (one per sequence) are quantised
+ * and written at slot_mapping, and query attends over the updated cache.  This is the pair of calls that the
+ * reference's vLLM hooks make back to back for every layer (do_kv_cache_update then forward,
+ * vllm_int8/vllm_shadow_cache_patch.py:154-166 and vllm_int8/vllm_int8_attention_patch.py:117-137).
+ * Contract: seq_lens already count the new token and slot_mapping[b] is the slot of token seq_lens[b] - 1 of
+ * sequence b (what a decode step produces), or negative for a padding row.  For the shapes the tiled kernel
+ * covers the write happens inside the attention kernel (no separate launch): the warp that owns a sequence's
+ * last tile quantises the row, stores it to the cache and patches its staged copy.  A slot that is not the last
+ * token's is still written, but attention may not see it and INT8KV_DEV_SLOT_MISMATCH is set in the status word.
+ * Other shapes run int8kv_cache_write followed by int8kv_paged_attn_int8.
  */
 int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
                        const int64_t key_strides[3], const int64_t value_strides[3],

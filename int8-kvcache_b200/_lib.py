@@ -21,6 +21,7 @@ ABI_VERSION = 1
 OK = 0
 E_NULLPTR, E_BAD_SHAPE, E_BAD_DTYPE, E_UNSUPPORTED, E_LAUNCH, E_WORKSPACE = -1, -2, -3, -4, -5, -6
 DEV_WAIT_TIMEOUT = 1
+DEV_SLOT_MISMATCH = 2
 STATIC_WS_BYTES = 8 * 1024 * 1024
 
 BF16, FP16, FP32 = 0, 1, 2

@@ -111,6 +111,10 @@ struct AttnCall {
   float* partial_out;  // non-null: emit merged partial rows instead of `out`
   int num_splits; void* ws; int64_t ws_bytes;
   int quantize_q; cudaStream_t stream;
+  // fused decode step (null new_k = plain attention)
+  const void* new_k = nullptr; const void* new_v = nullptr; int new_dtype = 0;
+  const int64_t* nk_st = nullptr; const int64_t* nv_st = nullptr;
+  const void* new_slots = nullptr; int new_slot_is_i64 = 0;
 };
 
 int run_attention(const AttnCall& a) {
@@ -173,6 +177,12 @@ int run_attention(const AttnCall& a) {
   const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
                      tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
                      (rf % 4 == 0);
+  if (a.new_k != nullptr && !(tiled && a.cache_kind == kCacheInt8)) return INT8KV_E_UNSUPPORTED;  // nothing launched yet
+  if (a.new_k != nullptr) {
+    p.new_k = a.new_k; p.new_v = a.new_v; p.new_dtype = a.new_dtype;
+    for (int i = 0; i < 3; ++i) { p.nk_st[i] = a.nk_st[i]; p.nv_st[i] = a.nv_st[i]; }
+    p.new_slots = a.new_slots; p.new_slot_is_i64 = a.new_slot_is_i64;
+  }
   int rc;
   if (tiled) {
     alignas(64) CUtensorMap tmK, tmV;
@@ -369,15 +379,28 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
                        const float* k_scale, const float* v_scale, void* out, int out_dtype,
                        const int64_t out_strides[3], int num_splits, void* workspace, int64_t workspace_bytes,
                        void* stream) {
-  const int rc = int8kv_cache_write(key, value, kv_dtype, batch, num_kv_heads, head_dim, key_strides, value_strides,
-                                    key_cache, value_cache, key_cache_strides, value_cache_strides, num_blocks,
-                                    block_size, slot_mapping, slot_is_i64, k_scale, v_scale, stream);
+  if (!key || !value || !slot_mapping || !key_strides || !value_strides) return batch == 0 ? INT8KV_OK : INT8KV_E_NULLPTR;
+  if (!valid_float_dtype(kv_dtype)) return INT8KV_E_BAD_DTYPE;
+  // Shapes the tiled kernel covers: one launch does both.  For any other shape run_attention refuses with
+  // INT8KV_E_UNSUPPORTED before launching anything, and the two-call form runs instead.
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             k_scale, v_scale, out, out_dtype, out_strides, nullptr,
+             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+  a.new_k = key; a.new_v = value; a.new_dtype = kv_dtype; a.nk_st = key_strides; a.nv_st = value_strides;
+  a.new_slots = slot_mapping; a.new_slot_is_i64 = slot_is_i64;
+  int rc = run_attention(a);
+  if (rc != INT8KV_E_UNSUPPORTED) return rc;
+  rc = int8kv_cache_write(key, value, kv_dtype, batch, num_kv_heads, head_dim, key_strides, value_strides,
+                          key_cache, value_cache, key_cache_strides, value_cache_strides, num_blocks,
+                          block_size, slot_mapping, slot_is_i64, k_scale, v_scale, stream);
   if (rc != INT8KV_OK) return rc;
   return int8kv_paged_attn_int8(query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, key_cache,
                                 value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
-                                block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
-                                k_scale, v_scale, out, out_dtype, out_strides, num_splits, workspace, workspace_bytes,
-                                0, stream);
+                                block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
+                                max_seq_len_hint, k_scale, v_scale, out, out_dtype, out_strides, num_splits,
+                                workspace, workspace_bytes, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

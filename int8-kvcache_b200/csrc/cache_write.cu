@@ -14,38 +14,6 @@
 
 namespace int8kv {
 
-// rint(x / scale) clamped to [-127, 127], bit-identical to IEEE division followed by round-half-even, at
-// the cost of a few full-rate FP32 instructions in the common case:
-//  * x * (1/scale) is within 2 ulp of the true quotient; its rounding to an integer can differ from that of
-//    the correctly rounded quotient only when the quotient is within a few ulp of a tie k + 0.5 (ulp <= 2^-17
-//    below 128), so exactly those elements — and anything huge, infinite or NaN — take the real division;
-//  * rounding uses the 1.5 * 2^23 trick (adding and subtracting it rounds to nearest-even in the FP32 adder,
-//    and the integer sits in the low mantissa bits), which keeps the work off the quarter-rate conversion unit.
-// Returns the integer still unclamped for |n| < 2^22; the caller saturates when packing.
-constexpr float kRoundMagic = 12582912.f;           // 1.5 * 2^23
-constexpr int kRoundMagicBits = 0x4B400000;
-
-__device__ __forceinline__ int quant1(float x, float scale, float rscale) {
-  float q = x * rscale;
-  float t = q + kRoundMagic;
-  const float n = t - kRoundMagic;
-  if (!(fabsf(q - n) < 0.5f - 6.2e-5f) || !(fabsf(q) < 4.0e6f)) {  // near a tie, beyond 2^22, infinite or NaN
-    q = x / scale;                          // div.rn.f32
-    q = fminf(fmaxf(q, -127.f), 127.f);     // also maps +-inf; NaN is handled below
-    t = q + kRoundMagic;
-    if (x != x) t = kRoundMagic;            // NaN -> 0, as a float-to-int8 cast of NaN gives on the CPU
-  }
-  return __float_as_int(t) - kRoundMagicBits;
-}
-
-// Four such integers saturated to int8 and packed little-endian; -128 is raised to -127.
-__device__ __forceinline__ uint32_t pack4_sat(int n0, int n1, int n2, int n3) {
-  uint32_t hi, w;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(n3), "r"(n2), "r"(0));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(n1), "r"(n0), "r"(hi));
-  return __vmaxs4(w, 0x81818181u);
-}
-
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

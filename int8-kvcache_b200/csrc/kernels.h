@@ -78,6 +78,14 @@ struct AttnParams {
   int quantize_q;
   float sm_scale_log2;   // log2(e) / sqrt(D)
   unsigned int* status;  // device status word, may be null
+  // fused decode step: the step's new K/V row of every sequence ([B, Hkv, D]) is quantised and written at
+  // new_slots[b] by the warp that owns the sequence's last tile, which also patches its staged copy of the tile
+  const void* new_k;  // null = plain attention
+  const void* new_v;
+  int new_dtype;
+  int64_t nk_st[3], nv_st[3];
+  const void* new_slots;
+  int new_slot_is_i64;
 };
 
 struct MergeParams {

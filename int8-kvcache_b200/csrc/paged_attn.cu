@@ -226,7 +226,7 @@ __device__ __forceinline__ void qk_tile(int (&s)[4], uint32_t kbase, const uint3
   for (int i = 0; i < 4; ++i) s[i] = (hi[i] << 8) + lo[i];
 }
 
-template <int NST>
+template <int NST, bool FUSED_WRITE>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
@@ -266,6 +266,26 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
+
+  // Fused decode step: the warp whose range ends with the sequence's last tile owns the step's new K/V row of
+  // this head.  Everything it needs is requested here, long before the tile arrives: the row (4 elements per
+  // lane), its slot, and the physical block of the last token.
+  const int last_rel = ((it.seq_len - 1) >> 4) - it.t0;  // ordinal of the last tile inside this range, if any
+  bool owns_new = false;
+  float nk[4], nv[4];
+  int64_t new_slot = -1, last_blk = -1;
+  if constexpr (FUSED_WRITE) {
+    owns_new = last_rel >= 0 && last_rel < it.t1 - it.t0;
+    if (owns_new) {
+      new_slot = load_index(p.new_slots, p.new_slot_is_i64, it.b);
+      last_blk = load_index(p.bt, p.bt_is_i64, it.b * p.bt_st[0] + ((it.seq_len - 1) / p.block_size) * p.bt_st[1]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        nk[e] = load_as_float(p.new_k, p.new_dtype, it.b * p.nk_st[0] + it.h * p.nk_st[1] + (4 * lane + e) * p.nk_st[2]);
+        nv[e] = load_as_float(p.new_v, p.new_dtype, it.b * p.nv_st[0] + it.h * p.nv_st[1] + (4 * lane + e) * p.nv_st[2]);
+      }
+    }
+  }
 
   const int n = it.t1 - it.t0;
   const int pre = n < NST ? n : NST;
@@ -351,6 +371,34 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       break;
     }
     const uint32_t sA = ring.stage(i), sB = ring.stage(i + 1);
+
+    if constexpr (FUSED_WRITE) {
+      if (owns_new && (last_rel == i || last_rel == i + 1)) {
+        // quantise the new row exactly as the cache-write kernel does, store it to the cache, and overwrite the
+        // row in the staged tile (TMA fetched the tile before this store, so the stage still holds the old bytes)
+        const float ks = fmaxf(__ldg(p.k_scale + it.h), 1e-6f), vsn = fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
+        const float rk = __frcp_rn(ks), rv = __frcp_rn(vsn);
+        const uint32_t kw = pack4_sat(quant1(nk[0], ks, rk), quant1(nk[1], ks, rk), quant1(nk[2], ks, rk), quant1(nk[3], ks, rk));
+        const uint32_t vw = pack4_sat(quant1(nv[0], vsn, rv), quant1(nv[1], vsn, rv), quant1(nv[2], vsn, rv), quant1(nv[3], vsn, rv));
+        const int64_t pos = it.seq_len - 1;
+        const int64_t expect = last_blk * p.block_size + pos % p.block_size;
+        if (new_slot >= 0 && new_slot < p.num_blocks * p.block_size) {
+          const int64_t blk = new_slot / p.block_size, off = new_slot - blk * p.block_size;
+          int8_t* kcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(p.kc));
+          int8_t* vcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(p.vc));
+          *reinterpret_cast<uint32_t*>(kcw + blk * p.kc_st[0] + off * p.kc_st[1] + it.h * p.kc_st[2] + 4 * lane) = kw;
+          *reinterpret_cast<uint32_t*>(vcw + blk * p.vc_st[0] + off * p.vc_st[1] + it.h * p.vc_st[2] + 4 * lane) = vw;
+          if (new_slot == expect) {
+            const uint32_t st = ring.stage(last_rel) + swz128(static_cast<int>(pos & 15), lane >> 2) + (lane & 3) * 4;
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st), "r"(kw) : "memory");
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st + 2048), "r"(vw) : "memory");
+          } else if (lane == 0 && p.status != nullptr) {
+            atomicOr(p.status, INT8KV_DEV_SLOT_MISMATCH);
+          }
+        }
+        __syncwarp();
+      }
+    }
 
     int ia[4], ib[4];
     qk_tile(ia, sA, koff, qh, ql, two_limbs);
@@ -926,8 +974,13 @@ template <int NST>
 static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                               cudaStream_t stream) {
   constexpr int smem_max = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
-  auto kernel = paged_attn_int8_kernel<NST>;
-  if (set_smem<10 + NST>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
+  const bool fused = p.new_k != nullptr;
+  auto kernel = fused ? paged_attn_int8_kernel<NST, true> : paged_attn_int8_kernel<NST, false>;
+  if (fused) {
+    if (set_smem<30 + NST>(paged_attn_int8_kernel<NST, true>, smem_max) != 0) return INT8KV_E_LAUNCH;
+  } else {
+    if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, false>, smem_max) != 0) return INT8KV_E_LAUNCH;
+  }
   const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);

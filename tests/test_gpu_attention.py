@@ -260,6 +260,50 @@ def test_decode_step_equals_write_then_attend(kv, workloads):
     _check(out, want)
     two = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale))
     assert torch.equal(out, two)
+    assert kv.device_status() == 0
+    # every split count, fp16 new rows, int32 slots, a padding row (slot -1: nothing written, attention unchanged)
+    for splits in (1, 2, 8):
+        kcd, vcd = kc0.to(dev), vc0.to(dev)
+        slots = case.slot_mapping[last].to(torch.int32)
+        slots[3] = -1
+        out = kv.int8_decode_step(case.query.to(dev), case.key[last].half().to(dev), case.value[last].half().to(dev),
+                                  kcd, vcd, slots.to(dev), case.block_tables.to(dev), case.seq_lens.to(dev),
+                                  case.k_scale.to(dev), case.v_scale.to(dev), max_seq_len=max(lens), num_splits=splits)
+        kc_e, vc_e = kc.clone(), vc.clone()
+        s3 = int(case.slot_mapping[last][3])
+        kc_e[s3 // 16, s3 % 16], vc_e[s3 // 16, s3 % 16] = kc0[s3 // 16, s3 % 16], vc0[s3 // 16, s3 % 16]
+        assert torch.equal(kcd.cpu(), kc_e) and torch.equal(vcd.cpu(), vc_e)
+        _check(out[:3], want[:3])
+    assert kv.device_status() == 0
+    # a slot that is not the last token's is written all the same, and reported
+    kcd, vcd = kc0.to(dev), vc0.to(dev)
+    wrong = case.slot_mapping[last].clone()
+    wrong[0] = int(case.slot_mapping[5])
+    kv.int8_decode_step(case.query.to(dev), case.key[last].to(dev), case.value[last].to(dev), kcd, vcd, wrong.to(dev),
+                        case.block_tables.to(dev), case.seq_lens.to(dev), case.k_scale.to(dev), case.v_scale.to(dev),
+                        max_seq_len=max(lens))
+    torch.cuda.synchronize()
+    s5 = int(case.slot_mapping[5])
+    q_last = oracle.static_quant_per_head(case.key[last][0:1], case.k_scale, head_axis=1)[0]
+    assert torch.equal(kcd.cpu()[s5 // 16, s5 % 16], q_last)
+    assert kv.device_status() == 2
+    # shapes outside the tiled kernel take the two-call form behind the same entry point
+    shape = workloads.LayerShape(8, 2, 64, 8)
+    lens2 = [33, 9]
+    c2 = workloads.make_decode_case(lens2, shape, seed=3)
+    k2 = torch.zeros(c2.num_blocks, 8, 2, 64, dtype=torch.int8)
+    v2 = torch.zeros_like(k2)
+    last2 = torch.tensor([32, 41])
+    keep2 = torch.ones(42, dtype=torch.bool)
+    keep2[last2] = False
+    oracle.cache_write(c2.key[keep2], c2.value[keep2], k2, v2, c2.slot_mapping[keep2], c2.k_scale, c2.v_scale)
+    k2d, v2d = k2.to(dev), v2.to(dev)
+    o2 = kv.int8_decode_step(c2.query.to(dev), c2.key[last2].to(dev), c2.value[last2].to(dev), k2d, v2d,
+                             c2.slot_mapping[last2].to(dev), c2.block_tables.to(dev), c2.seq_lens.to(dev),
+                             c2.k_scale.to(dev), c2.v_scale.to(dev), max_seq_len=33)
+    oracle.cache_write(c2.key[last2], c2.value[last2], k2, v2, c2.slot_mapping[last2], c2.k_scale, c2.v_scale)
+    assert torch.equal(k2d.cpu(), k2) and torch.equal(v2d.cpu(), v2)
+    _check(o2, oracle.int8_paged_attention_oracle(c2.query, k2, v2, c2.block_tables, lens2, c2.k_scale, c2.v_scale))
 
 
 def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
