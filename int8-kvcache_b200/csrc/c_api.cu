@@ -1,6 +1,7 @@
 // extern "C" entry points declared in include/int8kv_b200.h: argument validation, path selection
 // (TMA-tiled kernels vs the generic kernel), tensor-map construction, split-KV planning and launches.
 // Nothing here synchronises, allocates device memory or throws.
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstring>
@@ -78,23 +79,31 @@ int64_t ws_bytes(int B, int Hq, int D, int S) {
   return rows + 16;  // trailing 16 bytes hold the status word
 }
 
+static int64_t pow2_floor(int64_t x) {
+  int64_t p = 1;
+  while (p * 2 <= x) p *= 2;
+  return p;
+}
+
 int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
   (void)block_size;
   if (B <= 0 || Hkv <= 0 || max_seq <= 0) return 1;
   const int64_t tiles = (max_seq + 15) / 16;
   const int64_t items = static_cast<int64_t>(B) * Hkv;
-  // One warp serves one (sequence, kv head, split) and 12 warps are resident per SM.  Measured on B200: ragged
-  // batches balance best, and the tail of the last wave costs least, with about four waves of warps; short
-  // problems are latency-bound and want every SM busy even at 8 tiles (128 tokens) per split, below which the
-  // partial rows and their merge outweigh the gain.
-  const int64_t want = static_cast<int64_t>(sm_count) * 12 * 4;
-  int64_t s = (want + items - 1) / items;
-  const int64_t by_len = tiles / 8;
-  // powers of two measured best (C4-like ragged batch: 8 splits 0.87 of the HBM peak against 0.82 at 7)
-  int64_t pow2 = 1;
-  while (pow2 < s) pow2 *= 2;
-  s = pow2;
-  while (s > 1 && (s > by_len || s > kMaxSplits)) s /= 2;
+  // One warp serves one (sequence, kv head, split); 12 warps are resident per SM.  Two regimes, both measured on
+  // B200, powers of two throughout:
+  //  * small calls are bound by the latency chain of one warp, so the splits fill at most one resident wave of
+  //    warps, down to 2 tiles per part for short sequences (16 parts) and 8 tiles per part for long ones;
+  //  * large calls are bound by HBM, where ragged batches balance best with about four waves of warps, but a part
+  //    of fewer than 32 tiles would spend too much of its traffic on its partial rows.
+  const int64_t slots = static_cast<int64_t>(sm_count) * 12;
+  const int64_t by_latency = std::min<int64_t>(tiles / 2, std::max<int64_t>(16, tiles / 8));
+  int64_t s_fill = std::min(pow2_floor(std::max<int64_t>(1, slots / items)), pow2_floor(std::max<int64_t>(1, by_latency)));
+  int64_t s_bw = 1;
+  while (s_bw * items < slots * 4) s_bw *= 2;
+  s_bw = std::min(s_bw, pow2_floor(std::max<int64_t>(1, tiles / 32)));
+  int64_t s = std::max(s_fill, s_bw);
+  if (s > kMaxSplits) s = kMaxSplits;
   if (s < 1) s = 1;
   return static_cast<int>(s);
 }

@@ -61,23 +61,26 @@ def test_workspace_sizing(lib):
 def test_split_heuristic(lib):
     cap = lib.int8kv_max_splits()
     assert cap >= 16
+    pick = lambda B, H, seq: lib.int8kv_choose_splits(B, H, seq, 16, 148)
     # enough (sequence, head) pairs for four waves of warps on 148 SMs: no split
-    assert lib.int8kv_choose_splits(4096, 4, 8192, 16, 148) == 1
+    assert pick(4096, 4, 8192) == 1
     # a large ragged batch is still cut into a few parts per sequence for balance
-    assert 4 <= lib.int8kv_choose_splits(256, 4, 8192, 16, 148) <= 16
-    # short sequences are never split below 128 tokens per part
-    assert lib.int8kv_choose_splits(1, 4, 100, 16, 148) == 1
-    assert lib.int8kv_choose_splits(1, 4, 512, 16, 148) == 4
+    assert 4 <= pick(256, 4, 8192) <= 16
+    # ... unless the sequences are short: parts below 32 tiles would mostly move partial rows
+    assert pick(256, 4, 512) == 1
+    # small calls: one resident wave of warps, never fewer than 2 tiles (32 tokens) per part
+    assert pick(1, 4, 100) == 2
+    assert pick(1, 4, 512) == 16 and pick(8, 4, 512) == 16
+    assert pick(8, 4, 4096) == 32
     # long single sequence: many splits, bounded by the cap
-    s = lib.int8kv_choose_splits(1, 4, 65536, 16, 148)
-    assert 32 <= s <= cap
+    assert 32 <= pick(1, 4, 65536) <= cap
     for B in (1, 2, 4, 8):
         for seq in (512, 1024, 2048, 4096):
-            s = lib.int8kv_choose_splits(B, 4, seq, 16, 148)
-            assert 1 <= s <= max(1, seq // 128)
+            s = pick(B, 4, seq)
+            assert 1 <= s <= max(1, seq // 32) and (s & (s - 1)) == 0
     # monotone: more sequences never ask for more splits
-    assert lib.int8kv_choose_splits(8, 4, 4096, 16, 148) <= lib.int8kv_choose_splits(1, 4, 4096, 16, 148)
-    assert lib.int8kv_choose_splits(0, 4, 4096, 16, 148) == 1
+    assert pick(8, 4, 4096) <= pick(1, 4, 4096)
+    assert pick(0, 4, 4096) == 1
 
 
 def test_argument_validation_returns_codes_before_any_launch(lib):
