@@ -273,7 +273,7 @@ def bench_cache_write(kv, wl, device, args):
     print(json.dumps({
         "metric": "int8_kv_cache_write_achieved_hbm_gbps", "value": gbs, "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us * len(sets) / 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 -> int8 (fp32 quotient)",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "us_per_call": us, "gpu_launches": len(sets) * args.steps,
         "config": {"workload": "c3: prefill cache write, 16384 tokens x 4 heads x 128, permuted 1024-block pool, "
                                "~3% slots = -1, 8 rotated sets (larger than L2)"},
@@ -315,6 +315,7 @@ def main():
     metric = "int8_paged_decode_attn_achieved_hbm_gbps"
     config = {"workload": f"{args.workload}: {desc}", "Hq": hq, "Hkv": hkv, "head_dim": 128, "block_size": 16,
               "batch_per_gpu": len(seq_lens), "layers": layers,
+              "arithmetic": "int8 cache; QK^T on int8 tensor cores, PV in fp16 MMA, fp32 softmax and accumulation",
               "l2": "inputs larger than L2: each call reads a different layer's cache",
               "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"}
 
@@ -326,7 +327,7 @@ def main():
                                                         min_reps=max(1, args.steps), warm=max(0, args.warmup))
         line = {"impl": "reference", "metric": metric, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "int8 KV, fp32 math", "data": "synthetic",
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                 "config": config,
                 "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample_desc},
                 "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -543,7 +544,7 @@ def main():
         line = {
             "metric": metric, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 KV, fp16 tensor-core products, fp32 accumulate/softmax",
+            "vs_baseline": None, "dtype": "int8",
             "data": "synthetic", "config": config,
             "us_per_call": per_call_s * 1e6,
             "tokens_layers_per_s": world * B * layers / (ms_per_step * 1e-3),

@@ -210,6 +210,15 @@ int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64
 int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_q_heads, int head_dim,
                           void* out, int out_dtype, const int64_t out_strides[3], void* stream);
 
+/*
+ * Self-test of the failure path.  Every wait for staged data inside the kernels is bounded; when one runs out the
+ * kernel sets INT8KV_DEV_WAIT_TIMEOUT in the workspace's status word and returns.  This entry point launches one warp
+ * that waits, with at most `attempts` (1..65536) attempts of about a microsecond, for data that nothing sends, so a
+ * caller can check that the timeout is reported and the context stays usable.  No counterpart in the reference,
+ * which has no failure detection.
+ */
+int int8kv_selftest_bounded_wait(void* workspace, int64_t workspace_bytes, int attempts, void* stream);
+
 /* Floats per partial row: D for the output, one for the lse, padded to a multiple of 4. */
 int int8kv_partial_row_floats(int head_dim);
 

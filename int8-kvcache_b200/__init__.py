@@ -24,6 +24,7 @@ from .ops import (  # noqa: F401
     partial_row_floats,
     release_workspaces,
     reshape_and_cache_int8,
+    selftest_bounded_wait,
 )
 
 __all__ = [
@@ -37,4 +38,5 @@ __all__ = [
     "partial_row_floats",
     "device_status",
     "release_workspaces",
+    "selftest_bounded_wait",
 ]

@@ -78,6 +78,7 @@ _SIGNATURES = {
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
          C.c_int, _VP, C.c_int64, _VP],
     ),
+    "int8kv_selftest_bounded_wait": (C.c_int, [_VP, C.c_int64, C.c_int, _VP]),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),
 }
 

@@ -348,6 +348,14 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 
+int int8kv_selftest_bounded_wait(void* workspace, int64_t workspace_bytes, int attempts, void* stream) {
+  if (workspace == nullptr || workspace_bytes < 16) return INT8KV_E_WORKSPACE;
+  if (attempts <= 0 || attempts > (1 << 16)) return INT8KV_E_BAD_SHAPE;
+  unsigned int* status =
+      reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + int8kv_workspace_status_offset(workspace_bytes));
+  return launch_bounded_wait_selftest(status, static_cast<unsigned int>(attempts), static_cast<cudaStream_t>(stream));
+}
+
 int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype, int64_t num_tokens, int num_kv_heads,
                                int head_dim, const int64_t key_strides[3], const int64_t value_strides[3],
                                int8_t* key_cache, int8_t* value_cache, const int64_t key_cache_strides[4],

@@ -108,6 +108,7 @@ int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUt
                           cudaStream_t stream);
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
+int launch_bounded_wait_selftest(unsigned int* status, unsigned int attempts, cudaStream_t stream);
 
 // resident warps per SM the tiled int8 kernel is sized for (used by the split heuristic)
 constexpr int kTiledWarpsPerCta = 4;

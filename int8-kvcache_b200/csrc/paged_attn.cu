@@ -901,6 +901,29 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 }
 
 // ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait: one warp arms an mbarrier for bytes that no copy will ever deliver, waits with a
+// small attempt limit, and reports the timeout in the status word exactly as the attention kernels do.  It
+// returns normally; the context stays usable.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(unsigned int* status, unsigned int attempts) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t addr = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(addr, 1);
+    mbar_fence_init();
+    mbar_expect_tx(addr, 16);  // the phase now waits for 16 bytes that nothing sends
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_bounded(addr, 0, attempts);
+  if (!__all_sync(kFull, ok) && threadIdx.x == 0) atomicOr(status, INT8KV_DEV_WAIT_TIMEOUT);
+}
+
+int launch_bounded_wait_selftest(unsigned int* status, unsigned int attempts, cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, attempts);
+  return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
+
+// ---------------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------------
 constexpr int kInt8Stages = 4;

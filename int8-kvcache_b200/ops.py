@@ -65,6 +65,16 @@ def device_status(device=None) -> int:
     return value
 
 
+def selftest_bounded_wait(attempts: int = 200, device=None) -> int:
+    """Launch the library's bounded-wait self-test (a warp waits `attempts` times for data that never comes) and
+    return the status word afterwards: INT8KV_DEV_WAIT_TIMEOUT (1) is the expected answer.  Synchronises."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(device, 16)
+    rc = _require_lib().int8kv_selftest_bounded_wait(ws.data_ptr(), ws.numel(), int(attempts), _stream_ptr(device))
+    _lib.check("int8kv_selftest_bounded_wait", rc)
+    return device_status(device)
+
+
 def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 

@@ -390,3 +390,15 @@ def test_long_parts_and_sink_plus_crowd_distributions(kv, workloads):
         for splits in (1, None):
             _check(kv.int8_paged_attention(*args(q2), num_splits=splits), want2)
     assert kv.device_status() == 0
+
+
+def test_a_wait_that_cannot_finish_times_out_and_is_reported(kv, workloads):
+    """Failure detection without a GPU fault: the bounded wait runs out, the status word says so, and the
+    context keeps working."""
+    from conftest import package
+
+    assert kv.device_status() == 0
+    assert kv.selftest_bounded_wait(attempts=200) == package("_lib").DEV_WAIT_TIMEOUT
+    assert kv.device_status() == 0  # reading clears it
+    g = load_golden("attn_97_256")
+    _check(_run_int8(kv, g), g["out_chain_f32"], g["out_loop_bf16"])

@@ -115,3 +115,33 @@ def test_merge_of_partials_equals_unsplit():
         ])
         merged = oracle.merge_partials(torch.stack(outs), torch.stack(lses))
         assert max_abs(merged, full) < 2e-6
+
+
+def test_plain_c_quantiser_agrees_with_the_reference_vectors_and_the_torch_oracle():
+    """Two independent restatements (C with nearbyintf on a binary32 quotient, PyTorch) and the reference's own
+    outputs must give the same bytes, including ties, saturation and tiny scales."""
+    from oracle import quant_c
+
+    g = load_golden("write_t37")
+    assert torch.equal(quant_c.static_quant(g["key"], g["k_scale"]), g["key_q_static"][0].permute(1, 0, 2))
+    for name in ("write_t37", "write_n23", "attn_127_301"):
+        g = load_golden(name)
+        kc, vc = _fresh(g["key_cache"]), _fresh(g["value_cache"])
+        quant_c.cache_write(g["key"], g["k_scale"], kc, g["slot_mapping"])
+        quant_c.cache_write(g["value"], g["v_scale"], vc, g["slot_mapping"])
+        assert torch.equal(kc, g["key_cache"]) and torch.equal(vc, g["value_cache"])
+    r = load_golden("real_layer27")
+    k_tm = r["k"].permute(0, 2, 1, 3).reshape(40, 4, 128)
+    assert torch.equal(quant_c.static_quant(k_tm, r["k_scale"]), r["k_q"].permute(0, 2, 1, 3).reshape(40, 4, 128))
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(300, 4, 128, generator=gen) * 4
+    x[::9] = torch.round(x[::9] * 2) / 2  # exact halves: ties at scale 1 and 0.5
+    x[5] = 1e9
+    x[6] = -1e9
+    for scale in (torch.tensor([1.0, 0.5, 0.037, 1e-8]), torch.tensor([0.25, 2.0, 0.0123, 3.3])):
+        for dtype in (torch.float32, torch.bfloat16, torch.float16):
+            xs = x.to(dtype)
+            for floor in (False, True):
+                a = quant_c.static_quant(xs, scale, floor_scale=floor)
+                b = oracle.static_quant_per_head(xs, scale, head_axis=1, floor_scale=floor)
+                assert torch.equal(a, b)
