@@ -98,6 +98,7 @@ struct MergeParams {
   int out_dtype;
   int64_t o_st[3];
   float* part_out;  // [rows, row_floats] merged partial rows (out | lse), or null
+  int early_trigger;  // call griddepcontrol.launch_dependents right after the dependency wait
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
