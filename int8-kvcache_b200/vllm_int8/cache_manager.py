@@ -1,44 +1,37 @@
-"""Per-layer INT8 cache registry with the interface of the reference's vllm_int8/cache_manager.py:8-70:
-each layer owns zero-initialised int8 caches [num_blocks, block_size, Hkv, D] and its static scales."""
+"""Per-layer INT8 cache registry behind the interface of the reference's vllm_int8/cache_manager.py:8-70
+(`LayerInt8Cache`, `INT8_CACHE_POOL`, `has_layer_cache`, `get_layer_cache`, `allocate_layer_cache`,
+`clear_cache_pool`).  Every layer owns zero-initialised int8 caches [num_blocks, block_size, Hkv, D] — the
+layout both kernels read and write — and its static scales."""
 
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Dict
+from typing import Dict, NamedTuple
 
 import torch
 
 
-@dataclass
-class LayerInt8Cache:
+class LayerInt8Cache(NamedTuple):
     key_cache: torch.Tensor
     value_cache: torch.Tensor
     k_scale: torch.Tensor
     v_scale: torch.Tensor
 
 
-INT8_CACHE_POOL: Dict[str, LayerInt8Cache] = {}
+class _Pool(dict):
+    """layer name -> LayerInt8Cache"""
+
+    def allocate(self, layer_name: str, shape, k_scale, v_scale, device) -> LayerInt8Cache:
+        keys = torch.zeros(shape, dtype=torch.int8, device=device)
+        self[layer_name] = LayerInt8Cache(keys, torch.zeros_like(keys), k_scale, v_scale)
+        return self[layer_name]
 
 
-def has_layer_cache(layer_name: str) -> bool:
-    return layer_name in INT8_CACHE_POOL
+INT8_CACHE_POOL: Dict[str, LayerInt8Cache] = _Pool()
 
-
-def get_layer_cache(layer_name: str) -> LayerInt8Cache:
-    return INT8_CACHE_POOL[layer_name]
+has_layer_cache = INT8_CACHE_POOL.__contains__
+get_layer_cache = INT8_CACHE_POOL.__getitem__
+clear_cache_pool = INT8_CACHE_POOL.clear
 
 
 def allocate_layer_cache(*, layer_name, num_blocks, block_size, num_kv_heads, head_dim, k_scale, v_scale, device):
-    shape = (num_blocks, block_size, num_kv_heads, head_dim)
-    entry = LayerInt8Cache(
-        key_cache=torch.zeros(shape, dtype=torch.int8, device=device),
-        value_cache=torch.zeros(shape, dtype=torch.int8, device=device),
-        k_scale=k_scale,
-        v_scale=v_scale,
-    )
-    INT8_CACHE_POOL[layer_name] = entry
-    return entry
-
-
-def clear_cache_pool() -> None:
-    INT8_CACHE_POOL.clear()
+    return INT8_CACHE_POOL.allocate(layer_name, (num_blocks, block_size, num_kv_heads, head_dim), k_scale, v_scale, device)
