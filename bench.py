@@ -282,6 +282,51 @@ def bench_cache_write(kv, wl, device, args):
     }))
 
 
+def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens, config, metric):
+    """Long-context sequence split: rank r holds blocks [r*per, (r+1)*per) of every sequence in its own cache (all KV
+    heads); one step = partial attention over the local tokens, NCCL all-gather of the [B, Hq, D+4] fp32 partial
+    rows into local memory, local merge.  value = bytes of the whole context / max-over-ranks time."""
+    import torch.distributed as dist
+
+    sh = importlib.import_module("int8-kvcache_b200.sharding")
+    _, _, local_lens = sh.sequence_split(seq_lens, rank, world, 16)
+    layer = build_layers(kv, wl, device, hq, hkv, local_lens, 1, seed=300 + rank)[0]
+    max_local = max(local_lens)
+
+    def step():
+        return sh.sequence_parallel_int8_attention(layer.query, layer.kc, layer.vc, layer.block_tables, layer.seq_lens,
+                                                   layer.k_scale, layer.v_scale, max_seq_len=max_local)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(t.item())
+        nbytes = algorithmic_bytes(seq_lens, hq, hkv)
+        config["parallelism"] = (f"sequence split over {world} ranks ({max_local} tokens of every sequence per rank), "
+                                 "NCCL all-gather of partial rows + local merge")
+        config["batch_per_gpu"] = len(seq_lens)
+        print(json.dumps({
+            "metric": metric, "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config, "us_per_call": ms * 1e3,
+            "gpu_launches": 2 * args.steps,
+            "collective": {"op": "all_gather_into_tensor", "bytes_per_rank": len(seq_lens) * hq * 132 * 4},
+        }))
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -291,6 +336,11 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--num-splits", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: every rank runs the whole workload shape; strong: the workload is sharded by KV head "
+                         "and batch over the ranks (no collective)")
+    ap.add_argument("--seq-parallel", action="store_true",
+                    help="c5 only: split every sequence over the ranks; partial rows are all-gathered with NCCL and merged")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
     ap.add_argument("--no-bf16", dest="bf16_baseline", action="store_false", help="skip the same-run BF16 baseline")
@@ -347,6 +397,18 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
+    if args.seq_parallel:
+        return bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens, config, metric)
+    if args.scaling == "strong" and world > 1:
+        sh = importlib.import_module("int8-kvcache_b200.sharding")
+        shard = sh.head_batch_partition(world, hq, hkv, len(seq_lens))[rank]
+        group = hq // hkv
+        hkv = shard.kv_heads[1] - shard.kv_heads[0]
+        hq = hkv * group
+        seq_lens = seq_lens[shard.batch[0]:shard.batch[1]]
+        config["parallelism"] = (f"KV-head x batch sharded over {world} ranks, no collective: {hkv} KV head(s) x "
+                                 f"{len(seq_lens)} sequences per rank")
+        config["batch_per_gpu"] = len(seq_lens)
     layers_data = build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed=100 + rank)
     max_seq = max(seq_lens)
     B = len(seq_lens)
@@ -525,15 +587,18 @@ def main():
         clocks = sampler.stop() if rank == 0 else None
 
     times = torch.tensor([dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms], device=device, dtype=torch.float64)
+    total = torch.tensor([float(nbytes_step), float(B * layers)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+    total_step_bytes, total_token_layers = [float(x) for x in total.tolist()]
     dev_ms, e2e_ms, e2e_eager_ms, bf16_ms = [float(x) for x in times.tolist()]
     status = kv.device_status(device)
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
-        value = world * nbytes_step / (ms_per_step * 1e-3) / 1e9
-        e2e_value = world * nbytes_step / (e2e_ms / args.steps * 1e-3) / 1e9
+        value = total_step_bytes / (ms_per_step * 1e-3) / 1e9
+        e2e_value = total_step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
         peaks_path = REPO / "MEASURED_PEAKS.json"
         if peaks_path.exists():
             peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
@@ -543,11 +608,11 @@ def main():
         achieved = nbytes_call / per_call_s / 1e9
         line = {
             "metric": metric, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "int8",
             "data": "synthetic", "config": config,
             "us_per_call": per_call_s * 1e6,
-            "tokens_layers_per_s": world * B * layers / (ms_per_step * 1e-3),
+            "tokens_layers_per_s": total_token_layers / (ms_per_step * 1e-3),
             "frac_of_8TBps": value / world / HBM_NOMINAL_GBS,
             "num_splits": splits,
             "gpu_launches": launches_per_call * layers * args.steps,
@@ -556,7 +621,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps,
                     "eager_ms_per_step": e2e_eager_ms / args.steps,
-                    "eager_value": world * nbytes_step / (e2e_eager_ms / args.steps * 1e-3) / 1e9,
+                    "eager_value": total_step_bytes / (e2e_eager_ms / args.steps * 1e-3) / 1e9,
                     "what": "per step: one pinned-host buffer (all layers' new q/k/v rows, block tables, seq_lens, "
                             "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python operators, all "
                             "outputs -> pinned host, stream synchronised; `value` replays those calls as one CUDA "
