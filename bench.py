@@ -568,13 +568,27 @@ def main():
             barrier()
             return time.perf_counter() - t0
 
-        e2e_s = e2e_eager_s = float("nan")
+        e2e_s = e2e_eager_s = e2e_layers_s = float("nan")
         if not args.no_e2e:
             def eager_step():
                 e2e_enqueue()
                 stream.synchronize()
 
             e2e_eager_s = time_steps(eager_step)
+            # the same step through the L-layer entry point: one library call per step, arguments marshalled once
+            plan = kv.DecodeStepLayers([dv[i][0] for i in range(layers)], [dv[i][1] for i in range(layers)],
+                                       [dv[i][2] for i in range(layers)], [L.kc for L in layers_data],
+                                       [L.vc for L in layers_data], d_slots, d_bt, d_sl,
+                                       [L.k_scale for L in layers_data], [L.v_scale for L in layers_data],
+                                       num_splits=args.num_splits, max_seq_len=max_seq, out=d_out)
+
+            def layers_step():
+                d_in.copy_(h_in, non_blocking=True)
+                plan()
+                h_out.copy_(d_out, non_blocking=True)
+                stream.synchronize()
+
+            e2e_layers_s = time_steps(layers_step)
             g3 = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g3, stream=stream):
                 e2e_enqueue()
@@ -586,13 +600,14 @@ def main():
             e2e_s = time_steps(graph_step)
         clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms], device=device, dtype=torch.float64)
+    times = torch.tensor([dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms, e2e_layers_s * 1e3], device=device,
+                         dtype=torch.float64)
     total = torch.tensor([float(nbytes_step), float(B * layers)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(total, op=dist.ReduceOp.SUM)
     total_step_bytes, total_token_layers = [float(x) for x in total.tolist()]
-    dev_ms, e2e_ms, e2e_eager_ms, bf16_ms = [float(x) for x in times.tolist()]
+    dev_ms, e2e_ms, e2e_eager_ms, bf16_ms, e2e_layers_ms = [float(x) for x in times.tolist()]
     status = kv.device_status(device)
 
     if rank == 0:
@@ -622,10 +637,13 @@ def main():
                     "ms_per_step": e2e_ms / args.steps,
                     "eager_ms_per_step": e2e_eager_ms / args.steps,
                     "eager_value": total_step_bytes / (e2e_eager_ms / args.steps * 1e-3) / 1e9,
+                    "one_call_ms_per_step": e2e_layers_ms / args.steps,
+                    "one_call_value": total_step_bytes / (e2e_layers_ms / args.steps * 1e-3) / 1e9,
                     "what": "per step: one pinned-host buffer (all layers' new q/k/v rows, block tables, seq_lens, "
                             "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python operators, all "
                             "outputs -> pinned host, stream synchronised; `value` replays those calls as one CUDA "
-                            "graph, `eager_value` launches them from Python every step"},
+                            "graph, `eager_value` launches them from Python every step, `one_call_value` launches them "
+                            "every step through one int8kv_decode_step_layers call (no graph)"},
             "bf16_baseline": {"us_per_call": bf16_ms * 1e3 / layers, "int8_speedup": bf16_ms / ms_per_step,
                               "what": "bf16_paged_attention on un-quantised caches, same block tables, same graph "
                                       "replay timing"} if args.bf16_baseline else None,

@@ -168,6 +168,38 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
                        int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The decode step of `num_layers` layers in one call: int8kv_decode_step once per entry of `layers`, in order, on
+ * `stream`, sharing every shape, stride, table and the workspace.  It exists to pay the host cost of a call
+ * (argument marshalling of the binding, validation) once per model step instead of once per layer: the reference's
+ * microbenchmark and its vLLM hooks make 28 such calls per step for Qwen2.5-7B.  Per layer: query, output, the
+ * layer's cache pair and scales, and the step's new K/V rows (key == NULL: attention only, nothing is written, and
+ * slot_mapping may be NULL).  Stops at the first layer that fails and returns its status; *failed_layer (optional)
+ * then holds its index, else -1.
+ */
+typedef struct int8kv_layer_args {
+  const void* query;      /* [batch, Hq, D] */
+  void* out;              /* [batch, Hq, D] */
+  const void* key;        /* [batch, Hkv, D] new rows of this step, or NULL */
+  const void* value;
+  int8_t* key_cache;      /* [num_blocks, BS, Hkv, D] */
+  int8_t* value_cache;
+  const float* k_scale;   /* [Hkv] */
+  const float* v_scale;
+} int8kv_layer_args;
+
+int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer,
+                              int kv_dtype, const int64_t key_strides[3], const int64_t value_strides[3],
+                              const void* slot_mapping, int slot_is_i64,
+                              int q_dtype, const int64_t q_strides[3],
+                              int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                              int64_t num_blocks, int block_size,
+                              const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                              const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                              int out_dtype, const int64_t out_strides[3],
+                              int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * INT8 paged decode attention for callers that must not allocate device memory.  No counterpart in the
  * reference: there every call allocates its split-KV buffers with torch.empty.
  *

@@ -17,6 +17,8 @@ from .ops import (  # noqa: F401
     bf16_paged_attention,
     device_status,
     int8_decode_step,
+    int8_decode_step_layers,
+    DecodeStepLayers,
     int8_kv_cache_write,
     int8_paged_attention,
     int8_paged_attention_partial,
@@ -33,6 +35,8 @@ __all__ = [
     "bf16_paged_attention",
     "int8_paged_attention_partial",
     "int8_decode_step",
+    "int8_decode_step_layers",
+    "DecodeStepLayers",
     "reshape_and_cache_int8",
     "merge_partials",
     "partial_row_floats",

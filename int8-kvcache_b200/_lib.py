@@ -29,6 +29,16 @@ BF16, FP16, FP32 = 0, 1, 2
 _I64P = C.POINTER(C.c_int64)
 _VP = C.c_void_p
 
+
+class LayerArgs(C.Structure):
+    """int8kv_layer_args of include/int8kv_b200.h: the per-layer pointers of int8kv_decode_step_layers."""
+
+    _fields_ = [
+        ("query", _VP), ("out", _VP), ("key", _VP), ("value", _VP),
+        ("key_cache", _VP), ("value_cache", _VP), ("k_scale", _VP), ("v_scale", _VP),
+    ]
+
+
 _SIGNATURES = {
     "int8kv_abi_version": (C.c_int, []),
     "int8kv_status_str": (C.c_char_p, [C.c_int]),
@@ -76,6 +86,13 @@ _SIGNATURES = {
         [_VP, _VP, C.c_int, _I64P, _I64P, _VP, C.c_int,
          _VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
+         C.c_int, _VP, C.c_int64, _VP],
+    ),
+    "int8kv_decode_step_layers": (
+        C.c_int,
+        [C.POINTER(LayerArgs), C.c_int, C.POINTER(C.c_int), C.c_int, _I64P, _I64P, _VP, C.c_int, C.c_int, _I64P,
+         C.c_int, C.c_int, C.c_int, C.c_int, _I64P, _I64P, C.c_int64, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, C.c_int, _I64P,
          C.c_int, _VP, C.c_int64, _VP],
     ),
     "int8kv_selftest_bounded_wait": (C.c_int, [_VP, C.c_int64, C.c_int, _VP]),

@@ -420,6 +420,44 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
                                 workspace, workspace_bytes, 0, stream);
 }
 
+int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer, int kv_dtype,
+                              const int64_t key_strides[3], const int64_t value_strides[3],
+                              const void* slot_mapping, int slot_is_i64, int q_dtype, const int64_t q_strides[3],
+                              int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                              int64_t num_blocks, int block_size, const void* block_tables, int bt_is_i64,
+                              const int64_t bt_strides[2], int64_t bt_width, const void* seq_lens, int sl_is_i64,
+                              int64_t max_seq_len_hint, int out_dtype, const int64_t out_strides[3],
+                              int num_splits, void* workspace, int64_t workspace_bytes, void* stream) {
+  if (failed_layer) *failed_layer = -1;
+  if (num_layers < 0) return INT8KV_E_BAD_SHAPE;
+  if (num_layers == 0) return INT8KV_OK;
+  if (!layers) return INT8KV_E_NULLPTR;
+  for (int l = 0; l < num_layers; ++l) {
+    const int8kv_layer_args& L = layers[l];
+    int rc;
+    if (L.key != nullptr) {
+      rc = int8kv_decode_step(L.key, L.value, kv_dtype, key_strides, value_strides, slot_mapping, slot_is_i64,
+                              L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, L.key_cache,
+                              L.value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
+                              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+                              L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits, workspace,
+                              workspace_bytes, stream);
+    } else {
+      rc = int8kv_paged_attn_int8(L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+                                  L.key_cache, L.value_cache, key_cache_strides, value_cache_strides, num_blocks,
+                                  block_size, block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
+                                  max_seq_len_hint, L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits,
+                                  workspace, workspace_bytes, 0, stream);
+    }
+    if (rc != INT8KV_OK) {
+      if (failed_layer) *failed_layer = l;
+      return rc;
+    }
+  }
+  return INT8KV_OK;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Allocation-free variant: the split-KV workspace is a buffer inside the library image.
 // ---------------------------------------------------------------------------------------------------------

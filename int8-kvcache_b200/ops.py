@@ -11,6 +11,7 @@ PyTorch is used for device memory and streams only; all arithmetic happens in th
 
 from __future__ import annotations
 
+import ctypes as C
 import threading
 from typing import Dict, Optional, Tuple
 
@@ -402,6 +403,136 @@ def int8_decode_step(
     )
     _lib.check("int8kv_decode_step", rc)
     return out
+
+
+class DecodeStepLayers:
+    """The decode step of L layers behind ONE library call, with the arguments marshalled once.
+
+    A serving loop reuses the same buffers every step (the caches, and static input / output buffers exactly as
+    under CUDA-graph replay), so everything the binding needs — L pointer records, strides, table geometry, the
+    workspace — is fixed when this object is built; calling it costs one ctypes crossing and no per-layer Python.
+    Arguments as int8_decode_step_layers.  The tensors are kept alive by the object; their contents may change
+    between calls, their addresses may not."""
+
+    def __init__(self, queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens,
+                 k_scales, v_scales, *, max_seq_len: int, num_splits: Optional[int] = None,
+                 out: Optional[torch.Tensor] = None):
+        L = len(key_caches)
+        assert len(value_caches) == L and len(queries) == L and len(k_scales) == L and len(v_scales) == L
+        assert (keys is None) == (values is None)
+        fused = keys is not None
+        if fused:
+            assert len(keys) == L and len(values) == L and slot_mapping is not None
+        if out is None:
+            q0 = queries[0] if L else None
+            shape = (L,) + (tuple(q0.shape) if L else (0, 0, 0))
+            out = torch.empty(shape, device=block_tables.device, dtype=q0.dtype if L else torch.bfloat16)
+        else:
+            assert out.ndim == 4 and out.shape[0] == L and out.is_cuda and out.dtype in _FLOAT_CODES
+        self.out = out
+        self.num_layers = L
+        self._args = None
+        if L == 0:
+            return
+        q0, kc0, vc0 = queries[0], key_caches[0], value_caches[0]
+        B, Hq, Hkv, D, block_size = _check_decode_args(q0, kc0, vc0, block_tables, seq_lens)
+        assert out.shape[1:] == (B, Hq, D)
+        if B == 0:
+            return
+        lib = _require_lib()
+        if seq_lens.stride(0) != 1:
+            seq_lens = seq_lens.contiguous()
+        if fused:
+            assert slot_mapping.is_cuda and slot_mapping.ndim == 1 and slot_mapping.numel() == B
+            assert slot_mapping.dtype in (torch.int32, torch.int64)
+            if slot_mapping.stride(0) != 1:
+                slot_mapping = slot_mapping.contiguous()
+            k0, v0 = keys[0], values[0]
+            assert k0.shape == (B, Hkv, D) and v0.shape == k0.shape
+            assert k0.dtype in _FLOAT_CODES and v0.dtype == k0.dtype
+        keep = [queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens, out]
+        layers = (_lib.LayerArgs * L)()
+        for l in range(L):
+            q, kc, vc = queries[l], key_caches[l], value_caches[l]
+            assert q.is_cuda and q.shape == q0.shape and q.dtype == q0.dtype and q.stride() == q0.stride()
+            assert kc.dtype == torch.int8 and vc.dtype == torch.int8 and kc.is_cuda and vc.is_cuda
+            assert kc.shape == kc0.shape and vc.shape == kc0.shape
+            assert kc.stride() == kc0.stride() and vc.stride() == vc0.stride()
+            ks, vs = _as_f32_scale(k_scales[l]), _as_f32_scale(v_scales[l])
+            assert ks.is_cuda and vs.is_cuda and ks.numel() == Hkv and vs.numel() == Hkv
+            keep += [ks, vs]
+            assert out[l].stride() == out[0].stride()
+            a = layers[l]
+            a.query, a.out = q.data_ptr(), out[l].data_ptr()
+            a.key_cache, a.value_cache = kc.data_ptr(), vc.data_ptr()
+            a.k_scale, a.v_scale = ks.data_ptr(), vs.data_ptr()
+            if fused:
+                k, v = keys[l], values[l]
+                assert k.is_cuda and v.is_cuda and k.shape == k0.shape and v.shape == k0.shape
+                assert k.dtype == k0.dtype and v.dtype == k0.dtype
+                assert k.stride() == k0.stride() and v.stride() == v0.stride()
+                a.key, a.value = k.data_ptr(), v.data_ptr()
+        self._device = q0.device
+        splits, ws = _plan_workspace(lib, q0.device, B, Hq, Hkv, D, block_size, int(max_seq_len), num_splits)
+        self._ws_stream = torch.cuda.current_stream(q0.device).cuda_stream
+        keep.append(ws)
+        self._keep = keep
+        self._failed = C.c_int(-1)
+        zero3 = _lib.i64((0, 0, 0))
+        self._fn = lib.int8kv_decode_step_layers
+        self._args = (
+            layers, L, C.byref(self._failed),
+            _FLOAT_CODES[keys[0].dtype] if fused else 0,
+            _lib.i64(keys[0].stride()) if fused else zero3, _lib.i64(values[0].stride()) if fused else zero3,
+            slot_mapping.data_ptr() if fused else None, int(fused and slot_mapping.dtype == torch.int64),
+            _FLOAT_CODES[q0.dtype], _lib.i64(q0.stride()),
+            B, Hq, Hkv, D,
+            _lib.i64(kc0.stride()), _lib.i64(vc0.stride()),
+            kc0.shape[0], block_size,
+            block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+            _lib.i64(block_tables.stride()), block_tables.shape[1],
+            seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), int(max_seq_len),
+            _FLOAT_CODES[out.dtype], _lib.i64(out[0].stride()),
+            splits, ws.data_ptr(), ws.numel(),
+        )
+
+    def __call__(self) -> torch.Tensor:
+        """Enqueue the L layers on the current stream of the tensors' device and return `out` [L, B, Hq, D].
+        The split-KV workspace belongs to the stream that was current when the object was built: call it there."""
+        if self._args is None:
+            return self.out
+        stream = torch.cuda.current_stream(self._device).cuda_stream
+        assert stream == self._ws_stream, "DecodeStepLayers must run on the stream it was built on"
+        rc = self._fn(*self._args, stream)
+        if rc != _lib.OK:
+            raise _lib.Int8KVError(f"int8kv_decode_step_layers (layer {self._failed.value})", rc)
+        return self.out
+
+
+def int8_decode_step_layers(
+    queries,
+    keys,
+    values,
+    key_caches,
+    value_caches,
+    slot_mapping: Optional[torch.Tensor],
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    k_scales,
+    v_scales,
+    *,
+    max_seq_len: int,
+    num_splits: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """The decode step of L layers in one library call (one binding crossing per model step instead of one per
+    layer).  queries / keys / values: [L, B, ...] tensors or sequences of L same-shaped, same-strided tensors
+    (keys = values = None: attention only); key_caches / value_caches: sequences of L caches of one shape and
+    stride; k_scales / v_scales: [L, Hkv] or sequences of [Hkv].  Returns out [L, B, Hq, D].  Layer l computes
+    exactly what int8_decode_step (or int8_paged_attention) computes for its arguments.  A loop that reuses its
+    buffers should build a DecodeStepLayers once and call that instead."""
+    return DecodeStepLayers(queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens,
+                            k_scales, v_scales, max_seq_len=max_seq_len, num_splits=num_splits, out=out)()
 
 
 # ---------------------------------------------------------------------------------------------------

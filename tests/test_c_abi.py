@@ -104,6 +104,16 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert lib.int8kv_merge_partials(None, 2, 1, 28, 128, None, 0, st3, None) == _lib.E_NULLPTR
     assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 2, st4, st4, 4, 16, None, 0, st2, 4,
                                       None, 0, 64, None, 0, st3, 0, None, 0, None) == _lib.E_BAD_DTYPE
+    # the L-layer decode step: no layers is a no-op, a null array is refused, a failing layer is named
+    failed = C.c_int(7)
+    def layers_call(arr, n):
+        return lib.int8kv_decode_step_layers(arr, n, C.byref(failed), 0, st3, st3, None, 0, 0, st3, 1, 28, 4, 128, st4, st4,
+                                             4, 16, None, 0, st2, 4, None, 0, 64, 0, st3, 0, None, 0, None)
+    assert layers_call(None, 0) == _lib.OK and failed.value == -1
+    assert layers_call(None, -1) == _lib.E_BAD_SHAPE
+    assert layers_call(None, 2) == _lib.E_NULLPTR
+    arr = (_lib.LayerArgs * 2)()  # all-null per-layer pointers: the first layer fails its own null check
+    assert layers_call(arr, 2) == _lib.E_NULLPTR and failed.value == 0
 
 
 def test_error_type_carries_the_status(lib):

@@ -306,6 +306,58 @@ def test_decode_step_equals_write_then_attend(kv, workloads):
     _check(o2, oracle.int8_paged_attention_oracle(c2.query, k2, v2, c2.block_tables, lens2, c2.k_scale, c2.v_scale))
 
 
+def test_decode_step_layers_equals_per_layer_calls(kv, workloads):
+    """The L-layer entry point computes, layer by layer, exactly what L single-layer calls compute."""
+    lens = [513, 97, 1030, 16]
+    dev = "cuda"
+    L = 3
+    last = torch.tensor([sum(lens[: b + 1]) - 1 for b in range(len(lens))])
+    keep = torch.ones(sum(lens), dtype=torch.bool)
+    keep[last] = False
+    cases, full, start = [], [], []
+    c0 = workloads.make_decode_case(lens, workloads.QWEN25_7B, seed=40)
+    for l in range(L):  # every layer shares one block table and slot mapping, as in a model
+        case = workloads.make_decode_case(lens, workloads.QWEN25_7B, seed=40 + l)
+        kc = torch.zeros(c0.num_blocks, 16, 4, 128, dtype=torch.int8)
+        vc, kc0, vc0 = torch.zeros_like(kc), torch.zeros_like(kc), torch.zeros_like(kc)
+        oracle.cache_write(case.key, case.value, kc, vc, c0.slot_mapping, case.k_scale, case.v_scale)
+        oracle.cache_write(case.key[keep], case.value[keep], kc0, vc0, c0.slot_mapping[keep], case.k_scale, case.v_scale)
+        cases.append(case), full.append((kc, vc)), start.append((kc0, vc0))
+    bt, sl, slots = c0.block_tables.to(dev), c0.seq_lens.to(dev), c0.slot_mapping[last].to(dev)
+    queries = torch.stack([c.query for c in cases]).to(dev)
+    keys = torch.stack([c.key[last] for c in cases]).to(dev)
+    values = torch.stack([c.value[last] for c in cases]).to(dev)
+    kcs = [s[0].to(dev) for s in start]
+    vcs = [s[1].to(dev) for s in start]
+    kscales = torch.stack([c.k_scale for c in cases]).to(dev)
+    vscales = torch.stack([c.v_scale for c in cases]).to(dev)
+    out = kv.int8_decode_step_layers(queries, keys, values, kcs, vcs, slots, bt, sl, kscales, vscales, max_seq_len=max(lens))
+    assert out.shape == (L, len(lens), 28, 128)
+    for l in range(L):
+        assert torch.equal(kcs[l].cpu(), full[l][0]) and torch.equal(vcs[l].cpu(), full[l][1])
+        kcd, vcd = start[l][0].to(dev), start[l][1].to(dev)
+        one = kv.int8_decode_step(queries[l], keys[l], values[l], kcd, vcd, slots, bt, sl, kscales[l], vscales[l],
+                                  max_seq_len=max(lens))
+        assert torch.equal(out[l], one)
+        _check(out[l], oracle.int8_paged_attention_oracle(cases[l].query, full[l][0], full[l][1], c0.block_tables, lens,
+                                                          cases[l].k_scale, cases[l].v_scale))
+    # attention only (no new rows): lists of tensors, preallocated output, explicit split count
+    pre = torch.empty(L, len(lens), 28, 128, dtype=torch.bfloat16, device=dev)
+    got = kv.int8_decode_step_layers([q for q in queries], None, None, kcs, vcs, None, bt, sl, [k for k in kscales],
+                                     [v for v in vscales], max_seq_len=max(lens), num_splits=4, out=pre)
+    assert got is pre
+    for l in range(L):
+        one = kv.int8_paged_attention(queries[l], kcs[l], vcs[l], bt, sl, kscales[l], vscales[l], num_splits=4,
+                                      max_seq_len=max(lens))
+        assert torch.equal(pre[l], one)
+    assert kv.device_status() == 0
+    # a layer that fails is named
+    bad = [k for k in kcs]
+    bad[1] = kcs[1][:, :, :, :64]  # not the shape of layer 0
+    with pytest.raises(AssertionError):
+        kv.int8_decode_step_layers(queries, None, None, bad, vcs, None, bt, sl, kscales, vscales, max_seq_len=max(lens))
+
+
 def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
     """do_kv_cache_update -> INT8 mirror write, forward -> INT8 attention, through the patched methods of a fake
     attention-implementation class, in all three modes."""
