@@ -142,6 +142,26 @@ int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype,
                                const void* slot_mapping, int slot_is_i64, void* stream);
 
 /*
+ * INT8 paged decode attention over a cache written by int8kv_cache_write_dynamic: the K and V bytes of token t,
+ * head h dequantise with k_scale_cache / v_scale_cache [num_blocks, BS, Hkv] (fp32, any strides) instead of one
+ * static scale per head.  out = softmax(q . (K8 * ks)^T / sqrt(D)) . (V8 * vs), the attention of the cache that
+ * dequantize_int8_cache (vllm_int8/vllm_int8_cache_ops.py:250-277) reconstructs.  The reference stops at that
+ * write/dequantise pair and has no attention kernel for this scheme; this entry point is the reader that pairs
+ * with its writer.  Other arguments as int8kv_paged_attn_int8 (no quantize_q).
+ */
+int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t q_strides[3],
+                                   int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                                   const int8_t* key_cache, const int8_t* value_cache,
+                                   const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                                   const float* k_scale_cache, const float* v_scale_cache,
+                                   const int64_t k_scale_strides[3], const int64_t v_scale_strides[3],
+                                   int64_t num_blocks, int block_size,
+                                   const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                                   const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                                   void* out, int out_dtype, const int64_t out_strides[3],
+                                   int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * One decode step of one layer in a single call: the step's `batch` new K/V rows (one per sequence) are quantised
  * and written at slot_mapping, and query attends over the updated cache.  This is the pair of calls that the
  * reference's vLLM hooks make back to back for every layer (do_kv_cache_update then forward,

@@ -16,6 +16,7 @@ from . import _lib  # noqa: F401
 from .ops import (  # noqa: F401
     bf16_paged_attention,
     device_status,
+    int8_paged_attention_dynamic,
     int8_decode_step,
     int8_decode_step_layers,
     DecodeStepLayers,
@@ -34,6 +35,7 @@ __all__ = [
     "int8_paged_attention",
     "bf16_paged_attention",
     "int8_paged_attention_partial",
+    "int8_paged_attention_dynamic",
     "int8_decode_step",
     "int8_decode_step_layers",
     "DecodeStepLayers",

@@ -81,6 +81,12 @@ _SIGNATURES = {
         [_VP, _VP, C.c_int, C.c_int64, C.c_int, C.c_int, _I64P, _I64P, _VP, _VP, _I64P, _I64P, _VP, _VP, _I64P, _I64P,
          C.c_int64, C.c_int, _VP, C.c_int, _VP],
     ),
+    "int8kv_paged_attn_int8_dynamic": (
+        C.c_int,
+        [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, _VP, _VP, _I64P, _I64P,
+         C.c_int64, C.c_int, _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, C.c_int, _I64P,
+         C.c_int, _VP, C.c_int64, _VP],
+    ),
     "int8kv_decode_step": (
         C.c_int,
         [_VP, _VP, C.c_int, _I64P, _I64P, _VP, C.c_int,

@@ -124,6 +124,9 @@ struct AttnCall {
   const void* new_k = nullptr; const void* new_v = nullptr; int new_dtype = 0;
   const int64_t* nk_st = nullptr; const int64_t* nv_st = nullptr;
   const void* new_slots = nullptr; int new_slot_is_i64 = 0;
+  // dynamic per-(token, head) scales (null ks_cache = static scales)
+  const float* ks_cache = nullptr; const float* vs_cache = nullptr;
+  const int64_t* ks_st = nullptr; const int64_t* vs_st = nullptr;
 };
 
 int run_attention(const AttnCall& a) {
@@ -137,7 +140,10 @@ int run_attention(const AttnCall& a) {
   if (!a.query || !a.kc || !a.vc || !a.bt || !a.sl || !a.q_st || !a.kc_st || !a.vc_st || !a.bt_st)
     return INT8KV_E_NULLPTR;
   if (a.partial_out == nullptr && (!a.out || !a.o_st)) return INT8KV_E_NULLPTR;
-  if (a.cache_kind == kCacheInt8 && (!a.k_scale || !a.v_scale)) return INT8KV_E_NULLPTR;
+  const bool dyn = a.ks_cache != nullptr || a.vs_cache != nullptr;
+  if (dyn && (!a.ks_cache || !a.vs_cache || !a.ks_st || !a.vs_st)) return INT8KV_E_NULLPTR;
+  if (dyn && (a.cache_kind != kCacheInt8 || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
+  if (a.cache_kind == kCacheInt8 && !dyn && (!a.k_scale || !a.v_scale)) return INT8KV_E_NULLPTR;
   if (a.kc_st[3] != 1 || a.vc_st[3] != 1) return INT8KV_E_UNSUPPORTED;  // the reference asserts unit last stride too
 
   const int G = a.Hq / a.Hkv;
@@ -187,6 +193,10 @@ int run_attention(const AttnCall& a) {
                      tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
                      (rf % 4 == 0);
   if (a.new_k != nullptr && !(tiled && a.cache_kind == kCacheInt8)) return INT8KV_E_UNSUPPORTED;  // nothing launched yet
+  if (dyn) {
+    p.ks_cache = a.ks_cache; p.vs_cache = a.vs_cache;
+    for (int i = 0; i < 3; ++i) { p.ks_st[i] = a.ks_st[i]; p.vs_st[i] = a.vs_st[i]; }
+  }
   if (a.new_k != nullptr) {
     p.new_k = a.new_k; p.new_v = a.new_v; p.new_dtype = a.new_dtype;
     for (int i = 0; i < 3; ++i) { p.nk_st[i] = a.nk_st[i]; p.nv_st[i] = a.nv_st[i]; }
@@ -327,6 +337,26 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              k_scale, v_scale, nullptr, INT8KV_FP32, nullptr, partial,
              num_splits, workspace, workspace_bytes, quantize_q, static_cast<cudaStream_t>(stream)};
+  return run_attention(a);
+}
+
+int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t q_strides[3], int batch,
+                                   int num_q_heads, int num_kv_heads, int head_dim, const int8_t* key_cache,
+                                   const int8_t* value_cache, const int64_t key_cache_strides[4],
+                                   const int64_t value_cache_strides[4], const float* k_scale_cache,
+                                   const float* v_scale_cache, const int64_t k_scale_strides[3],
+                                   const int64_t v_scale_strides[3], int64_t num_blocks, int block_size,
+                                   const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                                   int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                                   void* out, int out_dtype, const int64_t out_strides[3], int num_splits,
+                                   void* workspace, int64_t workspace_bytes, void* stream) {
+  if (batch > 0 && (!k_scale_cache || !v_scale_cache || !k_scale_strides || !v_scale_strides)) return INT8KV_E_NULLPTR;
+  AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+             key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
+             block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+             nullptr, nullptr, out, out_dtype, out_strides, nullptr,
+             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+  a.ks_cache = k_scale_cache; a.vs_cache = v_scale_cache; a.ks_st = k_scale_strides; a.vs_st = v_scale_strides;
   return run_attention(a);
 }
 

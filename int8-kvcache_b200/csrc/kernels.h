@@ -86,6 +86,11 @@ struct AttnParams {
   int64_t nk_st[3], nv_st[3];
   const void* new_slots;
   int new_slot_is_i64;
+  // dynamic scales: one fp32 scale per (block, token-in-block, kv head) for K and for V (null = the static
+  // per-head k_scale / v_scale above)
+  const float* ks_cache;
+  const float* vs_cache;
+  int64_t ks_st[3], vs_st[3];
 };
 
 struct MergeParams {

@@ -40,7 +40,10 @@ constexpr int kTile = 16;  // tokens per tile
 // ---------------------------------------------------------------------------------------------
 // Per-warp TMA ring over the tiles [t0, t1) of one (sequence, kv head).
 // ---------------------------------------------------------------------------------------------
-template <int NST, int STAGE_BYTES, int LOADS_PER_TENSOR>
+// With DYN each stage also carries the tile's 16 K scales and 16 V scales (fp32, one per token) in a 128-byte
+// slot: every lane copies one of them with cp.async, whose completion arrives on the stage's mbarrier next to
+// the TMA bytes.
+template <int NST, int STAGE_BYTES, int LOADS_PER_TENSOR, bool DYN = false>
 struct TileRing {
   uint32_t stage0;  // shared address of stage 0 (1024-byte aligned)
   uint32_t bar0;    // shared address of the first mbarrier
@@ -57,6 +60,13 @@ struct TileRing {
   int cur_win;
   int bt_cur, bt_next;
   int lane;
+  // DYN only
+  uint32_t scale0;        // shared address of the first 128-byte scale slot
+  const float* sc_src;    // this lane's scale cache (lanes 0-15: K, 16-31: V), offset to the lane's head
+  int64_t sc_blk_stride;  // strides in elements of that cache: per block, per token
+  int64_t sc_tok_stride;
+  int64_t sc_blocks;      // number of blocks in the scale caches: ids outside are not read
+  int seq_len;
 
   __device__ __forceinline__ int load_window(int win) const {
     const int64_t lb = static_cast<int64_t>(lb0) + static_cast<int64_t>(win) * 32 + lane;
@@ -69,7 +79,7 @@ struct TileRing {
     lane = lane_;
     if (lane == 0) {
 #pragma unroll
-      for (int s = 0; s < NST; ++s) mbar_init(bar0 + 8 * s, 1);
+      for (int s = 0; s < NST; ++s) mbar_init(bar0 + 8 * s, DYN ? 1 + kWarp : 1);
       mbar_fence_init();
     }
     __syncwarp();
@@ -108,6 +118,14 @@ struct TileRing {
       bt_next = load_window(win + 1);
     }
     const int blk = __shfl_sync(kFull, bt_cur, idx & 31);
+    if constexpr (DYN) {
+      const int st = i % NST;
+      const int tok = lane & 15;
+      const bool live = blk >= 0 && blk < sc_blocks && tau * kTile + tok < seq_len;  // others get scale 0
+      const float* src = live ? sc_src + blk * sc_blk_stride + (sub * kTile + tok) * sc_tok_stride : sc_src;
+      cp_async_4(scale0 + st * 128 + lane * 4, src, live ? 4u : 0u);
+      cp_async_mbar_arrive_noinc(bar0 + 8 * st);
+    }
     if (lane == 0) {
       const int st = i % NST;
       const uint32_t bar = bar0 + 8 * st;
@@ -129,6 +147,7 @@ struct TileRing {
   }
 
   __device__ __forceinline__ uint32_t stage(int i) const { return stage0 + (i % NST) * STAGE_BYTES; }
+  __device__ __forceinline__ uint32_t scales(int i) const { return scale0 + (i % NST) * 128; }
 };
 
 struct ItemCoord {
@@ -230,11 +249,23 @@ __device__ __forceinline__ void qk_tile(int (&s)[4], uint32_t kbase, const uint3
   for (int i = 0; i < 4; ++i) s[i] = (hi[i] << 8) + lo[i];
 }
 
-template <int NST, bool FUSED_WRITE>
+// MODE: kPlain = static per-head scales; kFusedWrite = the same plus the decode step's cache write;
+// kDynScales = one scale per (token, head) read from scale caches beside the INT8 pages.
+constexpr int kPlain = 0, kFusedWrite = 1, kDynScales = 2;
+
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+
+template <int NST, int MODE>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
   static_assert(NST % 2 == 0, "tiles are consumed in pairs");
+  constexpr bool FUSED_WRITE = MODE == kFusedWrite;
+  constexpr bool DYN = MODE == kDynScales;
   constexpr int kStage = 4096;  // 16x128 K bytes + 16x128 V bytes
   extern __shared__ uint8_t smem_raw[];
   const int wpc = blockDim.x >> 5;  // warps per CTA: 1 for small grids (spread over all SMs), 4 otherwise
@@ -245,7 +276,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   if (!item_coords(p, static_cast<int64_t>(blockIdx.x) * wpc + warp, it)) return;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  TileRing<NST, kStage, 1> ring;
+  TileRing<NST, kStage, 1, DYN> ring;
   ring.stage0 = smem_base + warp * (NST * kStage);
   ring.bar0 = smem_base + wpc * NST * kStage + warp * (NST * 8);
   ring.tmK = &tmK;
@@ -256,6 +287,15 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   ring.bt_limit = p.bt_width;
   ring.tpb = p.tiles_per_block;
   ring.head = it.h;
+  if constexpr (DYN) {
+    ring.scale0 = smem_base + wpc * NST * (kStage + 8) + warp * (NST * 128);
+    const bool is_v = lane >= 16;
+    ring.sc_src = is_v ? p.vs_cache + it.h * p.vs_st[2] : p.ks_cache + it.h * p.ks_st[2];
+    ring.sc_blk_stride = is_v ? p.vs_st[0] : p.ks_st[0];
+    ring.sc_tok_stride = is_v ? p.vs_st[1] : p.ks_st[1];
+    ring.sc_blocks = p.num_blocks;
+    ring.seq_len = 0;
+  }
   if (lane == 0) {
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -274,6 +314,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
+  if constexpr (DYN) ring.seq_len = it.seq_len;
 
   // Fused decode step: the warp whose range ends with the sequence's last tile owns the step's new K/V row of
   // this head.  Everything it needs is requested here, long before the tile arrives: the row (4 elements per
@@ -352,7 +393,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     }
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
-  const float kmul = fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
+  const float kmul = DYN ? p.sm_scale_log2 : fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
   const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
   const float sc1 = kmul * __shfl_sync(kFull, q_mul, (2 * t + 1) * 4);
 
@@ -364,6 +405,11 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  // Dynamic V scales ride on P (p * v_scale[token]) into the fp16 MMA.  They are first multiplied by a power of
+  // two that brings the largest scale of the first 32 tokens into [1/4, 1/2), so that the products keep fp16
+  // precision whatever the magnitude of V; a later token whose scale is more than 2^11 times larger lowers the
+  // factor (and the accumulators with it), like a new row maximum in the softmax.  The epilogue divides it out.
+  float v_norm = 1.f, v_unnorm = 1.f;
 
   // Two tiles (32 tokens) per iteration: two independent score chains, one max reduction, one rescale test.
   // When the range holds an odd number of tiles the last pair's second tile is all-masked; its stage holds
@@ -426,6 +472,40 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       v[r] = static_cast<float>(ia[r]) * ((r & 1) ? sc1 : sc0);
       v[4 + r] = static_cast<float>(ib[r]) * ((r & 1) ? sc1 : sc0);
     }
+    float vsr[4] = {1.f, 1.f, 1.f, 1.f};  // V scales of rows g, g+8 (tile A), g, g+8 (tile B)
+    if constexpr (DYN) {
+      const uint32_t qa = ring.scales(i), qb = ring.scales(i + 1);
+      const float ka0 = lds32f(qa + g * 4), ka1 = lds32f(qa + (g + 8) * 4);
+      const float kb0 = second ? lds32f(qb + g * 4) : 0.f, kb1 = second ? lds32f(qb + (g + 8) * 4) : 0.f;
+      v[0] *= ka0; v[1] *= ka0; v[2] *= ka1; v[3] *= ka1;
+      v[4] *= kb0; v[5] *= kb0; v[6] *= kb1; v[7] *= kb1;
+      vsr[0] = lds32f(qa + 64 + g * 4);
+      vsr[1] = lds32f(qa + 64 + (g + 8) * 4);
+      vsr[2] = second ? lds32f(qb + 64 + g * 4) : 0.f;
+      vsr[3] = second ? lds32f(qb + 64 + (g + 8) * 4) : 0.f;
+      // (Re)normalise: at the first pair of tiles, and whenever a token's scale would push p * scale towards the
+      // top of the fp16 range; the accumulators follow by the same power of two.
+      float top = fmaxf(fmaxf(vsr[0], vsr[1]), fmaxf(vsr[2], vsr[3]));
+      if (i == 0 || __any_sync(kFull, top * v_norm > 1024.f)) {
+        top = fmaxf(top, __shfl_xor_sync(kFull, top, 4));
+        top = fmaxf(top, __shfl_xor_sync(kFull, top, 8));
+        top = fmaxf(top, __shfl_xor_sync(kFull, top, 16));
+        if (top > 0.f && top < INFINITY) {
+          int e = (__float_as_int(top) >> 23) & 0xff;  // biased exponent: top in [2^(e-127), 2^(e-126))
+          e = e < 24 ? 24 : (e > 230 ? 230 : e);
+          const float nn = __int_as_float((252 - e) << 23);  // 2^(125 - e): top * nn in [1/4, 1/2)
+          const float f = nn * v_unnorm;                     // new over old factor, an exact power of two
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[j][0] *= f; acc[j][1] *= f; acc[j][2] *= f; acc[j][3] *= f;
+          }
+          v_norm = nn;
+          v_unnorm = __int_as_float((e + 2) << 23);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) vsr[r] = fminf(vsr[r] * v_norm, 60000.f);
+    }
     if (tok0 >= it.seq_len) v[0] = v[1] = -INFINITY;
     if (tok0 + 8 >= it.seq_len) v[2] = v[3] = -INFINITY;
     if (!second || tok0 + 16 >= it.seq_len) v[4] = v[5] = -INFINITY;
@@ -455,6 +535,10 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     for (int r = 0; r < 8; ++r) pr[r] = exp2_fast(v[r] - ((r & 1) ? m1 : m0));
     l0 += (pr[0] + pr[2]) + (pr[4] + pr[6]);
     l1 += (pr[1] + pr[3]) + (pr[5] + pr[7]);
+    if constexpr (DYN) {
+#pragma unroll
+      for (int r = 0; r < 8; ++r) pr[r] *= vsr[r >> 1];
+    }
     // P^T as B operands: (tokens 2t,2t+1 | head g), (tokens 2t+8,2t+9 | head g) for each tile
     const uint32_t pa0 = movmatrix_trans(pack_half2(pr[0], pr[1]));
     const uint32_t pa1 = movmatrix_trans(pack_half2(pr[2], pr[3]));
@@ -485,7 +569,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   l1 += __shfl_xor_sync(kFull, l1, 8);
   l0 += __shfl_xor_sync(kFull, l0, 16);
   l1 += __shfl_xor_sync(kFull, l1, 16);
-  const float vs = fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
+  const float vs = DYN ? v_unnorm : fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int hg = 2 * t + e;
@@ -785,6 +869,11 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
     if (blk < 0 || blk >= p.num_blocks) continue;  // never read outside the cache
     const int64_t kof = blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
     const int64_t vof = blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
+    float kt = 1.f, vt = 1.f;  // per-token scales of the dynamic scheme
+    if (p.ks_cache != nullptr) {
+      kt = __ldg(p.ks_cache + blk * p.ks_st[0] + off * p.ks_st[1] + hkv * p.ks_st[2]);
+      vt = __ldg(p.vs_cache + blk * p.vs_st[0] + off * p.vs_st[1] + hkv * p.vs_st[2]);
+    }
     float dot = 0.f;
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
@@ -792,7 +881,7 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
       if (d < p.D) dot += q[s] * cache_elem(p.kc, p.cache_kind, kof + d * p.kc_st[3]);
     }
     for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(kFull, dot, o);
-    const float sv = dot * sc;
+    const float sv = dot * sc * kt;
     const float mn = fmaxf(m, sv);
     const float al = exp2f(m - mn);
     const float pe = exp2f(sv - mn);
@@ -800,7 +889,7 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
       const int d = lane + kWarp * s;
-      if (d < p.D) acc[s] = acc[s] * al + pe * cache_elem(p.vc, p.cache_kind, vof + d * p.vc_st[3]);
+      if (d < p.D) acc[s] = acc[s] * al + (pe * vt) * cache_elem(p.vc, p.cache_kind, vof + d * p.vc_st[3]);
     }
     m = mn;
   }
@@ -1012,11 +1101,11 @@ static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const
                               cudaStream_t stream) {
   constexpr int smem_max = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
   const bool fused = p.new_k != nullptr;
-  auto kernel = fused ? paged_attn_int8_kernel<NST, true> : paged_attn_int8_kernel<NST, false>;
+  auto kernel = fused ? paged_attn_int8_kernel<NST, kFusedWrite> : paged_attn_int8_kernel<NST, kPlain>;
   if (fused) {
-    if (set_smem<30 + NST>(paged_attn_int8_kernel<NST, true>, smem_max) != 0) return INT8KV_E_LAUNCH;
+    if (set_smem<30 + NST>(paged_attn_int8_kernel<NST, kFusedWrite>, smem_max) != 0) return INT8KV_E_LAUNCH;
   } else {
-    if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, false>, smem_max) != 0) return INT8KV_E_LAUNCH;
+    if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, kPlain>, smem_max) != 0) return INT8KV_E_LAUNCH;
   }
   const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
   if (items <= 0) return INT8KV_OK;
@@ -1025,8 +1114,23 @@ static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const
   return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
 }
 
+// Dynamic-scale variant: default ring depth only; each stage has a 128-byte scale slot beside it.
+static int launch_int8_dynamic(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                               cudaStream_t stream) {
+  constexpr int NST = kInt8Stages;
+  constexpr int per_warp = NST * (4096 + 8 + 128);
+  auto kernel = paged_attn_int8_kernel<NST, kDynScales>;
+  if (set_smem<50>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0) return INT8KV_E_LAUNCH;
+  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  if (items <= 0) return INT8KV_OK;
+  const int wpc = pick_wpc(items, sm_count);
+  const size_t smem = static_cast<size_t>(wpc) * per_warp + 1024;
+  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
+}
+
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                            cudaStream_t stream) {
+  if (p.ks_cache != nullptr) return launch_int8_dynamic(p, tmK, tmV, sm_count, stream);
   switch (tuning().stages) {
     case 2: return launch_int8_stages<2>(p, tmK, tmV, sm_count, stream);
     case 6: return launch_int8_stages<6>(p, tmK, tmV, sm_count, stream);

@@ -296,6 +296,57 @@ def int8_paged_attention(
     return out
 
 
+def int8_paged_attention_dynamic(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    k_scale_cache: torch.Tensor,
+    v_scale_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    num_splits: Optional[int] = None,
+    max_seq_len: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Decode attention over an INT8 paged cache whose scales are per (block, slot, head) — the caches that
+    reshape_and_cache_int8 fills (k_scale_cache / v_scale_cache [num_blocks, BS, Hkv] fp32).  Returns [B, Hq, D] in
+    query.dtype: the attention of `dequantize_int8_cache(key_cache, k_scale_cache)` and its V counterpart."""
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    assert k_scale_cache.is_cuda and v_scale_cache.is_cuda
+    assert k_scale_cache.dtype == torch.float32 and v_scale_cache.dtype == torch.float32
+    assert k_scale_cache.shape == key_cache.shape[:3] and v_scale_cache.shape == key_cache.shape[:3]
+    lib = _require_lib()
+    max_seq = _max_seq_len(seq_lens, block_tables, block_size, max_seq_len)
+    if out is None:
+        out = torch.empty((B, Hq, D), device=query.device, dtype=query.dtype)
+    else:
+        assert out.shape == (B, Hq, D) and out.dtype in _FLOAT_CODES and out.is_cuda
+    if B == 0:
+        return out
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, max_seq, num_splits)
+    rc = lib.int8kv_paged_attn_int8_dynamic(
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        k_scale_cache.data_ptr(), v_scale_cache.data_ptr(),
+        _lib.i64(k_scale_cache.stride()), _lib.i64(v_scale_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
+        out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
+        splits, ws.data_ptr(), ws.numel(),
+        _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_paged_attn_int8_dynamic", rc)
+    return out
+
+
 def bf16_paged_attention(
     query: torch.Tensor,
     key_cache: torch.Tensor,

@@ -1,13 +1,14 @@
 """Drop-in for the reference module vllm_int8/vllm_int8_cache_ops.py: `runtime_int8_cache_write` (:281-306, the
 static-scale write used by the attention path) and the dynamic per-(token, head) scheme with its helpers
 (`reshape_and_cache_int8` :134-210, `allocate_int8_kv_cache` :213-247, `dequantize_int8_cache` :250-256,
-`print_int8_cache_memory` :263-277)."""
+`print_int8_cache_memory` :263-277).  `int8_paged_attention_dynamic` is an addition: the decode attention that reads
+the caches and scale caches of the dynamic scheme, for which the reference has a writer and a debug dequantiser only."""
 
 from __future__ import annotations
 
 import torch
 
-from ..ops import int8_kv_cache_write, reshape_and_cache_int8  # noqa: F401
+from ..ops import int8_kv_cache_write, int8_paged_attention_dynamic, reshape_and_cache_int8  # noqa: F401
 
 
 def runtime_int8_cache_write(

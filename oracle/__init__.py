@@ -13,6 +13,7 @@ reference prototype cjsmt/Int8-kvcache:
   * slot_mapping scatter write                           src/triton_ops/int8_cache_write.py:152-183
   * fp32 decode attention with contiguous GQA groups     src/attention_ref.py:11-28
   * paged INT8 attention loop reference                  src/triton_ops/int8_paged_attention.py:776-814
+  * per-(slot, head) dequantisation                      vllm_int8/vllm_int8_cache_ops.py:250-256
   * split-KV partial merge                               src/triton_ops/int8_paged_attention.py:330-388
 
 Parity pin: every function here is checked against outputs of the reference's
@@ -37,6 +38,7 @@ from .attention_ref import (  # noqa: F401
     decode_attention,
     int8_paged_attention_oracle,
     float_paged_attention_oracle,
+    dynamic_int8_paged_attention_oracle,
     partial_attention_with_lse,
     merge_partials,
 )

@@ -89,3 +89,20 @@ def float_paged_attention_oracle(
     """Same attention on an un-quantised (bf16/fp16/fp32) paged cache; fp32 result."""
     ks, vs = gather_paged_cache(key_cache, value_cache, block_tables, seq_lens)
     return torch.stack([decode_attention(query[b], ks[b], vs[b]) for b in range(query.shape[0])])
+
+
+def dynamic_int8_paged_attention_oracle(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    k_scale_cache: torch.Tensor,
+    v_scale_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    seq_lens: Sequence[int],
+) -> torch.Tensor:
+    """[B, Hq, D] fp32 attention over an INT8 cache with one scale per (block, slot, head): the cache is first
+    dequantised as the reference's `dequantize_int8_cache` does (vllm_int8/vllm_int8_cache_ops.py:250-256,
+    `cache.float() * scale_cache[..., None]`), then attended with the fp32 reference attention."""
+    kf = key_cache.float() * k_scale_cache.float()[..., None]
+    vf = value_cache.float() * v_scale_cache.float()[..., None]
+    return float_paged_attention_oracle(query, kf, vf, block_tables, seq_lens)

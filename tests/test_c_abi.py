@@ -104,6 +104,12 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert lib.int8kv_merge_partials(None, 2, 1, 28, 128, None, 0, st3, None) == _lib.E_NULLPTR
     assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 2, st4, st4, 4, 16, None, 0, st2, 4,
                                       None, 0, 64, None, 0, st3, 0, None, 0, None) == _lib.E_BAD_DTYPE
+    # dynamic-scale attention: scale caches are required
+    def dyn(ksc, B=1):
+        return lib.int8kv_paged_attn_int8_dynamic(None, 0, st3, B, 28, 4, 128, None, None, st4, st4, ksc, None, st3, st3,
+                                                  4, 16, None, 0, st2, 4, None, 0, 64, None, 0, st3, 0, None, 0, None)
+    assert dyn(None) == _lib.E_NULLPTR
+    assert dyn(None, B=0) == _lib.OK
     # the L-layer decode step: no layers is a no-op, a null array is refused, a failing layer is named
     failed = C.c_int(7)
     def layers_call(arr, n):

@@ -358,6 +358,103 @@ def test_decode_step_layers_equals_per_layer_calls(kv, workloads):
         kv.int8_decode_step_layers(queries, None, None, bad, vcs, None, bt, sl, kscales, vscales, max_seq_len=max(lens))
 
 
+def _dynamic_case(workloads, lens, shape, seed, v_gain=None):
+    """A paged cache filled by the dynamic per-(token, head) scheme on the CPU (oracle arithmetic); unused slots
+    hold garbage bytes and NaN scales, which attention must never read into its result."""
+    case = workloads.make_decode_case(lens, shape, seed=seed)
+    value = case.value.float()
+    if v_gain is not None:
+        value = value * v_gain[:, None, None]
+    kq, ks = oracle.dynamic_quant_per_token_head(case.key)
+    vq, vs = oracle.dynamic_quant_per_token_head(value)
+    nb, bs, h, d = case.num_blocks, shape.block_size, shape.num_kv_heads, shape.head_dim
+    g = torch.Generator().manual_seed(seed + 99)
+    kc = torch.randint(-128, 128, (nb * bs, h, d), generator=g, dtype=torch.int8)
+    vc = torch.randint(-128, 128, (nb * bs, h, d), generator=g, dtype=torch.int8)
+    ksc = torch.full((nb * bs, h), float("nan"))
+    vsc = torch.full((nb * bs, h), float("nan"))
+    kc[case.slot_mapping], vc[case.slot_mapping] = kq, vq
+    ksc[case.slot_mapping], vsc[case.slot_mapping] = ks, vs
+    return case, kc.view(nb, bs, h, d), vc.view(nb, bs, h, d), ksc.view(nb, bs, h), vsc.view(nb, bs, h)
+
+
+def test_dynamic_scale_attention_tiled_path(kv, workloads):
+    """Attention over the per-(token, head) scale scheme equals the fp32 attention of the dequantised cache."""
+    lens = [513, 97, 1030, 16, 1, 31, 2048]
+    case, kc, vc, ksc, vsc = _dynamic_case(workloads, lens, workloads.QWEN25_7B, seed=21)
+    want = oracle.dynamic_int8_paged_attention_oracle(case.query, kc, vc, ksc, vsc, case.block_tables, lens)
+    assert torch.isfinite(want).all()
+    q, kcd, vcd, kscd, vscd, bt, sl = _dev(case.query, kc, vc, ksc, vsc, case.block_tables, case.seq_lens)
+    for splits in (None, 1, 2, 3, 8, 32):
+        out = kv.int8_paged_attention_dynamic(q, kcd, vcd, kscd, vscd, bt, sl, num_splits=splits)
+        _check(out, want)
+    # no host synchronisation with max_seq_len; fp32 query and output; int64 tables
+    out = kv.int8_paged_attention_dynamic(q.float(), kcd, vcd, kscd, vscd, bt.long(), sl.long(), max_seq_len=2048)
+    assert out.dtype == torch.float32
+    out = out.cpu()
+    assert max_abs(out, want) < 5e-3 and cosine(out, want) > 0.99999
+    assert kv.device_status() == 0
+
+
+def test_dynamic_scale_attention_wide_value_range(kv, workloads):
+    """Token scales that differ by orders of magnitude inside one sequence (tiny first tokens, huge later ones and
+    the reverse) keep their precision through the fp16 P.V product."""
+    lens = [700, 700, 64]
+    g = torch.Generator().manual_seed(5)
+    total = sum(lens)
+    for pattern in ("rising", "falling", "spiky"):
+        gain = torch.ones(total)
+        if pattern == "rising":
+            gain[:32], gain[700:732] = 1e-3, 1e-3
+            gain[400:700] = 300.0
+        elif pattern == "falling":
+            gain[:32] = 500.0
+            gain[32:700] = 1e-2
+        else:
+            gain[torch.randperm(total, generator=g)[:40]] = 2000.0
+        case, kc, vc, ksc, vsc = _dynamic_case(workloads, lens, workloads.QWEN25_7B, seed=22, v_gain=gain)
+        want = oracle.dynamic_int8_paged_attention_oracle(case.query, kc, vc, ksc, vsc, case.block_tables, lens)
+        q, kcd, vcd, kscd, vscd, bt, sl = _dev(case.query, kc, vc, ksc, vsc, case.block_tables, case.seq_lens)
+        for splits in (1, 4):
+            out = kv.int8_paged_attention_dynamic(q.float(), kcd, vcd, kscd, vscd, bt, sl, num_splits=splits).cpu()
+            scale = float(want.abs().max())
+            assert max_abs(out, want) < 2e-3 * scale, (pattern, splits, max_abs(out, want), scale)
+            assert cosine(out, want) > 0.9999
+    assert kv.device_status() == 0
+
+
+def test_dynamic_scale_attention_generic_path_and_write_chain(kv, workloads):
+    """Shapes outside the tiled kernel (D=64, BS=8, group 4), and the whole chain on the device:
+    reshape_and_cache_int8 writes the caches and scale caches that the attention then reads."""
+    from conftest import package
+
+    ops = package("vllm_int8.vllm_int8_cache_ops")
+    shape = workloads.LayerShape(8, 2, 64, 8)
+    lens = [33, 9, 70]
+    case, kc, vc, ksc, vsc = _dynamic_case(workloads, lens, shape, seed=23)
+    want = oracle.dynamic_int8_paged_attention_oracle(case.query, kc, vc, ksc, vsc, case.block_tables, lens)
+    q, kcd, vcd, kscd, vscd, bt, sl = _dev(case.query, kc, vc, ksc, vsc, case.block_tables, case.seq_lens)
+    for splits in (None, 1, 3):
+        _check(kv.int8_paged_attention_dynamic(q, kcd, vcd, kscd, vscd, bt, sl, num_splits=splits), want)
+    # device chain on the tiled shape
+    lens = [300, 77, 1]
+    c = workloads.make_decode_case(lens, workloads.QWEN25_7B, seed=24)
+    kc2, vc2, ks2, vs2 = ops.allocate_int8_kv_cache(c.num_blocks, 16, 4, 128, device="cuda")
+    ops.reshape_and_cache_int8(c.key.cuda(), c.value.cuda(), kc2, vc2, ks2, vs2, c.slot_mapping.cuda())
+    out = kv.int8_paged_attention_dynamic(c.query.cuda(), kc2, vc2, ks2, vs2, c.block_tables.cuda(), c.seq_lens.cuda())
+    want2 = oracle.dynamic_int8_paged_attention_oracle(c.query, kc2.cpu(), vc2.cpu(), ks2.cpu(), vs2.cpu(),
+                                                       c.block_tables, lens)
+    _check(out, want2)
+    # and it is close to the attention of the un-quantised K/V (the scheme's point): per-token scales beat 1e-2
+    kf = torch.zeros(c.num_blocks * 16, 4, 128)
+    vf = torch.zeros_like(kf)
+    kf[c.slot_mapping], vf[c.slot_mapping] = c.key.float(), c.value.float()
+    exact = oracle.float_paged_attention_oracle(c.query, kf.view(-1, 16, 4, 128), vf.view(-1, 16, 4, 128),
+                                                c.block_tables, lens)
+    assert max_abs(out.float().cpu(), exact) < 3e-2 and cosine(out.float().cpu(), exact) > 0.999
+    assert kv.device_status() == 0
+
+
 def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
     """do_kv_cache_update -> INT8 mirror write, forward -> INT8 attention, through the patched methods of a fake
     attention-implementation class, in all three modes."""
