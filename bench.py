@@ -327,6 +327,17 @@ def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens
     dist.destroy_process_group()
 
 
+def _without_nan(x):
+    """Legs that were skipped hold NaN; JSON has no NaN, so they become null."""
+    if isinstance(x, dict):
+        return {k: _without_nan(v) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return [_without_nan(v) for v in x]
+    if isinstance(x, float) and x != x:
+        return None
+    return x
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -345,6 +356,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
     ap.add_argument("--no-bf16", dest="bf16_baseline", action="store_false", help="skip the same-run BF16 baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--scales", default="static", choices=["static", "dynamic"],
+                    help="dynamic: time the attention over per-(token, head) scale caches (device leg only)")
     ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
     ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
     args = ap.parse_args()
@@ -413,12 +426,28 @@ def main():
     max_seq = max(seq_lens)
     B = len(seq_lens)
     nbytes_call = algorithmic_bytes(seq_lens, hq, hkv)
+    dynamic = args.scales == "dynamic"
+    if dynamic:
+        # one fp32 K scale and one fp32 V scale per (token, head) are read on top of the INT8 bytes
+        nbytes_call += sum(seq_lens) * hkv * 8
+        metric = "int8_dynamic_scale_paged_decode_attn_achieved_hbm_gbps"
+        config["scales"] = "per (token, head) fp32 scale caches [num_blocks, 16, Hkv], seeded uniform [0.005, 0.025]"
+        args.no_e2e, args.bf16_baseline, args.no_cpu = True, False, True
+        gen_s = torch.Generator(device=device)
+        for li, L in enumerate(layers_data):
+            gen_s.manual_seed(7000 + li)
+            L.ksc = torch.rand(L.kc.shape[:3], device=device, generator=gen_s) * 0.02 + 0.005
+            L.vsc = torch.rand(L.kc.shape[:3], device=device, generator=gen_s) * 0.02 + 0.005
     nbytes_step = nbytes_call * layers
 
     def device_step():
         for L in layers_data:
-            kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
-                                    num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
+            if dynamic:
+                kv.int8_paged_attention_dynamic(L.query, L.kc, L.vc, L.ksc, L.vsc, L.block_tables, L.seq_lens,
+                                                num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
+            else:
+                kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
 
     lib = kv._lib.load()
     sm = torch.cuda.get_device_properties(device).multi_processor_count
@@ -648,7 +677,8 @@ def main():
                               "what": "bf16_paged_attention on un-quantised caches, same block tables, same graph "
                                       "replay timing"} if args.bf16_baseline else None,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_DRAM_TRAFFIC_PER_LAUNCH.get(args.workload) if not (args.batch or args.layers) else None,
+                         "traffic": NCU_DRAM_TRAFFIC_PER_LAUNCH.get(args.workload)
+                         if not (args.batch or args.layers or dynamic) else None,
                          "peak_source": peak_src,
                          "kernel": "paged_attn_int8_kernel (+ merge_partials_kernel when split), per call inside the graph",
                          "algorithmic_bytes_per_call": nbytes_call},
@@ -657,7 +687,7 @@ def main():
             gbs, med, cores, sample_desc, _ = time_cpu(wl, hq, hkv, seq_lens, budget_s=args.cpu_seconds)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                                     "sample": sample_desc, "ms_per_call": med * 1e3}
-        print(json.dumps(line))
+        print(json.dumps(_without_nan(line)))
     if world > 1:
         dist.destroy_process_group()
 
