@@ -453,6 +453,7 @@ def main():
     sm = torch.cuda.get_device_properties(device).multi_processor_count
     splits = args.num_splits or lib.int8kv_choose_splits(B, hkv, max_seq, 16, sm)
     launches_per_call = 1 + (1 if splits > 1 else 0)
+    split_plan = None  # filled in after the warm-up when the library planned the parts on the device
 
     # warm up eagerly (kernel attribute set-up, workspace allocation), then capture one step as a CUDA graph
     stream = torch.cuda.Stream(device)
@@ -460,6 +461,11 @@ def main():
         for _ in range(2):
             device_step()
         stream.synchronize()
+        if args.num_splits is None:
+            plan = kv.last_split_plan(device)
+            if plan is not None:
+                split_plan = {"items": plan[0], "part_tiles": plan[1], "waves": plan[2]}
+                splits, launches_per_call = "planned on the device", 2
         if args.no_graph:
             class _Eager:
                 replay = staticmethod(device_step)
@@ -659,6 +665,7 @@ def main():
             "tokens_layers_per_s": total_token_layers / (ms_per_step * 1e-3),
             "frac_of_8TBps": value / world / HBM_NOMINAL_GBS,
             "num_splits": splits,
+            "split_plan": split_plan,
             "gpu_launches": launches_per_call * layers * args.steps,
             "clocks": clocks,
             "device_status": status,

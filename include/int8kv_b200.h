@@ -48,6 +48,10 @@ extern "C" {
 #define INT8KV_DEV_WAIT_TIMEOUT 1u /* a bounded wait for a staged page ran out; result invalid */
 #define INT8KV_DEV_SLOT_MISMATCH 2u /* int8kv_decode_step: a slot was not the slot of its sequence's last token */
 
+/* num_splits values with a special meaning (attention entry points) */
+#define INT8KV_SPLITS_AUTO 0      /* choose from the shape; large calls may plan their parts on the device */
+#define INT8KV_SPLITS_PLANNED (-1) /* always let the device-side plan choose (tiled shapes only) */
+
 int int8kv_abi_version(void);
 const char* int8kv_status_str(int status);
 
@@ -72,7 +76,10 @@ int int8kv_cache_write(const void* key, const void* value, int in_dtype,
  * INT8 paged decode attention.  Replaces int8_paged_attention with its V3/V4 kernels and the split-KV
  * merge (reference src/triton_ops/int8_paged_attention.py:68-769).  out[b,h,:] = softmax(q.K^T * k_scale/sqrt(D)) .
  * V * v_scale over the first seq_lens[b] tokens of sequence b.  A sequence with seq_len <= 0 yields zeros.
- *   num_splits  0 = choose from the shape (int8kv_choose_splits), >= 1 = use exactly that many KV splits
+ *   num_splits  0 = choose from the shape (int8kv_choose_splits; for large calls of up to 512 sequences the
+ *               kernel itself reads seq_lens and cuts every sequence into parts of one common length, chosen so
+ *               that all parts together fill a whole number of resident waves of warps, if the workspace has
+ *               int8kv_workspace_bytes_auto() bytes), -1 = always plan on the device, >= 1 = exactly that many
  *   max_seq_len_hint  upper bound of seq_lens used only to size the grid; <= 0 means width*BS
  *   workspace   required when the effective split count is > 1: int8kv_workspace_bytes() bytes
  *   quantize_q  non-zero: quantise each query head to INT8 (absmax/127, round half away from zero) before
@@ -276,6 +283,14 @@ int int8kv_partial_row_floats(int head_dim);
 
 /* Bytes of split-KV workspace for `num_splits` splits (includes the trailing status word). */
 int64_t int8kv_workspace_bytes(int batch, int num_q_heads, int head_dim, int num_splits);
+
+/* Bytes of workspace with which every automatic path (num_splits 0 or -1) of the attention entry points is
+ * available for this shape, the device-planned one included: partial rows of the items and the per-sequence
+ * table.  Never smaller than int8kv_workspace_bytes() for the split count int8kv_choose_splits() picks.
+ * A planned call leaves {items, part length in 16-token tiles, waves aimed for, 0} as four int32 in the 16 bytes
+ * before the status word. */
+int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t max_seq_len,
+                                    int block_size, int sm_count);
 
 /* Byte offset of the 32-bit device status word inside a workspace of `workspace_bytes` bytes. */
 int64_t int8kv_workspace_status_offset(int64_t workspace_bytes);

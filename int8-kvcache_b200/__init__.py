@@ -16,6 +16,7 @@ from . import _lib  # noqa: F401
 from .ops import (  # noqa: F401
     bf16_paged_attention,
     device_status,
+    last_split_plan,
     int8_paged_attention_dynamic,
     int8_decode_step,
     int8_decode_step_layers,
@@ -43,6 +44,7 @@ __all__ = [
     "merge_partials",
     "partial_row_floats",
     "device_status",
+    "last_split_plan",
     "release_workspaces",
     "selftest_bounded_wait",
 ]

@@ -23,6 +23,7 @@ E_NULLPTR, E_BAD_SHAPE, E_BAD_DTYPE, E_UNSUPPORTED, E_LAUNCH, E_WORKSPACE = -1, 
 DEV_WAIT_TIMEOUT = 1
 DEV_SLOT_MISMATCH = 2
 STATIC_WS_BYTES = 8 * 1024 * 1024
+SPLITS_AUTO, SPLITS_PLANNED = 0, -1
 
 BF16, FP16, FP32 = 0, 1, 2
 
@@ -44,6 +45,7 @@ _SIGNATURES = {
     "int8kv_status_str": (C.c_char_p, [C.c_int]),
     "int8kv_partial_row_floats": (C.c_int, [C.c_int]),
     "int8kv_workspace_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "int8kv_workspace_bytes_auto": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int]),
     "int8kv_workspace_status_offset": (C.c_int64, [C.c_int64]),
     "int8kv_choose_splits": (C.c_int, [C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int]),
     "int8kv_max_splits": (C.c_int, []),

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -108,6 +109,76 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   return static_cast<int>(s);
 }
 
+// ---- device-planned splits ----------------------------------------------------------------------------
+// Large calls (HBM-bound, up to a few resident waves of warps) choose the part length on the device from the
+// actual sequence lengths, so that the parts fill whole waves; see plan_in_warp.  INT8KV_PLAN=0 turns it off,
+// INT8KV_PLAN_MIN_TILES sets the shortest part the plan may choose when it aims for more than one wave.
+struct PlanShape {
+  int k_max;       // most waves the plan may aim for
+  int max_items;   // capacity of the item list = item numbers the attention launch covers
+  int min_part;
+};
+
+int env_int_or(const char* name, int fallback) {
+  const char* e = std::getenv(name);
+  return e ? std::atoi(e) : fallback;
+}
+
+// Whether the shape can be planned at all: every warp walks seq_lens a few times, which stays cheap up to a few
+// hundred sequences, and one part per (sequence, head) must fit one wave.
+constexpr int kPlanMaxBatch = 512;
+bool plan_possible(int B, int Hkv, int sm_count) {
+  return B <= kPlanMaxBatch && static_cast<int64_t>(B) * Hkv <= static_cast<int64_t>(sm_count) * 12;
+}
+
+// Whether planning pays: enough nominal work for one wave of parts of at least 12 tiles, and a split
+// heuristic that could not reach four waves of warps for this shape (with four or more waves the tail is small and
+// the plan's longer prologue, every warp reading seq_lens before its block table, costs more than it gains:
+// measured 222 us against 216 us per call on the 256-sequence ragged batch).
+bool plan_pays(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
+  static const int enabled = env_int_or("INT8KV_PLAN", 1);
+  if (!enabled || !plan_possible(B, Hkv, sm_count)) return false;
+  const int64_t slots = static_cast<int64_t>(sm_count) * 12;
+  const int64_t items = static_cast<int64_t>(B) * Hkv;
+  const int64_t tiles = (max_seq + 15) / 16;
+  if (items * tiles < slots * 12) return false;
+  return items * choose_splits(B, Hkv, max_seq, block_size, sm_count) < slots * 4;
+}
+
+PlanShape plan_shape(int B, int Hkv, int64_t tiles, int sm_count) {
+  static const int min_part = std::max(1, env_int_or("INT8KV_PLAN_MIN_TILES", 48));
+  const int64_t slots = static_cast<int64_t>(sm_count) * 12;
+  const int64_t items = static_cast<int64_t>(B) * Hkv;
+  PlanShape s{1, 0, min_part};
+  // the same rule the plan kernel applies, on the nominal lengths: the actual k can only be smaller
+  for (int k = 4; k >= 1; --k) {
+    const int64_t room = k * slots - items / 2;
+    if (room <= 0) continue;
+    const int64_t P = (items * tiles + room - 1) / room;
+    if (P >= min_part || k == 1) {
+      s.k_max = k;
+      break;
+    }
+  }
+  s.max_items = static_cast<int>(std::max<int64_t>(s.k_max * slots, items));
+  return s;
+}
+
+// Workspace of a planned call: partial rows (one per item and query head of its group), the sequence table,
+// then header and status word at the end.
+struct PlanLayout {
+  int64_t table_off, header_off, total;
+};
+PlanLayout plan_layout(int B, int Hq, int Hkv, int D, int max_items) {
+  const int G = Hq / Hkv;
+  PlanLayout l;
+  const int64_t rows = static_cast<int64_t>(max_items) * G * partial_row_floats(D) * 4;
+  l.table_off = (rows + 15) & ~int64_t(15);
+  l.header_off = (l.table_off + static_cast<int64_t>(B) * 8 + 15) & ~int64_t(15);  // earliest place for the header
+  l.total = l.header_off + 16 + 16;
+  return l;
+}
+
 struct AttnCall {
   const void* query; int q_dtype; const int64_t* q_st;
   int B, Hq, Hkv, D;
@@ -133,7 +204,7 @@ int run_attention(const AttnCall& a) {
   if (a.B < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.D <= 0 || a.block_size <= 0 || a.num_blocks < 0 || a.bt_width < 0)
     return INT8KV_E_BAD_SHAPE;
   if (a.Hq % a.Hkv != 0) return INT8KV_E_BAD_SHAPE;
-  if (a.num_splits < 0 || a.num_splits > kMaxSplits) return INT8KV_E_BAD_SHAPE;
+  if (a.num_splits < INT8KV_SPLITS_PLANNED || a.num_splits > kMaxSplits) return INT8KV_E_BAD_SHAPE;
   if (!valid_float_dtype(a.q_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.partial_out == nullptr && !valid_float_dtype(a.out_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.B == 0) return INT8KV_OK;
@@ -156,7 +227,31 @@ int run_attention(const AttnCall& a) {
   if (S > tiles) S = tiles > 0 ? static_cast<int>(tiles) : 1;
 
   const int rf = partial_row_floats(a.D);
-  const int64_t need = ws_bytes(a.B, a.Hq, a.D, S);
+  const int esz = a.cache_kind == kCacheInt8 ? 1 : 2;
+  const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
+                     tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
+                     (rf % 4 == 0);
+  // Device-planned splits: asked for explicitly, or chosen for a large automatic call when the workspace has
+  // room for the plan (callers that sized it with int8kv_workspace_bytes_auto always have).
+  bool planned = false;
+  PlanShape ps{};
+  PlanLayout pl{};
+  if (a.num_splits <= 0 && tiled && a.partial_out == nullptr && tiles > 0 &&
+      a.bt_width * a.block_size < (int64_t(1) << 21) * 16 &&  // tile counts stay exact in fp32 on the device
+      (a.num_splits == INT8KV_SPLITS_PLANNED ? plan_possible(a.B, a.Hkv, sm)
+                                              : plan_pays(a.B, a.Hkv, max_seq, a.block_size, sm))) {
+    ps = plan_shape(a.B, a.Hkv, tiles, sm);
+    pl = plan_layout(a.B, a.Hq, a.Hkv, a.D, ps.max_items);
+    // the plan's header sits in the 16 bytes before the status word, wherever the workspace ends
+    planned = a.ws != nullptr && a.ws_bytes >= pl.total && (reinterpret_cast<uintptr_t>(a.ws) & 15u) == 0 &&
+              pl.header_off + 16 <= int8kv_workspace_status_offset(a.ws_bytes);
+    if (planned) pl.header_off = int8kv_workspace_status_offset(a.ws_bytes) - 16;
+    if (!planned && a.num_splits == INT8KV_SPLITS_PLANNED) return INT8KV_E_WORKSPACE;
+  } else if (a.num_splits == INT8KV_SPLITS_PLANNED) {
+    return INT8KV_E_UNSUPPORTED;
+  }
+  if (planned) S = kMaxSplits;  // upper bound of the parts of one sequence; the real count is in the plan
+  const int64_t need = planned ? pl.total : ws_bytes(a.B, a.Hq, a.D, S);
   unsigned int* status = nullptr;
   if (a.ws != nullptr && a.ws_bytes >= 16)
     status = reinterpret_cast<unsigned int*>(static_cast<char*>(a.ws) + int8kv_workspace_status_offset(a.ws_bytes));
@@ -188,10 +283,6 @@ int run_attention(const AttnCall& a) {
   if (S > 1) p.part = reinterpret_cast<float*>(a.ws);
   else p.part = a.partial_out;  // null for the ordinary call: write `out` directly
 
-  const int esz = a.cache_kind == kCacheInt8 ? 1 : 2;
-  const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
-                     tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
-                     (rf % 4 == 0);
   if (a.new_k != nullptr && !(tiled && a.cache_kind == kCacheInt8)) return INT8KV_E_UNSUPPORTED;  // nothing launched yet
   if (dyn) {
     p.ks_cache = a.ks_cache; p.vs_cache = a.vs_cache;
@@ -203,6 +294,15 @@ int run_attention(const AttnCall& a) {
     p.new_slots = a.new_slots; p.new_slot_is_i64 = a.new_slot_is_i64;
   }
   int rc;
+  if (planned) {
+    char* base = static_cast<char*>(a.ws);
+    p.plan_table = reinterpret_cast<int2*>(base + pl.table_off);
+    p.plan_header = reinterpret_cast<int*>(base + pl.header_off);
+    p.plan_grid_items = ps.max_items;
+    p.plan_slots = sm * 12;
+    p.plan_k_max = ps.k_max;
+    p.plan_min_part = ps.min_part;
+  }
   if (tiled) {
     alignas(64) CUtensorMap tmK, tmV;
     if (!make_cache_map(&tmK, a.kc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.kc_st) ||
@@ -222,6 +322,7 @@ int run_attention(const AttnCall& a) {
   m.out = a.out; m.out_dtype = a.out_dtype;
   if (a.o_st) for (int i = 0; i < 3; ++i) m.o_st[i] = a.o_st[i];
   m.part_out = a.partial_out;
+  if (planned) m.seq_table = reinterpret_cast<const int2*>(static_cast<char*>(a.ws) + pl.table_off);
   return launch_merge(m, a.stream);
 }
 
@@ -249,6 +350,21 @@ int int8kv_partial_row_floats(int head_dim) { return partial_row_floats(head_dim
 int64_t int8kv_workspace_bytes(int batch, int num_q_heads, int head_dim, int num_splits) {
   if (batch < 0 || num_q_heads <= 0 || head_dim <= 0 || num_splits < 0) return -1;
   return ws_bytes(batch, num_q_heads, head_dim, num_splits);
+}
+
+int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t max_seq_len,
+                                    int block_size, int sm_count) {
+  if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || max_seq_len < 0 ||
+      num_q_heads % num_kv_heads != 0)
+    return -1;
+  const int sm = sm_count > 0 ? sm_count : 148;
+  const int64_t tiles = (max_seq_len + 15) / 16;
+  int64_t n = ws_bytes(batch, num_q_heads, head_dim, choose_splits(batch, num_kv_heads, max_seq_len, block_size, sm));
+  if (batch > 0 && tiles > 0 && plan_possible(batch, num_kv_heads, sm)) {
+    const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm);
+    n = std::max(n, plan_layout(batch, num_q_heads, num_kv_heads, head_dim, ps.max_items).total);
+  }
+  return n;
 }
 
 int64_t int8kv_workspace_status_offset(int64_t workspace_bytes) {

@@ -91,6 +91,14 @@ struct AttnParams {
   const float* ks_cache;
   const float* vs_cache;
   int64_t ks_st[3], vs_st[3];
+  // device-planned splits (plan_table != null): every warp derives the common part length from seq_lens and finds
+  // its own item, instead of numbering the items arithmetically from B, num_splits, Hkv; see plan_in_warp
+  int2* plan_table;     // [B] {row0, used}: written by the warp of (part 0, head 0), read by the merge kernel
+  int* plan_header;     // {items, part length in tiles, waves, 0}, written by item 0
+  int plan_grid_items;  // item numbers the launch covers (>= the items of any plan it can choose)
+  int plan_slots;       // resident warps of the kernel on the device
+  int plan_k_max;       // most waves to aim for
+  int plan_min_part;    // shortest part (tiles) the plan may choose when it aims for more than one wave
 };
 
 struct MergeParams {
@@ -103,6 +111,7 @@ struct MergeParams {
   int out_dtype;
   int64_t o_st[3];
   float* part_out;  // [rows, row_floats] merged partial rows (out | lse), or null
+  const int2* seq_table;  // device-planned splits: parts of row (b, hq) are rows (row0 + c) * Hq + hq, c < used
   int early_trigger;  // call griddepcontrol.launch_dependents right after the dependency wait
 };
 

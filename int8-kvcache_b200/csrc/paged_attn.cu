@@ -192,17 +192,153 @@ __device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   it.t1 = it.c < used ? min(it.t0 + per, ntiles) : it.t0;
 }
 
+// Device-planned splits.  Every sequence is cut into parts of one common length P (in 16-token tiles), the smallest
+// for which the parts of all sequences, W(P) = Hkv * sum_b max(1, ceil(tiles_b / P)), fit k resident waves of
+// warps, for the largest k <= plan_k_max whose parts are still plan_min_part tiles long.  P comes from the actual
+// lengths, so a ragged batch fills its waves as exactly as a batch of equal lengths.  There is no planning kernel
+// and no item list: every warp reads seq_lens (B values, L1-resident after the first pass), computes the same P
+// with the same integer arithmetic, and locates its own item in the order (sequence, part, kv head).  Returns
+// false for an item number past the end.  row0 = first partial row of the item's query-head group, or -1 when
+// the sequence has a single part and the result goes straight to `out`.
+// Length of sequence b clamped to what its table row can address (the host admits a plan only when that bound
+// is below 2^25 tokens).
+__device__ __forceinline__ int plan_len(const AttnParams& p, int b, int cap) {
+  if (p.sl_is_i64) {
+    const long long v = __ldg(reinterpret_cast<const long long*>(p.sl) + b);
+    return v > cap ? cap : (v < 0 ? 0 : static_cast<int>(v));
+  }
+  return min(max(__ldg(reinterpret_cast<const int*>(p.sl) + b), 0), cap);
+}
+
+// Parts of a sequence of `len` tokens cut into parts of P tiles: max(1, ceil(tiles / P)), 0 for len < 0 (no
+// sequence).  No integer division: tiles + P < 2^22 is exact in fp32, rP and the product are rounded down, so the
+// product can only fall short of the quotient, and by less than one.
+__device__ __forceinline__ int plan_parts(int len, int P, float rP) {
+  if (len < 0) return 0;
+  const int n = ((len + kTile - 1) >> 4) + P - 1;
+  int q = __float2int_rz(__fmul_rd(__int2float_rz(n), rP));
+  if ((q + 1) * P <= n) ++q;
+  return q < 1 ? 1 : q;
+}
+
+constexpr int kPlanRun = 16;  // sequences per lane: a plan covers up to 32 * 16 sequences
+constexpr int kPlanShortestPart = 8;
+
+__device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, int lane, ItemCoord& it, int64_t& row0) {
+  // lane l holds the lengths of sequences [l * run, (l + 1) * run) in registers; every pass below works on them
+  const int cap = static_cast<int>(p.bt_width * p.block_size);
+  const int run = (p.B + kWarp - 1) / kWarp;
+  const int b_lo = lane * run;
+  int len[kPlanRun];
+#pragma unroll
+  for (int j = 0; j < kPlanRun; ++j) {
+    len[j] = -1;
+    if (j < run && b_lo + j < p.B) len[j] = plan_len(p, b_lo + j, cap);
+  }
+  long long total = 0;
+  int longest = 0;
+#pragma unroll
+  for (int j = 0; j < kPlanRun; ++j) {
+    if (j >= run) break;
+    const int t = len[j] < 0 ? 0 : (len[j] + kTile - 1) >> 4;
+    total += t;
+    longest = max(longest, t);
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    total += __shfl_xor_sync(kFull, total, o);
+    longest = max(longest, __shfl_xor_sync(kFull, longest, o));
+  }
+  // estimate from W(P) ~ Hkv * (total / P + B / 2), then correct with the exact count
+  const long long work = total * p.Hkv;
+  const int floor_p = max(1, (longest + kMaxSplits - 1) / kMaxSplits);  // at most kMaxSplits parts per sequence
+  int k = p.plan_k_max < 1 ? 1 : p.plan_k_max;
+  int P = 1;
+  for (; k >= 1; --k) {
+    const long long room = static_cast<long long>(k) * p.plan_slots - static_cast<long long>(p.Hkv) * p.B / 2;
+    if (room <= 0) continue;
+    P = static_cast<int>((work + room - 1) / room);
+    if (P >= p.plan_min_part || k == 1) break;
+  }
+  if (k < 1) k = 1;
+  P = max(max(P, floor_p), kPlanShortestPart);  // below 8 tiles a part is mostly prologue and partial rows
+  const long long target = min(static_cast<long long>(k) * p.plan_slots, static_cast<long long>(p.plan_grid_items));
+  float rP = 1.f;
+  int mine = 0, upto = 0;
+  for (int round = 0; round < 64; ++round) {
+    rP = __frcp_rd(__int2float_rz(P));
+    mine = 0;
+#pragma unroll
+    for (int j = 0; j < kPlanRun; ++j) {
+      if (j >= run) break;
+      mine += plan_parts(len[j], P, rP);
+    }
+    upto = mine;  // inclusive scan over the lanes: lane 31 ends up with the number of parts
+    for (int o = 1; o < kWarp; o <<= 1) {
+      const int v = __shfl_up_sync(kFull, upto, o);
+      if (lane >= o) upto += v;
+    }
+    const int parts = __shfl_sync(kFull, upto, kWarp - 1);
+    // one part per sequence always fits: the launch covers at least B * Hkv items
+    if (static_cast<long long>(parts) * p.Hkv <= target || P >= longest) break;
+    P += round < 16 ? max(1, P >> 4) : P;
+  }
+  const int all_parts = __shfl_sync(kFull, upto, kWarp - 1);
+  const long long count = static_cast<long long>(all_parts) * p.Hkv;
+  if (item == 0 && lane == 0 && p.plan_header != nullptr) {
+    p.plan_header[0] = static_cast<int>(count);
+    p.plan_header[1] = P;
+    p.plan_header[2] = k;
+    p.plan_header[3] = 0;
+  }
+  if (item >= count) return false;
+
+  // the item in the order (sequence, part, kv head): its part index falls into exactly one lane's run
+  const int part = static_cast<int>(item / p.Hkv);
+  it.h = static_cast<int>(item - static_cast<int64_t>(part) * p.Hkv);
+  const bool owner = part >= upto - mine && part < upto;
+  int fb = 0, fc = 0, fused = 1, flen = 0;
+  if (owner) {
+    int first = upto - mine;
+#pragma unroll
+    for (int j = 0; j < kPlanRun; ++j) {
+      if (j >= run) break;
+      const int u = plan_parts(len[j], P, rP);
+      if (part >= first && part < first + u) {
+        fb = b_lo + j; fc = part - first; fused = u; flen = len[j];
+      }
+      first += u;
+    }
+  }
+  const int src = __ffs(__ballot_sync(kFull, owner)) - 1;
+  it.b = __shfl_sync(kFull, fb, src);
+  it.c = __shfl_sync(kFull, fc, src);
+  const int used = __shfl_sync(kFull, fused, src);
+  it.seq_len = __shfl_sync(kFull, flen, src);
+  const int tiles = (it.seq_len + kTile - 1) >> 4;
+  const int per = (tiles + used - 1) / used;
+  it.t0 = min(it.c * per, tiles);
+  it.t1 = min(it.t0 + per, tiles);
+  row0 = used == 1 ? -1 : static_cast<int64_t>(part) * p.Hq + it.h * p.G;
+  if (it.c == 0 && it.h == 0 && lane == 0) p.plan_table[it.b] = make_int2(part, used);
+  return true;
+}
+
+// First partial row of the item's query-head group when items are numbered arithmetically.
+__device__ __forceinline__ int64_t arithmetic_row0(const AttnParams& p, const ItemCoord& it) {
+  if (p.part == nullptr) return -1;
+  return (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + it.h * p.G;
+}
+
 // Result of an empty tile range: zeros to `out` (direct mode) or lse = -inf (partial mode).
-__device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord& it, int lane) {
-  if (p.part == nullptr) {
+__device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord& it, int lane, int64_t row0) {
+  if (row0 < 0) {
     for (int hg = 0; hg < p.G; ++hg) {
       const int hq = it.h * p.G + hg;
       for (int d = lane; d < p.D; d += kWarp)
         store_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], 0.f);
     }
   } else if (lane < p.G) {
-    const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + it.h * p.G + lane;
-    p.part[row * p.row_floats + p.D] = -INFINITY;
+    p.part[(row0 + lane) * p.row_floats + p.D] = -INFINITY;
   }
 }
 
@@ -273,7 +409,13 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const int g = lane >> 2, t = lane & 3;
 
   ItemCoord it;
-  if (!item_coords(p, static_cast<int64_t>(blockIdx.x) * wpc + warp, it)) return;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
+  const bool planned = p.plan_table != nullptr;
+  if (planned) {
+    if (item >= p.plan_grid_items) return;
+  } else if (!item_coords(p, item, it)) {
+    return;
+  }
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   TileRing<NST, kStage, 1, DYN> ring;
@@ -281,18 +423,14 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   ring.bar0 = smem_base + wpc * NST * kStage + warp * (NST * 8);
   ring.tmK = &tmK;
   ring.tmV = &tmV;
-  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.bt_is_i64 = p.bt_is_i64;
   ring.bt_stride = p.bt_st[1];
   ring.bt_limit = p.bt_width;
   ring.tpb = p.tiles_per_block;
-  ring.head = it.h;
   if constexpr (DYN) {
     ring.scale0 = smem_base + wpc * NST * (kStage + 8) + warp * (NST * 128);
-    const bool is_v = lane >= 16;
-    ring.sc_src = is_v ? p.vs_cache + it.h * p.vs_st[2] : p.ks_cache + it.h * p.ks_st[2];
-    ring.sc_blk_stride = is_v ? p.vs_st[0] : p.ks_st[0];
-    ring.sc_tok_stride = is_v ? p.vs_st[1] : p.ks_st[1];
+    ring.sc_blk_stride = lane >= 16 ? p.vs_st[0] : p.ks_st[0];
+    ring.sc_tok_stride = lane >= 16 ? p.vs_st[1] : p.ks_st[1];
     ring.sc_blocks = p.num_blocks;
     ring.seq_len = 0;
   }
@@ -307,10 +445,22 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   // Only now may the next kernel in the stream be scheduled (it waits for this grid before it reads): triggering
   // before the wait would let a whole chain of future kernels pile up on the SMs.
   grid_launch_dependents();
-  ring.prefetch_tables(guessed_first_block(p, it.c));
-  item_range(p, it);
+  int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
+  if (planned) {
+    if (!plan_in_warp(p, item, lane, it, row0)) return;
+  }
+  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
+  ring.head = it.h;
+  if constexpr (DYN) ring.sc_src = lane >= 16 ? p.vs_cache + it.h * p.vs_st[2] : p.ks_cache + it.h * p.ks_st[2];
+  if (planned) {
+    ring.prefetch_tables(it.t0 / p.tiles_per_block);
+  } else {
+    ring.prefetch_tables(guessed_first_block(p, it.c));
+    item_range(p, it);
+    row0 = arithmetic_row0(p, it);
+  }
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
-    write_empty(p, it, lane);
+    write_empty(p, it, lane, row0);
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
@@ -584,10 +734,10 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       o[2 * j] = acc[j][e] * inv;
       o[2 * j + 1] = acc[j][e + 2] * inv;
     }
-    if (p.part == nullptr) {
+    if (row0 < 0) {
       store16_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + 16 * g * p.o_st[2], p.o_st[2], o);
     } else {
-      const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + hq;
+      const int64_t row = row0 + hg;
       float4* dst = reinterpret_cast<float4*>(p.part + row * p.row_floats + 16 * g);
 #pragma unroll
       for (int d = 0; d < 4; ++d) dst[d] = make_float4(o[4 * d], o[4 * d + 1], o[4 * d + 2], o[4 * d + 3]);
@@ -620,7 +770,13 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   const int g = lane >> 2, t = lane & 3;
 
   ItemCoord it;
-  if (!item_coords(p, static_cast<int64_t>(blockIdx.x) * wpc + warp, it)) return;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
+  const bool planned = p.plan_table != nullptr;
+  if (planned) {
+    if (item >= p.plan_grid_items) return;
+  } else if (!item_coords(p, item, it)) {
+    return;
+  }
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   TileRing<NST, kStage, 2> ring;
@@ -628,12 +784,10 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   ring.bar0 = smem_base + wpc * NST * kStage + warp * (NST * 8);
   ring.tmK = &tmK;
   ring.tmV = &tmV;
-  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.bt_is_i64 = p.bt_is_i64;
   ring.bt_stride = p.bt_st[1];
   ring.bt_limit = p.bt_width;
   ring.tpb = p.tiles_per_block;
-  ring.head = it.h;
   if (lane == 0) {
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
@@ -645,10 +799,21 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   // Only now may the next kernel in the stream be scheduled (it waits for this grid before it reads): triggering
   // before the wait would let a whole chain of future kernels pile up on the SMs.
   grid_launch_dependents();
-  ring.prefetch_tables(guessed_first_block(p, it.c));
-  item_range(p, it);
+  int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
+  if (planned) {
+    if (!plan_in_warp(p, item, lane, it, row0)) return;
+  }
+  ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
+  ring.head = it.h;
+  if (planned) {
+    ring.prefetch_tables(it.t0 / p.tiles_per_block);
+  } else {
+    ring.prefetch_tables(guessed_first_block(p, it.c));
+    item_range(p, it);
+    row0 = arithmetic_row0(p, it);
+  }
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
-    write_empty(p, it, lane);
+    write_empty(p, it, lane, row0);
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
@@ -782,7 +947,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const float l = e ? l1 : l0;
     const float m = e ? m1 : m0;
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    if (p.part == nullptr) {
+    if (row0 < 0) {
       const int64_t base = it.b * p.o_st[0] + hq * p.o_st[1];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -790,7 +955,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         store_from_float(p.out, p.out_dtype, base + (16 * j + g + 8) * p.o_st[2], acc[j][e + 2] * inv);
       }
     } else {
-      const int64_t row = (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + hq;
+      const int64_t row = row0 + hg;
       float* dst = p.part + row * p.row_floats;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -920,13 +1085,24 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   __shared__ float top_s[kMergeWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = blockIdx.x;
-  const int64_t stride_r = p.rows * p.row_floats;
+  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row % p.Hq);
+  int64_t stride_r = p.rows * p.row_floats;
   const float* base = p.parts + row * p.row_floats;
+  int R = p.R;
 
   grid_dependency_wait();    // the partial rows come from the attention kernel launched just before
   if (p.early_trigger) grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before reading
+  if (p.seq_table != nullptr) {
+    // device-planned splits: this sequence's parts are consecutive part indices; a single part was written to
+    // `out` by the attention kernel itself
+    const int2 e = __ldg(p.seq_table + b);
+    if (e.y <= 1) return;
+    R = e.y < kMaxSplits ? e.y : kMaxSplits;
+    stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
+    base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
+  }
   float lse = -INFINITY;
-  if (static_cast<int>(threadIdx.x) < p.R) lse = base[threadIdx.x * stride_r + p.D];  // R <= kMaxSplits = blockDim
+  if (static_cast<int>(threadIdx.x) < R) lse = base[threadIdx.x * stride_r + p.D];  // R <= kMaxSplits = blockDim
   // The first batch of rows is requested before the weights exist, so that both reads share one latency.
   // Rows of empty parts were never written: whatever they hold is discarded by the weight test below.
   float4 pre[4];
@@ -934,35 +1110,34 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   for (int u = 0; u < 4; ++u) {
     const int r = warp + u * kMergeWarps;
     pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < p.R && 4 * lane < p.D) pre[u] = *reinterpret_cast<const float4*>(base + r * stride_r + 4 * lane);
+    if (r < R && 4 * lane < p.D) pre[u] = *reinterpret_cast<const float4*>(base + r * stride_r + 4 * lane);
   }
   float top = lse;
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
   if (lane == 0) top_s[warp] = top;
   __syncthreads();
   top = fmaxf(fmaxf(top_s[0], top_s[1]), fmaxf(top_s[2], top_s[3]));
-  if (static_cast<int>(threadIdx.x) < p.R) w_s[threadIdx.x] = lse == -INFINITY ? 0.f : __expf(lse - top);
+  if (static_cast<int>(threadIdx.x) < R) w_s[threadIdx.x] = lse == -INFINITY ? 0.f : __expf(lse - top);
   __syncthreads();
   float den = 0.f;
-  for (int r = lane; r < p.R; r += kWarp) den += w_s[r];
+  for (int r = lane; r < R; r += kWarp) den += w_s[r];
   for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(kFull, den, o);
   const float inv = den > 0.f ? 1.f / den : 0.f;
-  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row % p.Hq);
 
   for (int d0 = 0; d0 < p.D; d0 += 4 * kWarp) {
     const int d = d0 + 4 * lane;
     const bool live = d < p.D;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r0 = warp; r0 < p.R; r0 += 4 * kMergeWarps) {
+    for (int r0 = warp; r0 < R; r0 += 4 * kMergeWarps) {
       float w[4];
       float4 o[4];
       const bool have = d0 == 0 && r0 == warp;  // this batch was prefetched
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int r = r0 + u * kMergeWarps;
-        w[u] = r < p.R ? w_s[r] : 0.f;
+        w[u] = r < R ? w_s[r] : 0.f;
         o[u] = pre[u];
-        if (!have && live && r < p.R && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
+        if (!have && live && r < R && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -1089,6 +1264,12 @@ static int launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, s
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
 
+// Item numbers a tiled launch covers: the capacity of the planned list, or B * num_splits * Hkv.
+static int64_t grid_items(const AttnParams& p) {
+  if (p.plan_table != nullptr) return p.plan_grid_items;
+  return static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+}
+
 // Warps per CTA: a grid that cannot fill the machine with 4-warp CTAs is launched as 1-warp CTAs so that its
 // warps spread over all SMs instead of stacking four to an SM.
 static int pick_wpc(int64_t items, int sm_count) {
@@ -1107,7 +1288,7 @@ static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const
   } else {
     if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, kPlain>, smem_max) != 0) return INT8KV_E_LAUNCH;
   }
-  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * NST * 4096 + wpc * NST * 8 + 1024;
@@ -1121,7 +1302,7 @@ static int launch_int8_dynamic(const AttnParams& p, const CUtensorMap& tmK, cons
   constexpr int per_warp = NST * (4096 + 8 + 128);
   auto kernel = paged_attn_int8_kernel<NST, kDynScales>;
   if (set_smem<50>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0) return INT8KV_E_LAUNCH;
-  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * per_warp + 1024;
@@ -1145,7 +1326,7 @@ static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtenso
   constexpr int smem_max = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
   auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16>;
   if (set_smem<IS_BF16 ? 1 : 2>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
-  const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * kF16Stages * 8192 + wpc * kF16Stages * 8 + 1024;

@@ -224,15 +224,44 @@ def _max_seq_len(seq_lens, block_tables, block_size, max_seq_len, validate=True)
     return hi
 
 
+_SM_COUNT: Dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _SM_COUNT.get(idx)
+    if n is None:
+        n = _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
 def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits):
-    if num_splits is None:
-        sm = torch.cuda.get_device_properties(device).multi_processor_count
-        splits = lib.int8kv_choose_splits(B, Hkv, max_seq, block_size, sm)
+    """(split argument for the library, workspace).  num_splits None = automatic (the library picks a count from the
+    shape or, for large calls, plans the parts on the device from seq_lens), "planned" = always plan on the
+    device, an int = exactly that many."""
+    if num_splits is None or num_splits == "planned":
+        splits = _lib.SPLITS_AUTO if num_splits is None else _lib.SPLITS_PLANNED
+        nbytes = lib.int8kv_workspace_bytes_auto(B, Hq, Hkv, D, max_seq, block_size, _sm_count(device))
     else:
         splits = max(1, min(int(num_splits), lib.int8kv_max_splits()))
-    nbytes = lib.int8kv_workspace_bytes(B, Hq, D, splits)
+        nbytes = lib.int8kv_workspace_bytes(B, Hq, D, splits)
     ws = _workspace(device, nbytes)
     return splits, ws
+
+
+def last_split_plan(device=None):
+    """(items, part length in 16-token tiles, waves aimed for) that the most recent device-planned call on the
+    current stream of `device` left in its workspace, or None if no plan was written there.  Synchronises."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    with _WS_LOCK:
+        buf = _WS.get(key)
+    if buf is None:
+        return None
+    off = _require_lib().int8kv_workspace_status_offset(buf.numel()) - 16
+    items, part, waves, _ = buf[off:off + 16].view(torch.int32).tolist()
+    return (items, part, waves) if items > 0 else None
 
 
 def int8_paged_attention(

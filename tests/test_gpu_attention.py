@@ -358,6 +358,94 @@ def test_decode_step_layers_equals_per_layer_calls(kv, workloads):
         kv.int8_decode_step_layers(queries, None, None, bad, vcs, None, bt, sl, kscales, vscales, max_seq_len=max(lens))
 
 
+def test_device_planned_splits(kv, workloads):
+    """num_splits="planned": the kernel reads seq_lens and cuts the sequences into parts of one common length that
+    fill whole waves of warps; every operator that takes the tiled path accepts it."""
+    lens = [513, 97, 1030, 16, 1, 31, 2048, 300]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=31)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    q, kcd, vcd, bt, sl, ks, vs = _dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    kv.release_workspaces()
+    assert kv.last_split_plan() is None
+    out = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits="planned")
+    _check(out, want)
+    items, part, waves = kv.last_split_plan()
+    tiles = [(n + 15) // 16 for n in lens]
+    assert waves >= 1 and part >= 8
+    assert items == 4 * sum(max(1, -(-t // part)) for t in tiles)
+    assert items <= waves * 148 * 12
+    # lengths below the hint, zero-length sequences, int64 metadata: no host synchronisation, zeros for empty rows
+    sl2 = torch.tensor([513, 0, 700, 16, 0, 31, 1000, 300])
+    want2 = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, sl2.tolist(), case.k_scale, case.v_scale)
+    out2 = kv.int8_paged_attention(q, kcd, vcd, bt.long(), sl2.cuda(), ks, vs, num_splits="planned", max_seq_len=2048)
+    live = sl2 > 0
+    _check(out2[live.cuda()], want2[live])
+    assert float(out2[(~live).cuda()].abs().max()) == 0.0
+    # the other operators of the tiled path
+    kb = torch.full((case.num_blocks, 16, 4, 128), float("nan"), dtype=torch.bfloat16)
+    vb = torch.full_like(kb, float("nan"))
+    s_ = case.slot_mapping
+    kb[s_ // 16, s_ % 16], vb[s_ // 16, s_ % 16] = case.key, case.value
+    wantb = oracle.float_paged_attention_oracle(case.query, kb, vb, case.block_tables, lens)
+    _check(kv.bf16_paged_attention(q, kb.cuda(), vb.cuda(), bt, sl, num_splits="planned"), wantb)
+    from conftest import package
+
+    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
+    wantq = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
+    outq = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits="planned", quantize_q=True).float().cpu()
+    assert cosine(outq, wantq.float()) >= MIN_COS and max_abs(outq, wantq.float()) <= MAX_ABS
+    assert kv.device_status() == 0
+
+
+def test_device_planned_splits_many_sequences(kv, workloads):
+    """More sequences than lanes (each lane of the planning warp owns a run of them), ragged lengths, and enough
+    tiles that the parts are longer than one tile; every sequence is checked against the oracle."""
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(1, 1500, (150,), generator=g).tolist()
+    lens[7], lens[100] = 4000, 3999
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=33)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    q, kcd, vcd, bt, sl, ks, vs = _dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    kv.release_workspaces()
+    out = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits="planned")
+    _check(out, want)
+    items, part, waves = kv.last_split_plan()
+    tiles = [(n + 15) // 16 for n in lens]
+    assert part > 1 and items == 4 * sum(max(1, -(-t // part)) for t in tiles) and items <= waves * 148 * 12
+    assert kv.device_status() == 0
+
+
+def test_device_planned_splits_in_decode_step_and_dynamic_scales(kv, workloads):
+    lens = [513, 97, 1030, 16]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=16)
+    dev = "cuda"
+    last = torch.tensor([sum(lens[: b + 1]) - 1 for b in range(len(lens))])
+    kc0, vc0 = torch.zeros_like(kc), torch.zeros_like(vc)
+    keep = torch.ones(sum(lens), dtype=torch.bool)
+    keep[last] = False
+    oracle.cache_write(case.key[keep], case.value[keep], kc0, vc0, case.slot_mapping[keep], case.k_scale, case.v_scale)
+    kcd, vcd = kc0.to(dev), vc0.to(dev)
+    out = kv.int8_decode_step(case.query.to(dev), case.key[last].to(dev), case.value[last].to(dev), kcd, vcd,
+                              case.slot_mapping[last].to(dev), case.block_tables.to(dev), case.seq_lens.to(dev),
+                              case.k_scale.to(dev), case.v_scale.to(dev), max_seq_len=max(lens), num_splits="planned")
+    assert torch.equal(kcd.cpu(), kc) and torch.equal(vcd.cpu(), vc)
+    _check(out, oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale))
+    lens = [513, 97, 1030, 16, 1, 31, 2048]
+    case, kc, vc, ksc, vsc = _dynamic_case(workloads, lens, workloads.QWEN25_7B, seed=21)
+    want = oracle.dynamic_int8_paged_attention_oracle(case.query, kc, vc, ksc, vsc, case.block_tables, lens)
+    q, kcd, vcd, kscd, vscd, bt, sl = _dev(case.query, kc, vc, ksc, vsc, case.block_tables, case.seq_lens)
+    _check(kv.int8_paged_attention_dynamic(q, kcd, vcd, kscd, vscd, bt, sl, num_splits="planned"), want)
+    # shapes outside the tiled kernels cannot be planned: the library says so
+    shape = workloads.LayerShape(8, 2, 64, 8)
+    c2, k2, v2 = _case_on_gpu(kv, workloads, [33, 9], shape=shape, seed=3)
+    from conftest import package
+
+    with pytest.raises(package("_lib").Int8KVError):
+        kv.int8_paged_attention(*_dev(c2.query, k2, v2, c2.block_tables, c2.seq_lens, c2.k_scale, c2.v_scale),
+                                num_splits="planned")
+    assert kv.device_status() == 0
+
+
 def _dynamic_case(workloads, lens, shape, seed, v_gain=None):
     """A paged cache filled by the dynamic per-(token, head) scheme on the CPU (oracle arithmetic); unused slots
     hold garbage bytes and NaN scales, which attention must never read into its result."""
