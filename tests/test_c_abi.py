@@ -58,6 +58,20 @@ def test_workspace_sizing(lib):
     assert lib.int8kv_workspace_status_offset((1 << 20)) == (1 << 20) - 16
 
 
+def test_automatic_workspace_covers_the_planned_path(lib):
+    auto = lambda B, Hq, Hkv, seq: lib.int8kv_workspace_bytes_auto(B, Hq, Hkv, 128, seq, 16, 148)
+    fixed = lambda B, Hq, Hkv, seq: lib.int8kv_workspace_bytes(B, Hq, 128, lib.int8kv_choose_splits(B, Hkv, seq, 16, 148))
+    for B, Hq, Hkv, seq in ((1, 28, 4, 512), (8, 28, 4, 4096), (64, 28, 4, 8192), (256, 28, 4, 8192), (32, 64, 8, 65536),
+                            (32, 8, 1, 65536), (2000, 28, 4, 8192)):
+        assert auto(B, Hq, Hkv, seq) >= fixed(B, Hq, Hkv, seq)
+    # one wave of items (1776 warps), seven query heads each, 132 floats per partial row, plus the sequence table
+    assert auto(32, 7, 1, 65536) >= 1776 * 7 * 132 * 4 + 32 * 8 + 32
+    # more sequences than a plan covers: exactly the fixed size
+    assert auto(2000, 28, 4, 8192) == fixed(2000, 28, 4, 8192)
+    assert auto(-1, 28, 4, 512) == -1 and auto(8, 30, 4, 512) == -1
+    assert lib.int8kv_workspace_bytes_auto(0, 28, 4, 128, 512, 16, 148) == 16
+
+
 def test_split_heuristic(lib):
     cap = lib.int8kv_max_splits()
     assert cap >= 16
@@ -100,6 +114,8 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert attn() == _lib.E_NULLPTR
     assert attn(B=0) == _lib.OK
     assert attn(splits=10 ** 6) == _lib.E_BAD_SHAPE
+    assert attn(splits=-2) == _lib.E_BAD_SHAPE
+    assert attn(splits=_lib.SPLITS_PLANNED) == _lib.E_NULLPTR  # -1 is a valid request; the null pointers are not
     assert lib.int8kv_merge_partials(None, 0, 1, 28, 128, None, 0, st3, None) == _lib.E_BAD_SHAPE
     assert lib.int8kv_merge_partials(None, 2, 1, 28, 128, None, 0, st3, None) == _lib.E_NULLPTR
     assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 2, st4, st4, 4, 16, None, 0, st2, 4,
