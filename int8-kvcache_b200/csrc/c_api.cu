@@ -236,7 +236,7 @@ int run_attention(const AttnCall& a) {
   bool planned = false;
   PlanShape ps{};
   PlanLayout pl{};
-  if (a.num_splits <= 0 && tiled && a.partial_out == nullptr && tiles > 0 &&
+  if (a.num_splits <= 0 && tiled && tiles > 0 &&
       a.bt_width * a.block_size < (int64_t(1) << 21) * 16 &&  // tile counts stay exact in fp32 on the device
       (a.num_splits == INT8KV_SPLITS_PLANNED ? plan_possible(a.B, a.Hkv, sm)
                                               : plan_pays(a.B, a.Hkv, max_seq, a.block_size, sm))) {
@@ -302,6 +302,7 @@ int run_attention(const AttnCall& a) {
     p.plan_slots = sm * 12;
     p.plan_k_max = ps.k_max;
     p.plan_min_part = ps.min_part;
+    p.direct_part = a.partial_out;
   }
   if (tiled) {
     alignas(64) CUtensorMap tmK, tmV;

@@ -93,6 +93,7 @@ struct AttnParams {
   int64_t ks_st[3], vs_st[3];
   // device-planned splits (plan_table != null): every warp derives the common part length from seq_lens and finds
   // its own item, instead of numbering the items arithmetically from B, num_splits, Hkv; see plan_in_warp
+  float* direct_part;   // planned + caller wants partial rows: where a single-part sequence's row goes ([B*Hq, row_floats])
   int2* plan_table;     // [B] {row0, used}: written by the warp of (part 0, head 0), read by the merge kernel
   int* plan_header;     // {items, part length in tiles, waves, 0}, written by item 0
   int plan_grid_items;  // item numbers the launch covers (>= the items of any plan it can choose)

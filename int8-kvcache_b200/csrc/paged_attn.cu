@@ -329,16 +329,25 @@ __device__ __forceinline__ int64_t arithmetic_row0(const AttnParams& p, const It
   return (static_cast<int64_t>(it.c) * p.B + it.b) * p.Hq + it.h * p.G;
 }
 
+// Where the item's result goes: the partial row of the group's first query head (the others follow), or null
+// for `out`.  A planned sequence with a single part has no workspace row (row0 < 0): its result is final and
+// goes to `out`, or to the caller's partial rows when those were asked for.
+__device__ __forceinline__ float* result_row(const AttnParams& p, const ItemCoord& it, int64_t row0) {
+  if (row0 >= 0) return p.part + row0 * p.row_floats;
+  if (p.direct_part != nullptr) return p.direct_part + (static_cast<int64_t>(it.b) * p.Hq + it.h * p.G) * p.row_floats;
+  return nullptr;
+}
+
 // Result of an empty tile range: zeros to `out` (direct mode) or lse = -inf (partial mode).
-__device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord& it, int lane, int64_t row0) {
-  if (row0 < 0) {
+__device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord& it, int lane, const float* prow) {
+  if (prow == nullptr) {
     for (int hg = 0; hg < p.G; ++hg) {
       const int hq = it.h * p.G + hg;
       for (int d = lane; d < p.D; d += kWarp)
         store_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], 0.f);
     }
   } else if (lane < p.G) {
-    p.part[(row0 + lane) * p.row_floats + p.D] = -INFINITY;
+    const_cast<float*>(prow)[lane * p.row_floats + p.D] = -INFINITY;
   }
 }
 
@@ -459,8 +468,9 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     item_range(p, it);
     row0 = arithmetic_row0(p, it);
   }
+  float* const prow = result_row(p, it, row0);
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
-    write_empty(p, it, lane, row0);
+    write_empty(p, it, lane, prow);
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
@@ -734,14 +744,14 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       o[2 * j] = acc[j][e] * inv;
       o[2 * j + 1] = acc[j][e + 2] * inv;
     }
-    if (row0 < 0) {
+    if (prow == nullptr) {
       store16_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + 16 * g * p.o_st[2], p.o_st[2], o);
     } else {
-      const int64_t row = row0 + hg;
-      float4* dst = reinterpret_cast<float4*>(p.part + row * p.row_floats + 16 * g);
+      float* row = prow + hg * p.row_floats;
+      float4* dst = reinterpret_cast<float4*>(row + 16 * g);
 #pragma unroll
       for (int d = 0; d < 4; ++d) dst[d] = make_float4(o[4 * d], o[4 * d + 1], o[4 * d + 2], o[4 * d + 3]);
-      if (g == 0) p.part[row * p.row_floats + p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (g == 0) row[p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
 }
@@ -812,8 +822,9 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     item_range(p, it);
     row0 = arithmetic_row0(p, it);
   }
+  float* const prow = result_row(p, it, row0);
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
-    write_empty(p, it, lane, row0);
+    write_empty(p, it, lane, prow);
     return;
   }
   ring.set_range(it.t0, p.tiles_per_block);
@@ -947,7 +958,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     const float l = e ? l1 : l0;
     const float m = e ? m1 : m0;
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    if (row0 < 0) {
+    if (prow == nullptr) {
       const int64_t base = it.b * p.o_st[0] + hq * p.o_st[1];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -955,8 +966,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         store_from_float(p.out, p.out_dtype, base + (16 * j + g + 8) * p.o_st[2], acc[j][e + 2] * inv);
       }
     } else {
-      const int64_t row = row0 + hg;
-      float* dst = p.part + row * p.row_floats;
+      float* dst = prow + hg * p.row_floats;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         dst[16 * j + g] = acc[j][e] * inv;

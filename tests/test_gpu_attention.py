@@ -381,6 +381,13 @@ def test_device_planned_splits(kv, workloads):
     live = sl2 > 0
     _check(out2[live.cuda()], want2[live])
     assert float(out2[(~live).cuda()].abs().max()) == 0.0
+    # partial rows for a cross-device merge, planned: sequences with one part write their row themselves
+    rows = kv.int8_paged_attention_partial(q, kcd, vcd, bt, sl2.cuda(), ks, vs, num_splits="planned", max_seq_len=2048)
+    merged = kv.merge_partials(rows[None].contiguous(), 128, dtype=torch.float32)
+    _check(merged[live.cuda()], want2[live])
+    assert float(merged[(~live).cuda()].abs().max()) == 0.0
+    lse = rows[:, :, 128].cpu()
+    assert torch.isinf(lse[~live]).all() and torch.isfinite(lse[live]).all()
     # the other operators of the tiled path
     kb = torch.full((case.num_blocks, 16, 4, 128), float("nan"), dtype=torch.bfloat16)
     vb = torch.full_like(kb, float("nan"))
