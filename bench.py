@@ -297,18 +297,31 @@ def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens
         return sh.sequence_parallel_int8_attention(layer.query, layer.kc, layer.vc, layer.block_tables, layer.seq_lens,
                                                    layer.k_scale, layer.v_scale, max_seq_len=max_local)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize(device)
-    dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize(device)
-    dist.barrier()
+    # The step (partial kernel, NCCL all-gather, merge) is captured once into a CUDA graph and replayed, as a decode
+    # loop would run it; --no-graph launches it from Python every step.
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        run, launched = step, "eager"
+        if not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            run, launched = graph.replay, "cuda graph"
+            for _ in range(3):
+                run()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        torch.cuda.synchronize(device)
+        dist.barrier()
     t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
@@ -323,6 +336,7 @@ def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens
             "vs_baseline": None, "dtype": "int8", "data": "synthetic", "config": config, "us_per_call": ms * 1e3,
             "gpu_launches": 2 * args.steps,
             "collective": {"op": "all_gather_into_tensor", "bytes_per_rank": len(seq_lens) * hq * 132 * 4},
+            "launched": launched,
         }))
     dist.destroy_process_group()
 
