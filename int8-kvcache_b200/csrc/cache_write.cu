@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(256) cache_write_vec_kernel(const WriteParams 
   const uint32_t per_token = static_cast<uint32_t>(p.Hkv) * chunks;
   const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
+  grid_dependency_wait();    // the new rows and the slots may come from the kernel launched just before
+  grid_launch_dependents();  // the next kernel in the stream waits for this grid before it reads the cache
   const uint32_t t = idx / per_token;
   const uint32_t rem = idx - t * per_token;
   const uint32_t h = rem / chunks;
@@ -173,9 +175,9 @@ int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream) 
       for (bs_shift = 0; (1 << bs_shift) < p.block_size; ++bs_shift) {}
     const unsigned blocks = static_cast<unsigned>((units + threads - 1) / threads);
     const uint32_t total = static_cast<uint32_t>(units);
-    if (p.in_dtype == INT8KV_BF16) cache_write_vec_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
-    else if (p.in_dtype == INT8KV_FP16) cache_write_vec_kernel<__half><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
-    else cache_write_vec_kernel<float><<<blocks, threads, 0, stream>>>(p, total, bs_shift);
+    if (p.in_dtype == INT8KV_BF16) return launch_pdl(cache_write_vec_kernel<__nv_bfloat16>, blocks, threads, 0, stream, p, total, bs_shift);
+    if (p.in_dtype == INT8KV_FP16) return launch_pdl(cache_write_vec_kernel<__half>, blocks, threads, 0, stream, p, total, bs_shift);
+    return launch_pdl(cache_write_vec_kernel<float>, blocks, threads, 0, stream, p, total, bs_shift);
   } else {
     const int64_t work = p.T * p.Hkv * static_cast<int64_t>(p.D);
     int64_t blocks = (work + threads - 1) / threads;

@@ -8,6 +8,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <cstring>
+#include <utility>
+
 #include "../../include/int8kv_b200.h"
 #include "kernels.h"
 
@@ -139,6 +143,34 @@ __device__ __forceinline__ uint32_t pack4_sat(int n0, int n1, int n2, int n3) {
 // Both are no-ops for a kernel launched without the attribute.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// INT8KV_PDL=0 in the environment turns programmatic dependent launch off (read once).
+inline bool pdl_enabled() {
+  static const bool on = []() {
+    const char* e = std::getenv("INT8KV_PDL");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  return on;
+}
+
+// Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while the previous
+// kernel in the stream drains; every kernel here calls grid_dependency_wait() before its first global access.
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
+}
 
 __host__ __device__ __forceinline__ int dtype_bytes(int dtype) { return dtype == INT8KV_FP32 ? 4 : 2; }
 

@@ -1223,10 +1223,9 @@ static int env_int(const char* name, int fallback) {
 }
 
 // Tuning switches, read once from the environment: INT8KV_STAGES (ring depth of the INT8 kernel),
-// INT8KV_WPC (warps per CTA: 1 or 4, 0 = choose from the grid size), INT8KV_PDL (0 disables programmatic
-// dependent launch).
+// INT8KV_WPC (warps per CTA: 1 or 4, 0 = choose from the grid size).
 struct Tuning {
-  int stages, wpc, pdl;
+  int stages, wpc;
 };
 static const Tuning& tuning() {
   static const Tuning t = []() {
@@ -1235,7 +1234,6 @@ static const Tuning& tuning() {
     if (x.stages != 2 && x.stages != 4 && x.stages != 6 && x.stages != 8) x.stages = kInt8Stages;
     x.wpc = env_int("INT8KV_WPC", 0);
     if (x.wpc != 1 && x.wpc != 4) x.wpc = 0;
-    x.pdl = env_int("INT8KV_PDL", 1) != 0;
     return x;
   }();
   return t;
@@ -1253,25 +1251,6 @@ static int set_smem(K kernel, int bytes) {
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
   if (track) done[dev].store(true, std::memory_order_release);
   return 0;
-}
-
-// Launch with the programmatic-stream-serialisation attribute: the grid may be scheduled while the previous
-// kernel in the stream drains; every kernel here calls grid_dependency_wait() before its first global access.
-template <typename... KArgs, typename... Args>
-static int launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
-                      Args&&... args) {
-  cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(block, 1, 1);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = tuning().pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
 
 // Item numbers a tiled launch covers: the capacity of the planned list, or B * num_splits * Hkv.
