@@ -287,8 +287,9 @@ int64_t int8kv_workspace_bytes(int batch, int num_q_heads, int head_dim, int num
 /* Bytes of workspace with which every automatic path (num_splits 0 or -1) of the attention entry points is
  * available for this shape, the device-planned one included: partial rows of the items and the per-sequence
  * table.  Never smaller than int8kv_workspace_bytes() for the split count int8kv_choose_splits() picks.
- * A planned call leaves {items, part length in 16-token tiles, waves aimed for, 0} as four int32 in the 16 bytes
- * before the status word. */
+ * A planned call leaves {items, part length in 16-token tiles, waves aimed for, INT8KV_PLAN_HEADER_TAG} as four
+ * int32 in the 16 bytes before the status word (other calls may use those bytes for partial rows). */
+#define INT8KV_PLAN_HEADER_TAG 0x504c414e
 int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads, int head_dim, int64_t max_seq_len,
                                     int block_size, int sm_count);
 

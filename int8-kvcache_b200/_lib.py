@@ -24,6 +24,7 @@ DEV_WAIT_TIMEOUT = 1
 DEV_SLOT_MISMATCH = 2
 STATIC_WS_BYTES = 8 * 1024 * 1024
 SPLITS_AUTO, SPLITS_PLANNED = 0, -1
+PLAN_HEADER_TAG = 0x504C414E
 
 BF16, FP16, FP32 = 0, 1, 2
 

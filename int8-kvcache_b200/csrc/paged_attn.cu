@@ -223,6 +223,7 @@ __device__ __forceinline__ int plan_parts(int len, int P, float rP) {
 
 constexpr int kPlanRun = 16;  // sequences per lane: a plan covers up to 32 * 16 sequences
 constexpr int kPlanShortestPart = 8;
+constexpr int kPlanHeaderTag = 0x504c414e;  // marks the 16 bytes before the status word as a plan header
 
 __device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, int lane, ItemCoord& it, int64_t& row0) {
   // lane l holds the lengths of sequences [l * run, (l + 1) * run) in registers; every pass below works on them
@@ -288,7 +289,7 @@ __device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, 
     p.plan_header[0] = static_cast<int>(count);
     p.plan_header[1] = P;
     p.plan_header[2] = k;
-    p.plan_header[3] = 0;
+    p.plan_header[3] = kPlanHeaderTag;
   }
   if (item >= count) return false;
 

@@ -250,8 +250,9 @@ def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits)
 
 
 def last_split_plan(device=None):
-    """(items, part length in 16-token tiles, waves aimed for) that the most recent device-planned call on the
-    current stream of `device` left in its workspace, or None if no plan was written there.  Synchronises."""
+    """(items, part length in 16-token tiles, waves aimed for) that a device-planned call on the current stream of
+    `device` left in its workspace, or None if the bytes there are not a plan header (calls that are not planned
+    may overwrite them with partial rows, or leave an older header in place).  Synchronises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(device).cuda_stream)
@@ -260,8 +261,8 @@ def last_split_plan(device=None):
     if buf is None:
         return None
     off = _require_lib().int8kv_workspace_status_offset(buf.numel()) - 16
-    items, part, waves, _ = buf[off:off + 16].view(torch.int32).tolist()
-    return (items, part, waves) if items > 0 else None
+    items, part, waves, tag = buf[off:off + 16].view(torch.int32).tolist()
+    return (items, part, waves) if tag == _lib.PLAN_HEADER_TAG and items > 0 else None
 
 
 def int8_paged_attention(
