@@ -338,6 +338,13 @@ def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens
             "collective": {"op": "all_gather_into_tensor", "bytes_per_rank": len(seq_lens) * hq * 132 * 4},
             "launched": launched,
         }))
+    # a live CUDA graph that holds captured NCCL work blocks the communicator's teardown: release it first
+    run = graph = None
+    import gc
+
+    gc.collect()
+    torch.cuda.synchronize(device)
+    dist.barrier()
     dist.destroy_process_group()
 
 
