@@ -405,7 +405,9 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
   return v;
 }
 
-template <int NST, int MODE>
+// PLANNED: the items come from plan_in_warp instead of being numbered arithmetically.  A template parameter rather
+// than a run-time test, so that the kernel that serves small calls does not carry the planning code.
+template <int NST, int MODE, bool PLANNED>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
@@ -420,11 +422,11 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
   ItemCoord it;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
-  const bool planned = p.plan_table != nullptr;
-  if (planned) {
+  constexpr bool planned = PLANNED;
+  if constexpr (planned) {
     if (item >= p.plan_grid_items) return;
-  } else if (!item_coords(p, item, it)) {
-    return;
+  } else {
+    if (!item_coords(p, item, it)) return;
   }
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -456,13 +458,13 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   // before the wait would let a whole chain of future kernels pile up on the SMs.
   grid_launch_dependents();
   int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
-  if (planned) {
+  if constexpr (planned) {
     if (!plan_in_warp(p, item, lane, it, row0)) return;
   }
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.head = it.h;
   if constexpr (DYN) ring.sc_src = lane >= 16 ? p.vs_cache + it.h * p.vs_st[2] : p.ks_cache + it.h * p.ks_st[2];
-  if (planned) {
+  if constexpr (planned) {
     ring.prefetch_tables(it.t0 / p.tiles_per_block);
   } else {
     ring.prefetch_tables(guessed_first_block(p, it.c));
@@ -770,7 +772,7 @@ __device__ __forceinline__ void mma16(float (&d)[4], const uint32_t (&a)[4], uin
   else mma_f16(d, a[0], a[1], a[2], a[3], b0, b1);
 }
 
-template <int NST, bool IS_BF16>
+template <int NST, bool IS_BF16, bool PLANNED>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp)
 paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const AttnParams p) {
@@ -782,11 +784,11 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 
   ItemCoord it;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
-  const bool planned = p.plan_table != nullptr;
-  if (planned) {
+  constexpr bool planned = PLANNED;
+  if constexpr (planned) {
     if (item >= p.plan_grid_items) return;
-  } else if (!item_coords(p, item, it)) {
-    return;
+  } else {
+    if (!item_coords(p, item, it)) return;
   }
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -811,12 +813,12 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   // before the wait would let a whole chain of future kernels pile up on the SMs.
   grid_launch_dependents();
   int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
-  if (planned) {
+  if constexpr (planned) {
     if (!plan_in_warp(p, item, lane, it, row0)) return;
   }
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.head = it.h;
-  if (planned) {
+  if constexpr (planned) {
     ring.prefetch_tables(it.t0 / p.tiles_per_block);
   } else {
     ring.prefetch_tables(guessed_first_block(p, it.c));
@@ -1267,31 +1269,14 @@ static int pick_wpc(int64_t items, int sm_count) {
   return items <= static_cast<int64_t>(sm_count) * 12 ? 1 : kTiledWarpsPerCta;
 }
 
-template <int NST>
-static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                              cudaStream_t stream) {
-  constexpr int smem_max = kTiledWarpsPerCta * NST * 4096 + kTiledWarpsPerCta * NST * 8 + 1024;
-  const bool fused = p.new_k != nullptr;
-  auto kernel = fused ? paged_attn_int8_kernel<NST, kFusedWrite> : paged_attn_int8_kernel<NST, kPlain>;
-  if (fused) {
-    if (set_smem<30 + NST>(paged_attn_int8_kernel<NST, kFusedWrite>, smem_max) != 0) return INT8KV_E_LAUNCH;
-  } else {
-    if (set_smem<10 + NST>(paged_attn_int8_kernel<NST, kPlain>, smem_max) != 0) return INT8KV_E_LAUNCH;
-  }
-  const int64_t items = grid_items(p);
-  if (items <= 0) return INT8KV_OK;
-  const int wpc = pick_wpc(items, sm_count);
-  const size_t smem = static_cast<size_t>(wpc) * NST * 4096 + wpc * NST * 8 + 1024;
-  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
-}
-
-// Dynamic-scale variant: default ring depth only; each stage has a 128-byte scale slot beside it.
-static int launch_int8_dynamic(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+// One instantiation of the INT8 kernel: raises its dynamic shared-memory limit once, sizes the grid, launches.
+template <int NST, int MODE, bool PLANNED>
+static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                                cudaStream_t stream) {
-  constexpr int NST = kInt8Stages;
-  constexpr int per_warp = NST * (4096 + 8 + 128);
-  auto kernel = paged_attn_int8_kernel<NST, kDynScales>;
-  if (set_smem<50>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0) return INT8KV_E_LAUNCH;
+  constexpr int per_warp = NST * (4096 + 8 + (MODE == kDynScales ? 128 : 0));  // stages, barriers, scale slots
+  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED>;
+  if (set_smem<100 + NST * 8 + MODE * 2 + (PLANNED ? 1 : 0)>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
+    return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);
@@ -1299,9 +1284,25 @@ static int launch_int8_dynamic(const AttnParams& p, const CUtensorMap& tmK, cons
   return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
 }
 
+template <int NST>
+static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
+                              cudaStream_t stream) {
+  return p.new_k != nullptr ? launch_int8_variant<NST, kFusedWrite, false>(p, tmK, tmV, sm_count, stream)
+                            : launch_int8_variant<NST, kPlain, false>(p, tmK, tmV, sm_count, stream);
+}
+
+// The ring depth can be changed from the environment for the plain and fused kernels; the dynamic-scale and the
+// planned instantiations exist with the default depth only.
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                            cudaStream_t stream) {
-  if (p.ks_cache != nullptr) return launch_int8_dynamic(p, tmK, tmV, sm_count, stream);
+  constexpr int N = kInt8Stages;
+  const bool planned = p.plan_table != nullptr;
+  if (p.ks_cache != nullptr)
+    return planned ? launch_int8_variant<N, kDynScales, true>(p, tmK, tmV, sm_count, stream)
+                   : launch_int8_variant<N, kDynScales, false>(p, tmK, tmV, sm_count, stream);
+  if (planned)
+    return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, true>(p, tmK, tmV, sm_count, stream)
+                              : launch_int8_variant<N, kPlain, true>(p, tmK, tmV, sm_count, stream);
   switch (tuning().stages) {
     case 2: return launch_int8_stages<2>(p, tmK, tmV, sm_count, stream);
     case 6: return launch_int8_stages<6>(p, tmK, tmV, sm_count, stream);
@@ -1310,12 +1311,12 @@ int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CU
   }
 }
 
-template <bool IS_BF16>
+template <bool IS_BF16, bool PLANNED>
 static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                       cudaStream_t stream) {
   constexpr int smem_max = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
-  auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16>;
-  if (set_smem<IS_BF16 ? 1 : 2>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
+  auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16, PLANNED>;
+  if (set_smem<(IS_BF16 ? 1 : 2) + (PLANNED ? 2 : 0)>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   const int wpc = pick_wpc(items, sm_count);
@@ -1325,8 +1326,12 @@ static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtenso
 
 int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                           cudaStream_t stream) {
-  return p.cache_kind == kCacheBf16 ? launch_f16<true>(p, tmK, tmV, sm_count, stream)
-                                    : launch_f16<false>(p, tmK, tmV, sm_count, stream);
+  const bool planned = p.plan_table != nullptr;
+  if (p.cache_kind == kCacheBf16)
+    return planned ? launch_f16<true, true>(p, tmK, tmV, sm_count, stream)
+                   : launch_f16<true, false>(p, tmK, tmV, sm_count, stream);
+  return planned ? launch_f16<false, true>(p, tmK, tmV, sm_count, stream)
+                 : launch_f16<false, false>(p, tmK, tmV, sm_count, stream);
 }
 
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
