@@ -37,7 +37,7 @@ if str(REPO) not in sys.path:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch, from the one-pass ncu capture
 # summarised in profiles/bench_default__launch_list.md (default workload only)
-NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33691648}
+NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33690734}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
