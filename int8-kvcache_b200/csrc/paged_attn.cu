@@ -7,7 +7,10 @@
 // single warp when the grid is too small to fill the machine with 4-warp CTAs.  Warps never synchronise with
 // each other; there is no __syncthreads in the attention kernels.  A sequence uses as many of the num_splits
 // parts as it takes to give each about the tile count of the longest sequence's parts; partial results go to
-// a workspace and merge_partials_kernel, launched with programmatic dependent launch, combines them.
+// a workspace and merge_partials_kernel, launched with programmatic dependent launch, combines them.  For
+// mid-size calls the parts are not numbered from num_splits at all: every warp derives one common part length from
+// the actual seq_lens so that all parts fill whole resident waves of warps (plan_in_warp, the PLANNED
+// instantiations).
 //
 // Data movement.  Each warp runs its own NST-deep ring of shared-memory stages filled by TMA: one
 // cp.async.bulk.tensor tile load per 16x128-byte K tile and V tile, issued by lane 0, completion counted on an
@@ -25,7 +28,9 @@
 // obtained from the C fragments with movmatrix (8x8 transpose) and O^T = V^T . P^T runs as fp16 MMA m16n8k16 with
 // dims on M: int8 -> fp16 is exact (bytes are spliced into 0x64xx = 1024+u and 1152 is subtracted), and the V^T
 // A fragment needs pairs of tokens at one dim, produced by byte interleaving (prmt) of 16-byte row pieces on the
-// way to fp16.  v_scale and 1/l are applied once in the epilogue.
+// way to fp16.  v_scale and 1/l are applied once in the epilogue.  The kDynScales mode reads one K and one V scale
+// per (token, head) instead: they travel with the tile through the ring (cp.async, same mbarrier), K scales
+// multiply the score rows, V scales ride on P behind a running power-of-two normalisation.
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
