@@ -35,8 +35,8 @@ REPO = Path(__file__).resolve().parent
 if str(REPO) not in sys.path:
     sys.path.insert(0, str(REPO))
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch, from the one-pass ncu capture
-# summarised in profiles/bench_default__launch_list.md (default workload only)
+# dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch, from a one-pass ncu capture of
+# this script's default workload (the launch-list summary under profiles/)
 NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33690734}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0

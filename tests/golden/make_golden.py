@@ -62,8 +62,11 @@ def chain_attention(ref, query, kc, vc, block_tables, seq_lens, k_scale, v_scale
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("INT8KV_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("INT8KV_REFERENCE"),
+                    help="checkout of cjsmt/Int8-kvcache to import (or set INT8KV_REFERENCE)")
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("--reference (or INT8KV_REFERENCE) must name a checkout of the reference")
     sys.path.insert(0, args.reference)
     sys.path.insert(0, str(REPO))
     quant = importlib.import_module("src.quant")
