@@ -50,7 +50,9 @@ extern "C" {
 
 /* num_splits values with a special meaning (attention entry points) */
 #define INT8KV_SPLITS_AUTO 0      /* choose from the shape; large calls may plan their parts on the device */
-#define INT8KV_SPLITS_PLANNED (-1) /* always let the device-side plan choose (tiled shapes only) */
+#define INT8KV_SPLITS_PLANNED (-1) /* always plan on the device; INT8KV_E_UNSUPPORTED for shapes outside the tiled
+                                      kernels, more than 512 sequences or more (sequence, head) pairs than resident
+                                      warps; INT8KV_E_WORKSPACE below int8kv_workspace_bytes_auto() bytes */
 
 int int8kv_abi_version(void);
 const char* int8kv_status_str(int status);
