@@ -419,6 +419,24 @@ def test_device_planned_splits_many_sequences(kv, workloads):
     items, part, waves = kv.last_split_plan()
     tiles = [(n + 15) // 16 for n in lens]
     assert part > 1 and items == 4 * sum(max(1, -(-t // part)) for t in tiles) and items <= waves * 148 * 12
+    # the most sequences a plan covers (16 per lane of the planning warp), two KV heads, some of them empty
+    shape = workloads.LayerShape(14, 2, 128, 16)
+    lens = torch.randint(1, 400, (512,), generator=g).tolist()
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=34)
+    sl = case.seq_lens.clone()
+    sl[::37] = 0
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, sl.tolist(), case.k_scale, case.v_scale)
+    q, kcd, vcd, bt, ks, vs = _dev(case.query, kc, vc, case.block_tables, case.k_scale, case.v_scale)
+    out = kv.int8_paged_attention(q, kcd, vcd, bt, sl.cuda(), ks, vs, num_splits="planned", max_seq_len=400)
+    live = sl > 0
+    _check(out[live.cuda()], want[live])
+    assert float(out[(~live).cuda()].abs().max()) == 0.0
+    # one sequence more is refused, not mis-planned
+    from conftest import package
+
+    with pytest.raises(package("_lib").Int8KVError):
+        kv.int8_paged_attention(q[:1].expand(513, -1, -1).contiguous(), kcd, vcd, bt[:1].expand(513, -1).contiguous(),
+                                sl[:1].expand(513).contiguous().cuda() + 1, ks, vs, num_splits="planned", max_seq_len=400)
     assert kv.device_status() == 0
 
 
