@@ -440,6 +440,77 @@ def test_device_planned_splits_many_sequences(kv, workloads):
     assert kv.device_status() == 0
 
 
+def _plan_restated(lens, hkv, cap_tokens, k_max, min_part, grid_items, slots=148 * 12):
+    """The planning arithmetic of the kernels restated on the host: (items, part length in tiles, waves)."""
+    tiles = [(min(max(n, 0), cap_tokens) + 15) // 16 for n in lens]
+    total, longest, B = sum(tiles), max(tiles), len(lens)
+    parts = lambda P: sum(max(1, -(-t // P)) for t in tiles)
+    floor_p = max(1, -(-longest // 128))
+    k, P = max(k_max, 1), 1
+    while k >= 1:
+        room = k * slots - hkv * B // 2
+        if room > 0:
+            P = -(-(total * hkv) // room)
+            if P >= min_part or k == 1:
+                break
+        k -= 1
+    k = max(k, 1)
+    P = max(P, floor_p, 8)
+    target = min(k * slots, grid_items)
+    for rnd in range(64):
+        if parts(P) * hkv <= target or P >= longest:
+            break
+        P += max(1, P >> 4) if rnd < 16 else P
+    return parts(P) * hkv, P, k
+
+
+def test_device_plan_matches_its_restatement_on_random_batches(kv, workloads):
+    """Random batch sizes, head counts and length distributions: the plan the kernels leave in the workspace equals
+    the host restatement of the same arithmetic, fills at most the waves it aimed for, and the planned result
+    equals the result with a fixed split count."""
+    g = torch.Generator().manual_seed(2024)
+    dev = "cuda"
+    for trial, (B, hkv, lo, hi) in enumerate([(300, 4, 800, 2400), (37, 1, 4000, 30000), (512, 2, 16, 900),
+                                              (96, 8, 1, 6000), (200, 4, 3000, 3001), (5, 4, 20000, 60000)]):
+        lens = torch.randint(lo, hi + 1, (B,), generator=g).tolist()
+        hq = hkv * (7 if hkv <= 4 else 8)
+        width = -(-max(lens) // 16)
+        nblocks = sum(-(-n // 16) for n in lens)
+        gd = torch.Generator(device=dev).manual_seed(trial)
+        kc = torch.randint(-127, 128, (nblocks, 16, hkv, 128), generator=gd, device=dev, dtype=torch.int8)
+        vc = torch.randint(-127, 128, (nblocks, 16, hkv, 128), generator=gd, device=dev, dtype=torch.int8)
+        bt = torch.zeros(B, width, dtype=torch.int32)
+        perm = torch.randperm(nblocks, generator=g).to(torch.int32)
+        at = 0
+        for b, n in enumerate(lens):
+            nb = -(-n // 16)
+            bt[b, :nb] = perm[at : at + nb]
+            at += nb
+        q = torch.randn(B, hq, 128, generator=gd, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        ks = torch.rand(hkv, generator=gd, device=dev) * 0.02 + 0.01
+        vs = torch.rand(hkv, generator=gd, device=dev) * 0.02 + 0.01
+        sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+        kv.release_workspaces()
+        out = kv.int8_paged_attention(q, kc, vc, bt.to(dev), sl, ks, vs, num_splits="planned", max_seq_len=max(lens))
+        plan = kv.last_split_plan()
+        assert plan is not None
+        # what the host passes to the kernel for this shape: waves from the nominal lengths, 48-tile parts above one wave
+        nominal = (max(lens) + 15) // 16
+        k_max = 1
+        for k in (4, 3, 2, 1):
+            room = k * 1776 - B * hkv // 2
+            if room > 0 and (-(-(B * hkv * nominal) // room) >= 48 or k == 1):
+                k_max = k
+                break
+        want = _plan_restated(lens, hkv, width * 16, k_max, 48, max(k_max * 1776, B * hkv))
+        assert plan == want, (trial, plan, want)
+        assert plan[0] <= plan[2] * 1776 or plan[1] >= max(-(-n // 16) for n in lens)
+        fixed = kv.int8_paged_attention(q, kc, vc, bt.to(dev), sl, ks, vs, num_splits=3, max_seq_len=max(lens))
+        assert cosine(out.float().cpu(), fixed.float().cpu()) > 0.99999
+        assert max_abs(out.float().cpu(), fixed.float().cpu()) <= 2e-2 * max(1.0, float(fixed.float().abs().max()))
+    assert kv.device_status() == 0
+
+
 def test_device_planned_splits_in_decode_step_and_dynamic_scales(kv, workloads):
     lens = [513, 97, 1030, 16]
     case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=16)
