@@ -100,6 +100,9 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   const int64_t slots = static_cast<int64_t>(sm_count) * 12;
   const int64_t by_latency = std::min<int64_t>(tiles / 2, std::max<int64_t>(16, tiles / 8));
   int64_t s_fill = std::min(pow2_floor(std::max<int64_t>(1, slots / items)), pow2_floor(std::max<int64_t>(1, by_latency)));
+  // the smallest calls (512 warps or fewer in total) still gain from parts of only 4 tiles
+  const int64_t s_quarter = std::min<int64_t>(pow2_floor(std::max<int64_t>(1, tiles / 4)), kMaxSplits);
+  if (s_quarter > s_fill && items * s_quarter <= 512) s_fill = s_quarter;
   int64_t s_bw = 1;
   while (s_bw * items < slots * 4) s_bw *= 2;
   s_bw = std::min(s_bw, pow2_floor(std::max<int64_t>(1, tiles / 32)));
