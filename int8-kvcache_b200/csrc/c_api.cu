@@ -279,6 +279,7 @@ int run_attention(const AttnCall& a) {
   p.out = a.out; p.out_dtype = a.out_dtype;
   if (a.o_st) for (int i = 0; i < 3; ++i) p.o_st[i] = a.o_st[i];
   p.num_splits = S;
+  p.per_longest = static_cast<int>(std::max<int64_t>(1, (tiles + S - 1) / S));
   p.row_floats = rf;
   p.quantize_q = a.quantize_q;
   p.sm_scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(a.D)));

@@ -61,6 +61,7 @@ struct AttnParams {
   int block_size;
   int tiles_per_block;  // block_size / 16 (tiled kernels)
   int hint_tiles;       // ceil(max_seq_len hint / 16): sizes the grid and seeds the block-table prefetch
+  int per_longest;      // ceil(hint_tiles / num_splits), at least 1: tiles per part of the longest sequence
   const void* bt;
   int bt_is_i64;
   int64_t bt_st[2];

@@ -165,18 +165,21 @@ struct ItemCoord {
 __device__ __forceinline__ bool item_coords(const AttnParams& p, int64_t item, ItemCoord& it) {
   const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
   if (item >= total) return false;
-  it.h = static_cast<int>(item % p.Hkv);
-  const int64_t r = item / p.Hkv;
-  it.c = static_cast<int>(r % p.num_splits);
-  it.b = static_cast<int>(r / p.num_splits);
+  // a grid has fewer than 2^31 CTAs, so the item number fits 32 bits: unsigned 32-bit divisions cost a fraction of
+  // the 64-bit ones, and this runs in every warp's prologue
+  const uint32_t i = static_cast<uint32_t>(item);
+  const uint32_t r = i / static_cast<uint32_t>(p.Hkv);
+  it.h = static_cast<int>(i - r * static_cast<uint32_t>(p.Hkv));
+  const uint32_t b = r / static_cast<uint32_t>(p.num_splits);
+  it.c = static_cast<int>(r - b * static_cast<uint32_t>(p.num_splits));
+  it.b = static_cast<int>(b);
   return true;
 }
 
 // First logical block of split c if the sequence had the hinted maximum length (the guess used to start the
 // block-table read early; exact for batches of full-length sequences).
 __device__ __forceinline__ int guessed_first_block(const AttnParams& p, int c) {
-  const int per = (p.hint_tiles + p.num_splits - 1) / p.num_splits;
-  return (c * per) / p.tiles_per_block;
+  return static_cast<int>(static_cast<uint32_t>(c * p.per_longest) / static_cast<uint32_t>(p.tiles_per_block));
 }
 
 // The tile range of the item: reads seq_lens[b]; every sequence splits its own tiles evenly over the parts it uses.
@@ -190,9 +193,9 @@ __device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   // A sequence uses as many of the num_splits parts as it takes to give each about the tile count that the
   // longest sequence's parts have, and leaves the rest empty: in a ragged batch every working warp then has
   // a similar amount to read, and short sequences write few partial rows.
-  const int per_longest = max(1, (p.hint_tiles + p.num_splits - 1) / p.num_splits);
-  const int used = min(p.num_splits, max(1, (ntiles + per_longest - 1) / per_longest));
-  const int per = (ntiles + used - 1) / used;
+  const uint32_t per_longest = static_cast<uint32_t>(p.per_longest);  // ceil(hint_tiles / num_splits), at least 1
+  const int used = min(p.num_splits, max(1, static_cast<int>((static_cast<uint32_t>(ntiles) + per_longest - 1) / per_longest)));
+  const int per = static_cast<int>(static_cast<uint32_t>(ntiles + used - 1) / static_cast<uint32_t>(used));
   it.t0 = it.c * per;
   it.t1 = it.c < used ? min(it.t0 + per, ntiles) : it.t0;
 }
@@ -562,6 +565,8 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
   const float kmul = DYN ? p.sm_scale_log2 : fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
+  // requested here, used in the epilogue: a load issued there would put its whole latency on the critical path
+  const float v_scale_head = DYN ? 1.f : fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
   const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
   const float sc1 = kmul * __shfl_sync(kFull, q_mul, (2 * t + 1) * 4);
 
@@ -737,7 +742,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   l1 += __shfl_xor_sync(kFull, l1, 8);
   l0 += __shfl_xor_sync(kFull, l0, 16);
   l1 += __shfl_xor_sync(kFull, l1, 16);
-  const float vs = DYN ? v_unnorm : fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
+  const float vs = DYN ? v_unnorm : v_scale_head;
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
     const int hg = 2 * t + e;
