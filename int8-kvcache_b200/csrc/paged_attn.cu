@@ -548,19 +548,14 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       for (int i = 0; i < 32; ++i) qi[i] = __float2int_rn(qv[i] * inv);
       q_mul = amax > 0.f ? amax / 32000.f : 0.f;
     }
+    // v = 256 * hi + lo with lo in [-128, 127]: lo is the low byte of v, hi the second byte of v + 128 (two's
+    // complement), so four values pack into the two limb words with byte permutes
 #pragma unroll
     for (int w = 0; w < 8; ++w) {
-      uint32_t hw = 0, lw = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int v = qi[4 * w + e];
-        const int h = two_limbs ? ((v + 128) >> 8) : 0;
-        const int l = v - (h << 8);
-        hw |= (static_cast<uint32_t>(h) & 0xffu) << (8 * e);
-        lw |= (static_cast<uint32_t>(l) & 0xffu) << (8 * e);
-      }
-      qh[w] = hw;
-      ql[w] = lw;
+      const uint32_t v0 = static_cast<uint32_t>(qi[4 * w]), v1 = static_cast<uint32_t>(qi[4 * w + 1]);
+      const uint32_t v2 = static_cast<uint32_t>(qi[4 * w + 2]), v3 = static_cast<uint32_t>(qi[4 * w + 3]);
+      ql[w] = prmt(prmt(v0, v1, 0x0040u), prmt(v2, v3, 0x0040u), 0x5410u);
+      qh[w] = two_limbs ? prmt(prmt(v0 + 128u, v1 + 128u, 0x0051u), prmt(v2 + 128u, v3 + 128u, 0x0051u), 0x5410u) : 0u;
     }
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
