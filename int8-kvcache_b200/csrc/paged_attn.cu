@@ -1284,6 +1284,7 @@ static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, cons
     return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
+  if (items >= (int64_t(1) << 31)) return INT8KV_E_UNSUPPORTED;  // the kernels number their items in 32 bits
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * per_warp + 1024;
   return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
@@ -1324,6 +1325,7 @@ static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtenso
   if (set_smem<(IS_BF16 ? 1 : 2) + (PLANNED ? 2 : 0)>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
+  if (items >= (int64_t(1) << 31)) return INT8KV_E_UNSUPPORTED;  // the kernels number their items in 32 bits
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * kF16Stages * 8192 + wpc * kF16Stages * 8 + 1024;
   return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
