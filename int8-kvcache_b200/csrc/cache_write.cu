@@ -148,15 +148,107 @@ __global__ void __launch_bounds__(256) cache_write_dynamic_kernel(const DynWrite
   }
 }
 
+// One element of the dynamic scheme: clamp(x / scale, +-127) rounded half away from zero, bit-identical to the
+// fp32 sequence divide, clamp, floor(q + 0.5) / ceil(q - 0.5).  The quotient comes from a multiplication by the
+// reciprocal, which is within a few ulp of the division; only where that could decide the rounding, within 1e-3 of
+// a half-integer, is the IEEE division done.
+__device__ __forceinline__ int quant_half_away(float x, float scale, float rscale) {
+  float q = x * rscale;
+  const float t = fabsf(q);
+  if (fabsf((t - floorf(t)) - 0.5f) < 1e-3f) q = __fdiv_rn(x, scale);
+  q = fminf(fmaxf(q, -127.f), 127.f);
+  return static_cast<int>(q >= 0.f ? floorf(q + 0.5f) : ceilf(q - 0.5f));
+}
+
+// Vector path of the dynamic scheme: D / 16 (a power of two, at most 32) consecutive lanes share one
+// (token, head) row; each holds 16 elements of K and of V, the row maxima are three to five shuffles, and the
+// bytes leave as 16-byte stores.  Same conditions on strides and alignment as the static vector path.
+template <typename T>
+__global__ void __launch_bounds__(256) cache_write_dynamic_vec_kernel(const DynWriteParams p, const uint32_t total,
+                                                                      const int chunk_shift) {
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool valid = idx < total;  // whole row groups are valid or not: total is a multiple of the group size
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const uint32_t chunks = 1u << chunk_shift;
+  const uint32_t row = idx >> chunk_shift;
+  const uint32_t c = idx & (chunks - 1);
+  const uint32_t t = row / static_cast<uint32_t>(p.Hkv);
+  const uint32_t h = row - t * static_cast<uint32_t>(p.Hkv);
+  int64_t slot = -1;
+  Raw16<T> kr, vr;
+  if (valid) {
+    slot = load_index(p.slots, p.slot_is_i64, t);
+    kr.load(reinterpret_cast<const T*>(p.key) + static_cast<int64_t>(t) * p.k_st[0] + h * p.k_st[1] + c * 16);
+    vr.load(reinterpret_cast<const T*>(p.value) + static_cast<int64_t>(t) * p.v_st[0] + h * p.v_st[1] + c * 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < Raw16<T>::kVecs; ++i) kr.v[i] = vr.v[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+  const T* ke = reinterpret_cast<const T*>(kr.v);
+  const T* ve = reinterpret_cast<const T*>(vr.v);
+  float kx[16], vx[16], kmax = 0.f, vmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    kx[i] = to_f32<T>(ke[i]);
+    vx[i] = to_f32<T>(ve[i]);
+    kmax = fmaxf(kmax, fabsf(kx[i]));
+    vmax = fmaxf(vmax, fabsf(vx[i]));
+  }
+  for (uint32_t o = 1; o < chunks; o <<= 1) {
+    kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+  }
+  if (!valid || slot < 0 || slot >= p.num_slots) return;
+  const float ks = fmaxf(__fdiv_rn(kmax, 127.f), 1e-6f), vs = fmaxf(__fdiv_rn(vmax, 127.f), 1e-6f);
+  const float rk = __frcp_rn(ks), rv = __frcp_rn(vs);
+  uint32_t kw[4], vw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    kw[i] = pack4_sat(quant_half_away(kx[4 * i], ks, rk), quant_half_away(kx[4 * i + 1], ks, rk),
+                      quant_half_away(kx[4 * i + 2], ks, rk), quant_half_away(kx[4 * i + 3], ks, rk));
+    vw[i] = pack4_sat(quant_half_away(vx[4 * i], vs, rv), quant_half_away(vx[4 * i + 1], vs, rv),
+                      quant_half_away(vx[4 * i + 2], vs, rv), quant_half_away(vx[4 * i + 3], vs, rv));
+  }
+  const int64_t blk = slot / p.block_size;
+  const int64_t off = slot - blk * p.block_size;
+  *reinterpret_cast<uint4*>(p.kc + blk * p.kc_st[0] + off * p.kc_st[1] + h * p.kc_st[2] + c * 16) =
+      make_uint4(kw[0], kw[1], kw[2], kw[3]);
+  *reinterpret_cast<uint4*>(p.vc + blk * p.vc_st[0] + off * p.vc_st[1] + h * p.vc_st[2] + c * 16) =
+      make_uint4(vw[0], vw[1], vw[2], vw[3]);
+  if (c == 0) {
+    p.ks[blk * p.ks_st[0] + off * p.ks_st[1] + h * p.ks_st[2]] = ks;
+    p.vs[blk * p.vs_st[0] + off * p.vs_st[1] + h * p.vs_st[2]] = vs;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 int launch_cache_write_dynamic(const DynWriteParams& p, cudaStream_t stream) {
   const int64_t rows = p.T * p.Hkv;
   if (rows <= 0) return INT8KV_OK;
+  const int esz = dtype_bytes(p.in_dtype);
+  const int per16 = 16 / esz;
+  const int chunks = p.D / 16;
+  const int64_t units = rows * chunks;
+  bool vec = (p.D % 16 == 0) && chunks >= 1 && chunks <= 32 && (chunks & (chunks - 1)) == 0 && p.k_st[2] == 1 &&
+             p.v_st[2] == 1 && p.kc_st[3] == 1 && p.vc_st[3] == 1 && aligned16(p.key) && aligned16(p.value) &&
+             aligned16(p.kc) && aligned16(p.vc) && units < (int64_t(1) << 31);
+  for (int i = 0; i < 2 && vec; ++i) vec = (p.k_st[i] % per16 == 0) && (p.v_st[i] % per16 == 0);
+  for (int i = 0; i < 3 && vec; ++i) vec = (p.kc_st[i] % 16 == 0) && (p.vc_st[i] % 16 == 0);
+  if (vec) {
+    int shift = 0;
+    while ((1 << shift) < chunks) ++shift;
+    const unsigned blocks = static_cast<unsigned>((units + 255) / 256);
+    const uint32_t total = static_cast<uint32_t>(units);
+    if (p.in_dtype == INT8KV_BF16) return launch_pdl(cache_write_dynamic_vec_kernel<__nv_bfloat16>, blocks, 256, 0, stream, p, total, shift);
+    if (p.in_dtype == INT8KV_FP16) return launch_pdl(cache_write_dynamic_vec_kernel<__half>, blocks, 256, 0, stream, p, total, shift);
+    return launch_pdl(cache_write_dynamic_vec_kernel<float>, blocks, 256, 0, stream, p, total, shift);
+  }
   const int64_t blocks = (rows + 7) / 8;  // 8 warps per CTA
   cache_write_dynamic_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
-
-static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream) {
   if (p.T == 0) return INT8KV_OK;

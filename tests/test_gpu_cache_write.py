@@ -163,11 +163,17 @@ def test_dynamic_per_token_head_write(kv):
 
     ops = package("vllm_int8.vllm_int8_cache_ops")
     g = torch.Generator().manual_seed(0)
-    for dtype, D in ((torch.bfloat16, 128), (torch.float16, 80), (torch.float32, 576)):
+    # D = 128, 64, 256, 512, 16 take the vector kernel (D / 16 lanes per row); 80 and 576 the general one
+    for dtype, D in ((torch.bfloat16, 128), (torch.float16, 80), (torch.float32, 576), (torch.float16, 64),
+                     (torch.float32, 256), (torch.bfloat16, 512), (torch.float32, 128), (torch.bfloat16, 16)):
         T, H = 23, 4
         key = torch.randn(T, H, D, generator=g).to(dtype)
         value = (torch.randn(T, H, D, generator=g) * 3).to(dtype)
         key[3, 1] = 0  # all-zero row: scale floors at 1e-6
+        # exact ties: absmax 127 makes the scale exactly 1, so x.5 sits on a rounding boundary (half away from zero)
+        ties = torch.tensor([127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, -126.5, 63.5, 0.25, -0.75, 3.0, -127.0, 8.5, -8.5])
+        key[4, 2, :16] = ties.to(dtype)
+        value[5, 0, :16] = (ties * 0.5).to(dtype)  # scale 0.5: the same quotients
         slots = torch.arange(7, 7 + T, dtype=torch.int64)
         slots[5] = -1
         kc, vc, ksc, vsc = ops.allocate_int8_kv_cache(32, 16, H, D, device="cuda")
