@@ -241,10 +241,17 @@ def bench_cache_write(kv, wl, device, args):
         sets.append((key, value, slots, ks, vs, kc, torch.zeros_like(kc)))
     valid = sum(int((s[2] >= 0).sum()) for s in sets) / len(sets)
     nbytes = 16384 * 4 * 128 * 4 + valid * 4 * 128 * 2 + 8 * 16384 + 32
+    dynamic = args.scales == "dynamic"
+    if dynamic:  # the per-(token, head) scheme: no input scales, one fp32 scale written per row of K and of V
+        nbytes += valid * 4 * 2 * 4 - 32
+        scale_caches = [(torch.zeros(s[5].shape[:3], device=device), torch.zeros(s[5].shape[:3], device=device)) for s in sets]
 
     def step():
-        for key, value, slots, ks, vs, kc, vc in sets:
-            kv.int8_kv_cache_write(key, value, kc, vc, slots, ks, vs)
+        for i, (key, value, slots, ks, vs, kc, vc) in enumerate(sets):
+            if dynamic:
+                kv.reshape_and_cache_int8(key, value, kc, vc, scale_caches[i][0], scale_caches[i][1], slots)
+            else:
+                kv.int8_kv_cache_write(key, value, kc, vc, slots, ks, vs)
 
     stream = torch.cuda.Stream(device)
     with torch.cuda.stream(stream):
@@ -271,14 +278,17 @@ def bench_cache_write(kv, wl, device, args):
     peak = float(json.loads(peaks_path.read_text())["hbm_gbs"]) if peaks_path.exists() else FALLBACK_PEAK_GBS
     gbs = nbytes / us / 1e3
     print(json.dumps({
-        "metric": "int8_kv_cache_write_achieved_hbm_gbps", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "metric": "int8_dynamic_scale_kv_cache_write_achieved_hbm_gbps" if dynamic else "int8_kv_cache_write_achieved_hbm_gbps",
+        "value": gbs, "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us * len(sets) / 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic", "us_per_call": us, "gpu_launches": len(sets) * args.steps,
         "config": {"workload": "c3: prefill cache write, 16384 tokens x 4 heads x 128, permuted 1024-block pool, "
                                "~3% slots = -1, 8 rotated sets (larger than L2)"},
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
-                     "traffic": None, "kernel": "cache_write_vec_kernel<bf16>", "algorithmic_bytes_per_call": nbytes},
+                     "traffic": None,
+                     "kernel": "cache_write_dynamic_vec_kernel<bf16>" if dynamic else "cache_write_vec_kernel<bf16>",
+                     "algorithmic_bytes_per_call": nbytes},
     }))
 
 
