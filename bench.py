@@ -292,6 +292,68 @@ def bench_cache_write(kv, wl, device, args):
     }))
 
 
+def _time_graph(fn, stream, steps, warmup):
+    """ms per replay of `fn` captured as a CUDA graph on `stream` (CUDA events on that stream)."""
+    with torch.cuda.stream(stream):
+        fn()
+        fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        for _ in range(max(warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def bench_sweep(kv, wl, device, args):
+    """The whole single-GPU sweep of BASELINE config 2 (B in {1,2,4,8} x seq in {512,1024,2048,4096}, the grid of
+    the reference's bench/bench_paged_attention.py): microseconds per call for the INT8 kernels and the same-run
+    BF16 baseline, each cell rotated over enough distinct layer caches to exceed the L2."""
+    hq, hkv = wl.QWEN25_7B.num_q_heads, wl.QWEN25_7B.num_kv_heads
+    stream = torch.cuda.Stream(device)
+    cells = []
+    for B in (1, 2, 4, 8):
+        for seq in (512, 1024, 2048, 4096):
+            cell_bytes = B * seq * hkv * 128 * 2 * 3  # INT8 and BF16 caches of one layer
+            layers = max(4, min(64, int(600e6 / cell_bytes)))
+            L = build_layers(kv, wl, device, hq, hkv, [seq] * B, layers, seed=5, with_bf16=True)
+
+            def int8_step():
+                for x in L:
+                    kv.int8_paged_attention(x.query, x.kc, x.vc, x.block_tables, x.seq_lens, x.k_scale, x.v_scale,
+                                            max_seq_len=seq, out=x.out)
+
+            def bf16_step():
+                for x in L:
+                    kv.bf16_paged_attention(x.query, x.kb, x.vb, x.block_tables, x.seq_lens, max_seq_len=seq, out=x.out)
+
+            i8 = _time_graph(int8_step, stream, args.steps, args.warmup) / layers * 1e3
+            bf = _time_graph(bf16_step, stream, args.steps, args.warmup) / layers * 1e3
+            nb = algorithmic_bytes([seq] * B, hq, hkv)
+            cells.append({"batch": B, "seq_len": seq, "layer_caches": layers, "int8_us": i8, "bf16_us": bf,
+                          "int8_speedup": bf / i8, "int8_gbs": nb / i8 / 1e3})
+            del L
+            torch.cuda.empty_cache()
+    top = cells[-1]
+    print(json.dumps({
+        "metric": "int8_paged_decode_attn_achieved_hbm_gbps", "value": top["int8_gbs"], "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": top["int8_us"] * top["layer_caches"] / 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "c2 sweep: B in {1,2,4,8} x seq in {512,1024,2048,4096}, value = the largest cell",
+                   "Hq": hq, "Hkv": hkv, "head_dim": 128, "block_size": 16,
+                   "l2": "inputs larger than L2: each call reads a different layer's cache"},
+        "us_per_call": top["int8_us"], "cells": cells, "device_status": kv.device_status(device),
+    }))
+
+
 def bench_sequence_parallel(kv, wl, device, args, rank, world, hq, hkv, seq_lens, config, metric):
     """Long-context sequence split: rank r holds blocks [r*per, (r+1)*per) of every sequence in its own cache (all KV
     heads); one step = partial attention over the local tokens, NCCL all-gather of the [B, Hq, D+4] fp32 partial
@@ -389,6 +451,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--scales", default="static", choices=["static", "dynamic"],
                     help="dynamic: time the attention over per-(token, head) scale caches (device leg only)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="c2 only, one GPU: time all 16 cells of the sweep, INT8 and BF16, and list them under `cells`")
     ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
     ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
     args = ap.parse_args()
@@ -437,6 +501,10 @@ def main():
     device = torch.device("cuda", local_rank)
     if args.workload == "c3":
         return bench_cache_write(kv, wl, device, args)
+    if args.sweep:
+        if args.workload != "c2" or world > 1:
+            raise SystemExit("--sweep runs the c2 grid on one GPU")
+        return bench_sweep(kv, wl, device, args)
     if world > 1:
         import torch.distributed as dist
 
