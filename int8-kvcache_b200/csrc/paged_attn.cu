@@ -65,6 +65,7 @@ struct TileRing {
   int cur_win;
   int bt_cur, bt_next;
   int lane;
+  uint64_t kv_policy;  // L2 policy of the tile loads: every page is read once
   // DYN only
   uint32_t scale0;        // shared address of the first 128-byte scale slot
   const float* sc_src;    // this lane's scale cache (lanes 0-15: K, 16-31: V), offset to the lane's head
@@ -82,6 +83,7 @@ struct TileRing {
   // Barrier set-up: touches shared memory only, so it may run before the grid dependency is resolved.
   __device__ __forceinline__ void init_barriers(int lane_) {
     lane = lane_;
+    kv_policy = l2_evict_first_policy();
     if (lane == 0) {
 #pragma unroll
       for (int s = 0; s < NST; ++s) mbar_init(bar0 + 8 * s, DYN ? 1 + kWarp : 1);
@@ -138,10 +140,10 @@ struct TileRing {
       mbar_expect_tx(bar, STAGE_BYTES);
 #pragma unroll
       for (int x = 0; x < LOADS_PER_TENSOR; ++x)
-        tma_load_4d(dst + x * 2048, tmK, bar, x * 128, sub * kTile, head, blk);
+        tma_load_4d(dst + x * 2048, tmK, bar, x * 128, sub * kTile, head, blk, kv_policy);
 #pragma unroll
       for (int x = 0; x < LOADS_PER_TENSOR; ++x)
-        tma_load_4d(dst + (LOADS_PER_TENSOR + x) * 2048, tmV, bar, x * 128, sub * kTile, head, blk);
+        tma_load_4d(dst + (LOADS_PER_TENSOR + x) * 2048, tmV, bar, x * 128, sub * kTile, head, blk, kv_policy);
     }
   }
 
