@@ -37,7 +37,7 @@ if str(REPO) not in sys.path:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch, from a one-pass ncu capture of
 # this script's default workload (the launch-list summary under profiles/)
-NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33690734}
+NCU_DRAM_TRAFFIC_PER_LAUNCH = {"c2": 33690154}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 
