@@ -417,7 +417,8 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
 
 // PLANNED: the items come from plan_in_warp instead of being numbered arithmetically.  A template parameter rather
 // than a run-time test, so that the kernel that serves small calls does not carry the planning code.
-template <int NST, int MODE, bool PLANNED>
+// QQ: the reference's optional INT8 query (quantize_q), one limb; its own instantiation as well.
+template <int NST, int MODE, bool PLANNED, bool QQ>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p) {
@@ -519,7 +520,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   // INT8 query (absmax/127, half away from zero) sits in the low limb alone.
   uint32_t qh[8], ql[8];
   float q_mul;
-  const bool two_limbs = !p.quantize_q;
+  constexpr bool two_limbs = !QQ;
   {
     float qv[32];
     const int hq = it.h * p.G + g;
@@ -535,7 +536,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
     amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
     int qi[32];
-    if (p.quantize_q) {
+    if constexpr (QQ) {
       const float qs = fmaxf(amax / 127.f, 1e-6f);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
@@ -1277,12 +1278,12 @@ static int pick_wpc(int64_t items, int sm_count) {
 }
 
 // One instantiation of the INT8 kernel: raises its dynamic shared-memory limit once, sizes the grid, launches.
-template <int NST, int MODE, bool PLANNED>
+template <int NST, int MODE, bool PLANNED, bool QQ = false>
 static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                                cudaStream_t stream) {
   constexpr int per_warp = NST * (4096 + 8 + (MODE == kDynScales ? 128 : 0));  // stages, barriers, scale slots
-  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED>;
-  if (set_smem<100 + NST * 8 + MODE * 2 + (PLANNED ? 1 : 0)>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
+  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED, QQ>;
+  if (set_smem<100 + NST * 16 + MODE * 4 + (PLANNED ? 2 : 0) + (QQ ? 1 : 0)>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
     return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
@@ -1308,6 +1309,9 @@ int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CU
   if (p.ks_cache != nullptr)
     return planned ? launch_int8_variant<N, kDynScales, true>(p, tmK, tmV, sm_count, stream)
                    : launch_int8_variant<N, kDynScales, false>(p, tmK, tmV, sm_count, stream);
+  if (p.quantize_q && p.new_k == nullptr)  // the INT8 query exists with the default ring depth only
+    return planned ? launch_int8_variant<N, kPlain, true, true>(p, tmK, tmV, sm_count, stream)
+                   : launch_int8_variant<N, kPlain, false, true>(p, tmK, tmV, sm_count, stream);
   if (planned)
     return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, true>(p, tmK, tmV, sm_count, stream)
                               : launch_int8_variant<N, kPlain, true>(p, tmK, tmV, sm_count, stream);
