@@ -41,8 +41,11 @@ __device__ __forceinline__ int64_t load_index(const void* base, int is_i64, int6
 }
 
 // 32 consecutive elements of a float tensor starting at element `off` (element stride `stride`) -> floats;
-// 16-byte vector loads when the run is contiguous and aligned.
-__device__ __forceinline__ void load32_as_float(const void* base, int dtype, int64_t off, int64_t stride, float (&x)[32]) {
+// 16-byte vector loads when the run is contiguous and aligned.  Any other layout goes element by element through
+// `scratch` (shared memory, 128 bytes per lane, free at the time of the call) in a loop that is not unrolled: the
+// rare path then costs a few dozen instructions of code instead of several hundred.
+__device__ __forceinline__ void load32_as_float(const void* base, int dtype, int64_t off, int64_t stride, float (&x)[32],
+                                                uint32_t scratch, int lane) {
   const int esz = dtype == INT8KV_FP32 ? 4 : 2;
   const char* ptr = reinterpret_cast<const char*>(base) + off * esz;
   if (stride == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) {
@@ -68,13 +71,25 @@ __device__ __forceinline__ void load32_as_float(const void* base, int dtype, int
       }
     }
   } else {
+    const uint32_t mine = scratch + lane * 128;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      const float v = load_as_float(base, dtype, off + i * stride);
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(mine + 4 * i), "f"(v) : "memory");
+    }
 #pragma unroll
-    for (int i = 0; i < 32; ++i) x[i] = load_as_float(base, dtype, off + i * stride);
+    for (int i = 0; i < 8; ++i) {
+      float4 v;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(mine + 16 * i) : "memory");
+      x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+    }
   }
 }
 
-// 16 consecutive output elements from floats; 16-byte vector stores when contiguous and aligned.
-__device__ __forceinline__ void store16_from_float(void* base, int dtype, int64_t off, int64_t stride, const float (&x)[16]) {
+// 16 consecutive output elements from floats; 16-byte vector stores when contiguous and aligned, else element by
+// element through `scratch` (shared memory, 64 bytes per lane) in a rolled loop.
+__device__ __forceinline__ void store16_from_float(void* base, int dtype, int64_t off, int64_t stride, const float (&x)[16],
+                                                   uint32_t scratch, int lane) {
   const int esz = dtype == INT8KV_FP32 ? 4 : 2;
   char* ptr = reinterpret_cast<char*>(base) + off * esz;
   if (stride == 1 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) {
@@ -98,8 +113,18 @@ __device__ __forceinline__ void store16_from_float(void* base, int dtype, int64_
       reinterpret_cast<uint4*>(ptr)[1] = make_uint4(w[4], w[5], w[6], w[7]);
     }
   } else {
+    const uint32_t mine = scratch + lane * 64;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) store_from_float(base, dtype, off + i * stride, x[i]);
+    for (int i = 0; i < 4; ++i)
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16 * i), "f"(x[4 * i]), "f"(x[4 * i + 1]),
+                   "f"(x[4 * i + 2]), "f"(x[4 * i + 3])
+                   : "memory");
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+      float v;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(mine + 4 * i) : "memory");
+      store_from_float(base, dtype, off + i * stride, v);
+    }
   }
 }
 

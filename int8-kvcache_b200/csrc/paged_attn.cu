@@ -510,6 +510,18 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     }
   }
 
+  // The query is requested first (a strided or unaligned one is staged through the ring's first stage, which must
+  // therefore still be idle), then the first tiles; the query's arithmetic runs while the tiles are in flight.
+  float qv[32];
+  if (g < p.G) {
+    const int hq = it.h * p.G + g;
+    load32_as_float(p.q, p.q_dtype, it.b * p.q_st[0] + hq * p.q_st[1] + 32 * t * p.q_st[2], p.q_st[2], qv, ring.stage0, lane);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) qv[i] = 0.f;
+  }
+  __syncwarp();  // every lane is done with the staging area before the first tile may land in it
+
   const int n = it.t1 - it.t0;
   const int pre = n < NST ? n : NST;
   for (int i = 0; i < pre; ++i) ring.issue(i);
@@ -522,14 +534,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   float q_mul;
   constexpr bool two_limbs = !QQ;
   {
-    float qv[32];
-    const int hq = it.h * p.G + g;
-    if (g < p.G) {
-      load32_as_float(p.q, p.q_dtype, it.b * p.q_st[0] + hq * p.q_st[1] + 32 * t * p.q_st[2], p.q_st[2], qv);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) qv[i] = 0.f;
-    }
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(qv[i]));
@@ -756,7 +760,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       o[2 * j + 1] = acc[j][e + 2] * inv;
     }
     if (prow == nullptr) {
-      store16_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + 16 * g * p.o_st[2], p.o_st[2], o);
+      store16_from_float(p.out, p.out_dtype, it.b * p.o_st[0] + hq * p.o_st[1] + 16 * g * p.o_st[2], p.o_st[2], o, ring.stage0, lane);
     } else {
       float* row = prow + hg * p.row_floats;
       float4* dst = reinterpret_cast<float4*>(row + 16 * g);
