@@ -853,17 +853,29 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   {
     const int hq = it.h * p.G + g;
     const int64_t base = it.b * p.q_st[0] + hq * p.q_st[1];
+    // a query already in the cache's 16-bit type, contiguous and 4-byte aligned, is the fragment as it lies in memory
+    const bool same_type = p.q_dtype == (IS_BF16 ? INT8KV_BF16 : INT8KV_FP16) && p.q_st[2] == 1 &&
+                           ((reinterpret_cast<uintptr_t>(p.q) + 2 * base) & 3u) == 0;
+    if (g >= p.G) {
 #pragma unroll
-    for (int s = 0; s < 8; ++s) {
-      float a = 0.f, b = 0.f, c = 0.f, d = 0.f;
-      if (g < p.G) {
-        a = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t) * p.q_st[2]);
-        b = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t + 1) * p.q_st[2]);
-        c = load_as_float(p.q, p.q_dtype, base + (16 * s + 8 + 2 * t) * p.q_st[2]);
-        d = load_as_float(p.q, p.q_dtype, base + (16 * s + 9 + 2 * t) * p.q_st[2]);
+      for (int s = 0; s < 16; ++s) qf[s] = 0u;
+    } else if (same_type) {
+      const uint32_t* words = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.q) + base);
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        qf[2 * s] = __ldg(words + 8 * s + t);
+        qf[2 * s + 1] = __ldg(words + 8 * s + 4 + t);
       }
-      qf[2 * s] = pack16<IS_BF16>(a, b);
-      qf[2 * s + 1] = pack16<IS_BF16>(c, d);
+    } else {
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float a = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t) * p.q_st[2]);
+        const float b = load_as_float(p.q, p.q_dtype, base + (16 * s + 2 * t + 1) * p.q_st[2]);
+        const float c = load_as_float(p.q, p.q_dtype, base + (16 * s + 8 + 2 * t) * p.q_st[2]);
+        const float d = load_as_float(p.q, p.q_dtype, base + (16 * s + 9 + 2 * t) * p.q_st[2]);
+        qf[2 * s] = pack16<IS_BF16>(a, b);
+        qf[2 * s + 1] = pack16<IS_BF16>(c, d);
+      }
     }
   }
   const float sc = p.sm_scale_log2;
