@@ -40,6 +40,33 @@ __device__ __forceinline__ int64_t load_index(const void* base, int is_i64, int6
                 : static_cast<int64_t>(reinterpret_cast<const int32_t*>(base)[idx]);
 }
 
+// Four consecutive elements -> floats: one vector load when contiguous and aligned (a scalar load per element with
+// its own dtype branch keeps the compiler from overlapping the loads).
+__device__ __forceinline__ void load4_as_float(const void* base, int dtype, int64_t off, int64_t stride, float (&x)[4]) {
+  const int esz = dtype == INT8KV_FP32 ? 4 : 2;
+  const char* ptr = reinterpret_cast<const char*>(base) + off * esz;
+  if (stride == 1 && (reinterpret_cast<uintptr_t>(ptr) & static_cast<uintptr_t>(4 * esz - 1)) == 0) {
+    if (dtype == INT8KV_FP32) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(ptr));
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(ptr));
+      float2 lo, hi;
+      if (dtype == INT8KV_BF16) {
+        lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+        hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+      } else {
+        lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      }
+      x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) x[i] = load_as_float(base, dtype, off + i * stride);
+  }
+}
+
 // 32 consecutive elements of a float tensor starting at element `off` (element stride `stride`) -> floats;
 // 16-byte vector loads when the run is contiguous and aligned.  Any other layout goes element by element through
 // `scratch` (shared memory, 128 bytes per lane, free at the time of the call) in a loop that is not unrolled: the

@@ -502,11 +502,8 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     if (owns_new) {
       new_slot = load_index(p.new_slots, p.new_slot_is_i64, it.b);
       last_blk = load_index(p.bt, p.bt_is_i64, it.b * p.bt_st[0] + ((it.seq_len - 1) / p.block_size) * p.bt_st[1]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        nk[e] = load_as_float(p.new_k, p.new_dtype, it.b * p.nk_st[0] + it.h * p.nk_st[1] + (4 * lane + e) * p.nk_st[2]);
-        nv[e] = load_as_float(p.new_v, p.new_dtype, it.b * p.nv_st[0] + it.h * p.nv_st[1] + (4 * lane + e) * p.nv_st[2]);
-      }
+      load4_as_float(p.new_k, p.new_dtype, it.b * p.nk_st[0] + it.h * p.nk_st[1] + 4 * lane * p.nk_st[2], p.nk_st[2], nk);
+      load4_as_float(p.new_v, p.new_dtype, it.b * p.nv_st[0] + it.h * p.nv_st[1] + 4 * lane * p.nv_st[2], p.nv_st[2], nv);
     }
   }
 
