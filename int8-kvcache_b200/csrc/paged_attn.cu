@@ -491,21 +491,12 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   if constexpr (DYN) ring.seq_len = it.seq_len;
 
   // Fused decode step: the warp whose range ends with the sequence's last tile owns the step's new K/V row of
-  // this head.  Everything it needs is requested here, long before the tile arrives: the row (4 elements per
-  // lane), its slot, and the physical block of the last token.
+  // this head.  Everything it needs is requested right after the first tile loads below, long before the tile
+  // arrives: the row (4 elements per lane), its slot, and the physical block of the last token.
   const int last_rel = ((it.seq_len - 1) >> 4) - it.t0;  // ordinal of the last tile inside this range, if any
   bool owns_new = false;
   float nk[4], nv[4];
   int64_t new_slot = -1, last_blk = -1;
-  if constexpr (FUSED_WRITE) {
-    owns_new = last_rel >= 0 && last_rel < it.t1 - it.t0;
-    if (owns_new) {
-      new_slot = load_index(p.new_slots, p.new_slot_is_i64, it.b);
-      last_blk = load_index(p.bt, p.bt_is_i64, it.b * p.bt_st[0] + ((it.seq_len - 1) / p.block_size) * p.bt_st[1]);
-      load4_as_float(p.new_k, p.new_dtype, it.b * p.nk_st[0] + it.h * p.nk_st[1] + 4 * lane * p.nk_st[2], p.nk_st[2], nk);
-      load4_as_float(p.new_v, p.new_dtype, it.b * p.nv_st[0] + it.h * p.nv_st[1] + 4 * lane * p.nv_st[2], p.nv_st[2], nv);
-    }
-  }
 
   // The query is requested first (a strided or unaligned one is staged through the ring's first stage, which must
   // therefore still be idle), then the first tiles; the query's arithmetic runs while the tiles are in flight.
@@ -522,6 +513,15 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const int n = it.t1 - it.t0;
   const int pre = n < NST ? n : NST;
   for (int i = 0; i < pre; ++i) ring.issue(i);
+  if constexpr (FUSED_WRITE) {  // after the tile loads, so that none of these reads delays them
+    owns_new = last_rel >= 0 && last_rel < it.t1 - it.t0;
+    if (owns_new) {
+      new_slot = load_index(p.new_slots, p.new_slot_is_i64, it.b);
+      last_blk = load_index(p.bt, p.bt_is_i64, it.b * p.bt_st[0] + ((it.seq_len - 1) / p.block_size) * p.bt_st[1]);
+      load4_as_float(p.new_k, p.new_dtype, it.b * p.nk_st[0] + it.h * p.nk_st[1] + 4 * lane * p.nk_st[2], p.nk_st[2], nk);
+      load4_as_float(p.new_v, p.new_dtype, it.b * p.nv_st[0] + it.h * p.nv_st[1] + 4 * lane * p.nv_st[2], p.nv_st[2], nv);
+    }
+  }
 
   // ---- Q as two INT8 limbs: lane (g, t) holds head g of the group, dims [32t, 32t+32), 4 dims per word ----
   // q ~= q_mul * (256 * hi + lo) with |256 hi + lo| <= 32000: 16-bit fixed point per head, finer than the bf16
@@ -563,7 +563,8 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     }
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
-  const float kmul = DYN ? p.sm_scale_log2 : fmaxf(__ldg(p.k_scale + it.h), 1e-6f) * p.sm_scale_log2;
+  const float k_scale_head = DYN ? 1.f : fmaxf(__ldg(p.k_scale + it.h), 1e-6f);
+  const float kmul = k_scale_head * p.sm_scale_log2;
   // requested here, used in the epilogue: a load issued there would put its whole latency on the critical path
   const float v_scale_head = DYN ? 1.f : fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
   const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
@@ -602,7 +603,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (owns_new && (last_rel == i || last_rel == i + 1)) {
         // quantise the new row exactly as the cache-write kernel does, store it to the cache, and overwrite the
         // row in the staged tile (TMA fetched the tile before this store, so the stage still holds the old bytes)
-        const float ks = fmaxf(__ldg(p.k_scale + it.h), 1e-6f), vsn = fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
+        const float ks = k_scale_head, vsn = v_scale_head;  // loaded in the prologue
         const float rk = __frcp_rn(ks), rv = __frcp_rn(vsn);
         const uint32_t kw = pack4_sat(quant1(nk[0], ks, rk), quant1(nk[1], ks, rk), quant1(nk[2], ks, rk), quant1(nk[3], ks, rk));
         const uint32_t vw = pack4_sat(quant1(nv[0], vsn, rv), quant1(nv[1], vsn, rv), quant1(nv[2], vsn, rv), quant1(nv[3], vsn, rv));
