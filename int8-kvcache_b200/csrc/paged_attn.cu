@@ -34,6 +34,7 @@
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <utility>
 
 #include "common.cuh"
@@ -1016,6 +1017,17 @@ __device__ __forceinline__ float cache_elem(const void* base, int kind, int64_t 
   return __half2float(reinterpret_cast<const __half*>(base)[idx]);
 }
 
+// KIND: cache element type (no per-element dtype branch); SLOTS: elements per lane, head_dim <= 32 * SLOTS.
+// Four tokens per iteration: their loads, dot products and reductions are independent, one softmax update serves
+// all four.
+template <int KIND>
+__device__ __forceinline__ float generic_elem(const void* base, int64_t idx) {
+  if constexpr (KIND == kCacheInt8) return static_cast<float>(__ldg(reinterpret_cast<const int8_t*>(base) + idx));
+  else if constexpr (KIND == kCacheBf16) return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + idx));
+  else return __half2float(__ldg(reinterpret_cast<const __half*>(base) + idx));
+}
+
+template <int KIND, int SLOTS>
 __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParams p) {
   grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1037,11 +1049,10 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
   if (tok_hi > sl) tok_hi = sl;
   const int64_t row = (static_cast<int64_t>(c) * p.B + b) * p.Hq + hq;
 
-  constexpr int kSlots = kGenericMaxD / kWarp;
-  float q[kSlots], acc[kSlots];
+  float q[SLOTS], acc[SLOTS];
   float q_mul = 1.f;
 #pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
+  for (int s = 0; s < SLOTS; ++s) {
     const int d = lane + kWarp * s;
     q[s] = d < p.D ? load_as_float(p.q, p.q_dtype, b * p.q_st[0] + hq * p.q_st[1] + d * p.q_st[2]) : 0.f;
     acc[s] = 0.f;
@@ -1049,11 +1060,11 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
   if (p.quantize_q) {
     float amax = 0.f;
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) amax = fmaxf(amax, fabsf(q[s]));
+    for (int s = 0; s < SLOTS; ++s) amax = fmaxf(amax, fabsf(q[s]));
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
     const float qs = fmaxf(amax / 127.f, 1e-6f);
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
+    for (int s = 0; s < SLOTS; ++s) {
       const float x = q[s] / qs;
       const float r = x >= 0.f ? floorf(x + 0.5f) : -floorf(-x + 0.5f);
       q[s] = fminf(fmaxf(r, -127.f), 127.f);
@@ -1063,41 +1074,87 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
   const float ks = p.k_scale ? fmaxf(__ldg(p.k_scale + hkv), 1e-6f) : 1.f;
   const float vs = p.v_scale ? fmaxf(__ldg(p.v_scale + hkv), 1e-6f) : 1.f;
   const float sc = ks * q_mul * p.sm_scale_log2;
+  const bool dyn = p.ks_cache != nullptr;
   float m = -INFINITY, l = 0.f;
-  for (int64_t tok = tok_lo; tok < tok_hi; ++tok) {
-    const int64_t lb = tok / p.block_size;
-    const int64_t off = tok - lb * p.block_size;
-    const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
-    if (blk < 0 || blk >= p.num_blocks) continue;  // never read outside the cache
-    const int64_t kof = blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
-    const int64_t vof = blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
-    float kt = 1.f, vt = 1.f;  // per-token scales of the dynamic scheme
-    if (p.ks_cache != nullptr) {
-      kt = __ldg(p.ks_cache + blk * p.ks_st[0] + off * p.ks_st[1] + hkv * p.ks_st[2]);
-      vt = __ldg(p.vs_cache + blk * p.vs_st[0] + off * p.vs_st[1] + hkv * p.vs_st[2]);
-    }
-    float dot = 0.f;
+  constexpr int kTok = 4;
+  for (int64_t tok = tok_lo; tok < tok_hi; tok += kTok) {
+    bool ok[kTok];
+    int64_t kof[kTok], vof[kTok];
+    float kt[kTok], vt[kTok], dot[kTok];
+    int64_t lb = tok / p.block_size;  // one division per four tokens; the others step from it
+    int off = static_cast<int>(tok - lb * p.block_size);
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      const int d = lane + kWarp * s;
-      if (d < p.D) dot += q[s] * cache_elem(p.kc, p.cache_kind, kof + d * p.kc_st[3]);
+    for (int u = 0; u < kTok; ++u) {
+      const int64_t t = tok + u;
+      ok[u] = t < tok_hi;
+      kof[u] = vof[u] = 0;
+      kt[u] = vt[u] = 1.f;
+      dot[u] = 0.f;
+      if (u > 0) {
+        ++off;
+        while (off >= p.block_size) {
+          off -= p.block_size;
+          ++lb;
+        }
+      }
+      if (ok[u]) {
+        const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+        ok[u] = blk >= 0 && blk < p.num_blocks;  // never read outside the cache
+        if (ok[u]) {
+          kof[u] = blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
+          vof[u] = blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
+          if (dyn) {  // per-token scales of the dynamic scheme
+            kt[u] = __ldg(p.ks_cache + blk * p.ks_st[0] + off * p.ks_st[1] + hkv * p.ks_st[2]);
+            vt[u] = __ldg(p.vs_cache + blk * p.vs_st[0] + off * p.vs_st[1] + hkv * p.vs_st[2]);
+          }
+        }
+      }
     }
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(kFull, dot, o);
-    const float sv = dot * sc * kt;
-    const float mn = fmaxf(m, sv);
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
+      const int d = lane + kWarp * s;
+      if (d < p.D) {
+#pragma unroll
+        for (int u = 0; u < kTok; ++u)
+          if (ok[u]) dot[u] += q[s] * generic_elem<KIND>(p.kc, kof[u] + d * p.kc_st[3]);
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < kTok; ++u) dot[u] += __shfl_xor_sync(kFull, dot[u], o);
+    }
+    float sv[kTok], mn = m;
+#pragma unroll
+    for (int u = 0; u < kTok; ++u) {
+      sv[u] = ok[u] ? dot[u] * sc * kt[u] : -INFINITY;
+      mn = fmaxf(mn, sv[u]);
+    }
+    if (mn == -INFINITY) continue;  // nothing valid so far
     const float al = exp2f(m - mn);
-    const float pe = exp2f(sv - mn);
-    l = l * al + pe;
+    float pe[kTok], sum = 0.f;
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
+    for (int u = 0; u < kTok; ++u) {
+      pe[u] = ok[u] ? exp2f(sv[u] - mn) : 0.f;
+      sum += pe[u];
+      pe[u] *= vt[u];
+    }
+    l = l * al + sum;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) {
       const int d = lane + kWarp * s;
-      if (d < p.D) acc[s] = acc[s] * al + (pe * vt) * cache_elem(p.vc, p.cache_kind, vof + d * p.vc_st[3]);
+      if (d < p.D) {
+        float a = acc[s] * al;
+#pragma unroll
+        for (int u = 0; u < kTok; ++u)
+          if (ok[u]) a += pe[u] * generic_elem<KIND>(p.vc, vof[u] + d * p.vc_st[3]);
+        acc[s] = a;
+      }
     }
     m = mn;
   }
   const float inv = l > 0.f ? vs / l : 0.f;
 #pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
+  for (int s = 0; s < SLOTS; ++s) {
     const int d = lane + kWarp * s;
     if (d >= p.D) continue;
     if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[s] * inv);
@@ -1105,6 +1162,224 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
   }
   if (p.part != nullptr && lane == 0)
     p.part[row * p.row_floats + p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouped kernel for INT8 caches outside the tiled kernels' shapes (head_dim != 128, odd block sizes): one warp per
+// (sequence, KV head, split) serves the whole GQA group from one read of the pages, with plain loads.
+//   scores: lane = token.  Each lane walks its token's K row four elements at a time against the group's queries,
+//           which sit pre-scaled in shared memory and are read as broadcasts: no shuffle per dot product.
+//   softmax: per head over the 32 tokens of a step (warp max and sum).
+//   P.V:    lane = dims lane, lane + 32, ...  Token by token the probabilities are broadcast by shuffle and the V
+//           row is read coalesced.
+// GM bounds the group (registers per head), E = elements per lane; head_dim % 4 == 0, head_dim <= 32 * E.
+// ---------------------------------------------------------------------------------------------
+// Byte i of a word of four INT8 values (already XORed with 0x80808080) as a float, without the conversion unit:
+// the byte becomes the low mantissa of 2^23 * 1.5 and the offset is subtracted on the FP32 adder.
+template <int I>
+__device__ __forceinline__ float s8_of_word(uint32_t biased) {
+  return __uint_as_float(prmt(biased, 0x4B400000u, 0x7650u | I)) - 12583040.f;  // 12582912 + 128
+}
+
+template <int GM, int E>
+__global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) float q_smem[];
+  grid_dependency_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  const int64_t total = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+  if (item >= total) return;
+  const int hkv = static_cast<int>(item % p.Hkv);
+  const int64_t rr = item / p.Hkv;
+  const int c = static_cast<int>(rr % p.num_splits);
+  const int b = static_cast<int>(rr / p.num_splits);
+  const int G = p.G, D = p.D;
+  int64_t sl = load_index(p.sl, p.sl_is_i64, b);
+  const int64_t cap = p.bt_width * p.block_size;
+  sl = sl > cap ? cap : (sl < 0 ? 0 : sl);
+  const int64_t nblk = (sl + p.block_size - 1) / p.block_size;
+  const int64_t per = (nblk + p.num_splits - 1) / p.num_splits;
+  const int64_t tok_lo = c * per * p.block_size;
+  int64_t tok_hi = (c + 1) * per * p.block_size;
+  if (tok_hi > sl) tok_hi = sl;
+
+  // queries of the group, multiplied by everything that is constant per head, into this warp's shared memory
+  float* qs = q_smem + warp * (GM * 32 * E);
+  const float ksc = p.k_scale ? fmaxf(__ldg(p.k_scale + hkv), 1e-6f) : 1.f;
+  const float vsc = p.v_scale ? fmaxf(__ldg(p.v_scale + hkv), 1e-6f) : 1.f;
+  for (int g = 0; g < G; ++g) {
+    const int hq = hkv * G + g;
+    float x[E];
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int d = lane + kWarp * e;
+      x[e] = d < D ? load_as_float(p.q, p.q_dtype, b * p.q_st[0] + hq * p.q_st[1] + d * p.q_st[2]) : 0.f;
+      amax = fmaxf(amax, fabsf(x[e]));
+    }
+    float mul = ksc * p.sm_scale_log2;
+    if (p.quantize_q) {
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
+      const float qscale = fmaxf(amax / 127.f, 1e-6f);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float y = x[e] / qscale;
+        const float r = y >= 0.f ? floorf(y + 0.5f) : -floorf(-y + 0.5f);
+        x[e] = fminf(fmaxf(r, -127.f), 127.f);
+      }
+      mul *= qscale;
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int d = lane + kWarp * e;
+      if (d < D) qs[g * D + d] = x[e] * mul;
+    }
+  }
+  __syncwarp();
+
+  const bool dyn = p.ks_cache != nullptr;
+  float m[GM], l[GM], acc[GM][E];
+#pragma unroll
+  for (int g = 0; g < GM; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+  }
+  const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc);
+  const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc);
+
+  for (int64_t tok0 = tok_lo; tok0 < tok_hi; tok0 += kWarp) {
+    // ---- scores of token tok0 + lane against every head of the group ----
+    const int64_t t = tok0 + lane;
+    bool ok = t < tok_hi;
+    int64_t blk = -1;
+    int off = 0;
+    if (ok) {
+      const int64_t lb = t / p.block_size;
+      off = static_cast<int>(t - lb * p.block_size);
+      blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+      ok = blk >= 0 && blk < p.num_blocks;  // never read outside the cache
+    }
+    float sc[GM];
+#pragma unroll
+    for (int g = 0; g < GM; ++g) sc[g] = 0.f;
+    float vt = 1.f;
+    if (ok) {
+      const int8_t* krow = kc + blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
+      const bool aligned = (reinterpret_cast<uintptr_t>(krow) & 3u) == 0;
+      // 64 elements at a time: all sixteen loads are issued before the first is used
+      for (int d0 = 0; d0 < D; d0 += 64) {
+        int w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int d = d0 + 4 * i;
+          w[i] = 0;
+          if (d < D) {
+            if (aligned) {
+              w[i] = __ldg(reinterpret_cast<const int*>(krow + d));
+            } else {
+              w[i] = (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d)))) |
+                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 1))) << 8) |
+                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 2))) << 16) |
+                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 3))) << 24);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int d = d0 + 4 * i;
+          if (d < D) {
+            const uint32_t kb = static_cast<uint32_t>(w[i]) ^ 0x80808080u;
+            const float k0 = s8_of_word<0>(kb), k1 = s8_of_word<1>(kb), k2 = s8_of_word<2>(kb), k3 = s8_of_word<3>(kb);
+#pragma unroll
+            for (int g = 0; g < GM; ++g) {
+              if (g < G) {
+                const float4 qv = *reinterpret_cast<const float4*>(qs + g * D + d);  // same address in every lane
+                sc[g] += k0 * qv.x + k1 * qv.y + k2 * qv.z + k3 * qv.w;
+              }
+            }
+          }
+        }
+      }
+      if (dyn) {
+        const float kt = __ldg(p.ks_cache + blk * p.ks_st[0] + off * p.ks_st[1] + hkv * p.ks_st[2]);
+        vt = __ldg(p.vs_cache + blk * p.vs_st[0] + off * p.vs_st[1] + hkv * p.vs_st[2]);
+#pragma unroll
+        for (int g = 0; g < GM; ++g) sc[g] *= kt;
+      }
+    }
+    // ---- online softmax per head over the step's 32 tokens ----
+    float pr[GM];
+#pragma unroll
+    for (int g = 0; g < GM; ++g) {
+      pr[g] = 0.f;
+      if (g < G) {
+        float top = ok ? sc[g] : -INFINITY;
+        for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
+        const float mn = fmaxf(m[g], top);
+        if (mn != -INFINITY) {
+          const float al = exp2f(m[g] - mn);
+          const float pe = ok ? exp2f(sc[g] - mn) : 0.f;
+          float sum = pe;
+          for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(kFull, sum, o);
+          l[g] = l[g] * al + sum;
+          m[g] = mn;
+          pr[g] = pe * vt;
+#pragma unroll
+          for (int e = 0; e < E; ++e) acc[g][e] *= al;
+        }
+      }
+    }
+    // ---- O += P . V, token by token: lane = dims lane + 32 e ----
+    const int steps = static_cast<int>(min(static_cast<int64_t>(kWarp), tok_hi - tok0));
+    constexpr int U = GM >= 16 ? 2 : 4;  // tokens in flight: their V loads are issued together
+    for (int j0 = 0; j0 < steps; j0 += U) {
+      float pj[U][GM], v[U][E];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;  // lanes beyond `steps` hold ok = false
+        const int64_t bj = __shfl_sync(kFull, blk, j & 31);
+        const int oj = __shfl_sync(kFull, off, j & 31);
+        const bool okj = j < steps && __shfl_sync(kFull, ok ? 1 : 0, j & 31) != 0;
+#pragma unroll
+        for (int g = 0; g < GM; ++g) pj[u][g] = okj ? __shfl_sync(kFull, pr[g], j & 31) : 0.f;
+        const int8_t* vrow = vc + (okj ? bj * p.vc_st[0] + oj * p.vc_st[1] + hkv * p.vc_st[2] : 0);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int d = lane + kWarp * e;
+          v[u][e] = 0.f;
+          if (okj && d < D)
+            v[u][e] = s8_of_word<0>(static_cast<uint32_t>(static_cast<uint8_t>(__ldg(vrow + d))) ^ 0x80u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+#pragma unroll
+          for (int g = 0; g < GM; ++g) acc[g][e] += pj[u][g] * v[u][e];
+        }
+      }
+    }
+  }
+
+#pragma unroll
+  for (int g = 0; g < GM; ++g) {
+    if (g >= G) continue;
+    const int hq = hkv * G + g;
+    const float inv = l[g] > 0.f ? vsc / l[g] : 0.f;
+    const int64_t row = (static_cast<int64_t>(c) * p.B + b) * p.Hq + hq;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int d = lane + kWarp * e;
+      if (d >= D) continue;
+      if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[g][e] * inv);
+      else p.part[row * p.row_floats + d] = acc[g][e] * inv;
+    }
+    if (p.part != nullptr && lane == 0)
+      p.part[row * p.row_floats + D] = l[g] > 0.f ? (m[g] + log2f(l[g])) * 0.6931471805599453f : -INFINITY;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1367,7 +1642,38 @@ int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
   if (p.D > kGenericMaxD) return INT8KV_E_UNSUPPORTED;
   const int64_t items = static_cast<int64_t>(p.B) * p.num_splits * p.Hq;
   if (items <= 0) return INT8KV_OK;
-  return launch_pdl(paged_attn_generic_kernel, static_cast<unsigned>((items + 3) / 4), 128, 0, stream, p);
+  // INT8 caches with a head_dim that is a multiple of 4 (up to 256) and a group of up to 16: one read of the pages
+  // serves the whole group
+  if (p.cache_kind == kCacheInt8 && p.D % 4 == 0 && p.D <= 256 && p.G <= 16 && p.kc_st[3] == 1 && p.vc_st[3] == 1) {
+    const int gm = p.G <= 4 ? 4 : (p.G <= 8 ? 8 : 16);
+    const int e = p.D <= 64 ? 2 : (p.D <= 128 ? 4 : 8);
+    if (gm * e <= 64) {
+      const int64_t gitems = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
+      const unsigned ggrid = static_cast<unsigned>((gitems + 3) / 4);
+      const size_t smem = static_cast<size_t>(4) * gm * 32 * e * sizeof(float);
+      auto grouped = [&](auto kernel) { return launch_pdl(kernel, ggrid, 128, smem, stream, p); };
+      if (gm == 4 && e == 2) return grouped(paged_attn_grouped_kernel<4, 2>);
+      if (gm == 4 && e == 4) return grouped(paged_attn_grouped_kernel<4, 4>);
+      if (gm == 4 && e == 8) return grouped(paged_attn_grouped_kernel<4, 8>);
+      if (gm == 8 && e == 2) return grouped(paged_attn_grouped_kernel<8, 2>);
+      if (gm == 8 && e == 4) return grouped(paged_attn_grouped_kernel<8, 4>);
+      if (gm == 8 && e == 8) return grouped(paged_attn_grouped_kernel<8, 8>);
+      if (gm == 16 && e == 2) return grouped(paged_attn_grouped_kernel<16, 2>);
+      return grouped(paged_attn_grouped_kernel<16, 4>);
+    }
+  }
+  const unsigned grid = static_cast<unsigned>((items + 3) / 4);
+  auto go = [&](auto kernel) { return launch_pdl(kernel, grid, 128, 0, stream, p); };
+  auto by_slots = [&](auto kind) {
+    constexpr int K = decltype(kind)::value;
+    if (p.D <= 64) return go(paged_attn_generic_kernel<K, 2>);
+    if (p.D <= 128) return go(paged_attn_generic_kernel<K, 4>);
+    if (p.D <= 256) return go(paged_attn_generic_kernel<K, 8>);
+    return go(paged_attn_generic_kernel<K, 16>);
+  };
+  if (p.cache_kind == kCacheInt8) return by_slots(std::integral_constant<int, kCacheInt8>{});
+  if (p.cache_kind == kCacheBf16) return by_slots(std::integral_constant<int, kCacheBf16>{});
+  return by_slots(std::integral_constant<int, kCacheFp16>{});
 }
 
 int launch_merge(const MergeParams& p_in, cudaStream_t stream) {
