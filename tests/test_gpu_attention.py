@@ -173,6 +173,39 @@ def test_generic_path_shapes(kv, workloads):
             out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
                                                 case.k_scale, case.v_scale), num_splits=splits)
             _check(out, want)
+    # the per-query-head kernel: a group of 17, a head_dim that is not a multiple of 4
+    for (hq, hkv, d, bs) in [(34, 2, 128, 16), (4, 2, 66, 16)]:
+        shape = workloads.LayerShape(hq, hkv, d, bs)
+        lens = [5, 64, 131]
+        case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=hq)
+        want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+        for splits in (None, 2):
+            _check(kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
+                                                 case.k_scale, case.v_scale), num_splits=splits), want)
+    # the grouped kernel on rows that are not 4-byte aligned (a view into a wider cache), with the INT8 query
+    # option, and the 16-bit baseline on a head_dim of 64
+    shape = workloads.LayerShape(8, 2, 64, 16)
+    lens = [70, 9, 200]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=77)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    wide_k = torch.zeros(kc.shape[0], 16, 2, 66, dtype=torch.int8, device="cuda")
+    wide_v = torch.zeros_like(wide_k)
+    wide_k[..., 1:65], wide_v[..., 1:65] = kc.cuda(), vc.cuda()
+    q, bt, sl, ks, vs = _dev(case.query, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    _check(kv.int8_paged_attention(q, wide_k[..., 1:65], wide_v[..., 1:65], bt, sl, ks, vs), want)
+    from conftest import package
+
+    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
+    wantq = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
+    outq = kv.int8_paged_attention(q, kc.cuda(), vc.cuda(), bt, sl, ks, vs, quantize_q=True).float().cpu()
+    assert cosine(outq, wantq.float()) >= MIN_COS and max_abs(outq, wantq.float()) <= MAX_ABS
+    kb = torch.zeros(case.num_blocks, 16, 2, 64, dtype=torch.bfloat16)
+    vb = torch.zeros_like(kb)
+    s_ = case.slot_mapping
+    kb[s_ // 16, s_ % 16], vb[s_ // 16, s_ % 16] = case.key, case.value
+    _check(kv.bf16_paged_attention(q, kb.cuda(), vb.cuda(), bt, sl),
+           oracle.float_paged_attention_oracle(case.query, kb, vb, case.block_tables, lens))
+    assert kv.device_status() == 0
 
 
 def test_larger_block_size_and_group_of_8(kv, workloads):
