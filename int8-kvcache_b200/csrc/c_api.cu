@@ -112,6 +112,18 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   return static_cast<int>(s);
 }
 
+// Split count for the kernels outside the tiled shapes: they hide their load latency with warps, not with a
+// ring, so they want about 32 warps per SM in total (measured on a head_dim-64 layer: 8 x 4096 tokens 230 GB/s at
+// 16 parts, 364 GB/s at 32), but parts of at least 8 blocks of 16 tokens.
+int untiled_splits(int B, int Hkv, int64_t max_seq, int sm_count) {
+  const int64_t items = std::max<int64_t>(1, static_cast<int64_t>(B) * Hkv);
+  const int64_t tiles = (max_seq + 15) / 16;
+  int64_t s = 1;
+  while (s * items < static_cast<int64_t>(sm_count) * 32) s *= 2;
+  s = std::min<int64_t>(s, pow2_floor(std::max<int64_t>(1, tiles / 8)));
+  return static_cast<int>(std::min<int64_t>(std::max<int64_t>(s, 1), kMaxSplits));
+}
+
 // ---- device-planned splits ----------------------------------------------------------------------------
 // Large calls (HBM-bound, up to a few resident waves of warps) choose the part length on the device from the
 // actual sequence lengths, so that the parts fill whole waves; see plan_in_warp.  INT8KV_PLAN=0 turns it off,
@@ -234,6 +246,12 @@ int run_attention(const AttnCall& a) {
   const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
                      tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
                      (rf % 4 == 0);
+  if (!tiled && a.num_splits == 0) {
+    // the automatic count above is fitted to the tiled kernels; use the untiled one if the workspace allows it
+    int su = untiled_splits(a.B, a.Hkv, max_seq, sm);
+    if (su > tiles) su = tiles > 0 ? static_cast<int>(tiles) : 1;
+    if (su <= 1 || (a.ws != nullptr && a.ws_bytes >= ws_bytes(a.B, a.Hq, a.D, su))) S = su;
+  }
   // Device-planned splits: asked for explicitly, or chosen for a large automatic call when the workspace has
   // room for the plan (callers that sized it with int8kv_workspace_bytes_auto always have).
   bool planned = false;
@@ -365,6 +383,8 @@ int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads
   const int sm = sm_count > 0 ? sm_count : 148;
   const int64_t tiles = (max_seq_len + 15) / 16;
   int64_t n = ws_bytes(batch, num_q_heads, head_dim, choose_splits(batch, num_kv_heads, max_seq_len, block_size, sm));
+  if (head_dim != 128)  // a shape for the untiled kernels, which split further
+    n = std::max(n, ws_bytes(batch, num_q_heads, head_dim, untiled_splits(batch, num_kv_heads, max_seq_len, sm)));
   if (batch > 0 && tiles > 0 && plan_possible(batch, num_kv_heads, sm)) {
     const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm);
     n = std::max(n, plan_layout(batch, num_q_heads, num_kv_heads, head_dim, ps.max_items).total);
