@@ -416,6 +416,36 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
   return v;
 }
 
+// The fused step's write of the new token's row, once per (sequence, kv head): quantise the row exactly as the
+// cache-write kernel does, store it to the cache, and overwrite the row in the staged tile (TMA fetched the tile
+// before this store, so the stage still holds the old bytes).  Out of line on purpose: one warp in Hkv-th of the
+// grid runs it, once, and its 64-bit divisions and the quantiser's exact-division fallback would otherwise sit in
+// the middle of every warp's streaming loop.
+__device__ __noinline__ void fused_row_write(const void* kc, const void* vc, int64_t k_st0, int64_t k_st1, int64_t k_head,
+                                             int64_t v_st0, int64_t v_st1, int64_t v_head, int64_t num_blocks,
+                                             int block_size, int pos, int64_t new_slot, int64_t last_blk, float k0,
+                                             float k1, float k2, float k3, float v0, float v1, float v2, float v3,
+                                             float ks, float vsn, uint32_t stage, unsigned int* status, int lane) {
+  const float rk = __frcp_rn(ks), rv = __frcp_rn(vsn);
+  const uint32_t kw = pack4_sat(quant1(k0, ks, rk), quant1(k1, ks, rk), quant1(k2, ks, rk), quant1(k3, ks, rk));
+  const uint32_t vw = pack4_sat(quant1(v0, vsn, rv), quant1(v1, vsn, rv), quant1(v2, vsn, rv), quant1(v3, vsn, rv));
+  const int64_t expect = last_blk * block_size + pos % block_size;
+  if (new_slot >= 0 && new_slot < num_blocks * block_size) {
+    const int64_t blk = new_slot / block_size, off = new_slot - blk * block_size;
+    int8_t* kcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(kc));
+    int8_t* vcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(vc));
+    *reinterpret_cast<uint32_t*>(kcw + blk * k_st0 + off * k_st1 + k_head + 4 * lane) = kw;
+    *reinterpret_cast<uint32_t*>(vcw + blk * v_st0 + off * v_st1 + v_head + 4 * lane) = vw;
+    if (new_slot == expect) {
+      const uint32_t st = stage + swz128(pos & 15, lane >> 2) + (lane & 3) * 4;
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(st), "r"(kw) : "memory");
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(st + 2048), "r"(vw) : "memory");
+    } else if (lane == 0 && status != nullptr) {
+      atomicOr(status, INT8KV_DEV_SLOT_MISMATCH);
+    }
+  }
+}
+
 // PLANNED: the items come from plan_in_warp instead of being numbered arithmetically.  A template parameter rather
 // than a run-time test, so that the kernel that serves small calls does not carry the planning code.
 // QQ: the reference's optional INT8 query (quantize_q), one limb; its own instantiation as well.
@@ -604,28 +634,9 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 
     if constexpr (FUSED_WRITE) {
       if (owns_new && (last_rel == i || last_rel == i + 1)) {
-        // quantise the new row exactly as the cache-write kernel does, store it to the cache, and overwrite the
-        // row in the staged tile (TMA fetched the tile before this store, so the stage still holds the old bytes)
-        const float ks = k_scale_head, vsn = v_scale_head;  // loaded in the prologue
-        const float rk = __frcp_rn(ks), rv = __frcp_rn(vsn);
-        const uint32_t kw = pack4_sat(quant1(nk[0], ks, rk), quant1(nk[1], ks, rk), quant1(nk[2], ks, rk), quant1(nk[3], ks, rk));
-        const uint32_t vw = pack4_sat(quant1(nv[0], vsn, rv), quant1(nv[1], vsn, rv), quant1(nv[2], vsn, rv), quant1(nv[3], vsn, rv));
-        const int64_t pos = it.seq_len - 1;
-        const int64_t expect = last_blk * p.block_size + pos % p.block_size;
-        if (new_slot >= 0 && new_slot < p.num_blocks * p.block_size) {
-          const int64_t blk = new_slot / p.block_size, off = new_slot - blk * p.block_size;
-          int8_t* kcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(p.kc));
-          int8_t* vcw = const_cast<int8_t*>(reinterpret_cast<const int8_t*>(p.vc));
-          *reinterpret_cast<uint32_t*>(kcw + blk * p.kc_st[0] + off * p.kc_st[1] + it.h * p.kc_st[2] + 4 * lane) = kw;
-          *reinterpret_cast<uint32_t*>(vcw + blk * p.vc_st[0] + off * p.vc_st[1] + it.h * p.vc_st[2] + 4 * lane) = vw;
-          if (new_slot == expect) {
-            const uint32_t st = ring.stage(last_rel) + swz128(static_cast<int>(pos & 15), lane >> 2) + (lane & 3) * 4;
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st), "r"(kw) : "memory");
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(st + 2048), "r"(vw) : "memory");
-          } else if (lane == 0 && p.status != nullptr) {
-            atomicOr(p.status, INT8KV_DEV_SLOT_MISMATCH);
-          }
-        }
+        fused_row_write(p.kc, p.vc, p.kc_st[0], p.kc_st[1], it.h * p.kc_st[2], p.vc_st[0], p.vc_st[1], it.h * p.vc_st[2],
+                        p.num_blocks, p.block_size, it.seq_len - 1, new_slot, last_blk, nk[0], nk[1], nk[2], nk[3],
+                        nv[0], nv[1], nv[2], nv[3], k_scale_head, v_scale_head, ring.stage(last_rel), p.status, lane);
         __syncwarp();
       }
     }
