@@ -1177,12 +1177,17 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
 
 // ---------------------------------------------------------------------------------------------
 // Grouped kernel for INT8 caches outside the tiled kernels' shapes (head_dim != 128, odd block sizes): one warp per
-// (sequence, KV head, split) serves the whole GQA group from one read of the pages, with plain loads.
-//   scores: lane = token.  Each lane walks its token's K row four elements at a time against the group's queries,
-//           which sit pre-scaled in shared memory and are read as broadcasts: no shuffle per dot product.
-//   softmax: per head over the 32 tokens of a step (warp max and sum).
-//   P.V:    lane = dims lane, lane + 32, ...  Token by token the probabilities are broadcast by shuffle and the V
-//           row is read coalesced.
+// (sequence, KV head, split) serves the whole GQA group from one read of the pages, with plain loads, 32 tokens
+// per step.
+//   rows:    lane = token.  The rows of the NEXT step are located first and requested into L2, so that every
+//            step but a part's first finds its rows there instead of in DRAM.
+//   scores:  lane = token.  Each lane walks its token's K row (16-byte loads when the layout allows) against the
+//            group's queries, which sit pre-scaled in shared memory and are read as broadcasts: no shuffle per
+//            dot product.
+//   softmax: per head over the 32 tokens of the step (warp max and sum); the probabilities go to shared memory.
+//   P.V:     lane = dims [E lane, E lane + E).  The V rows of the step are requested BEFORE the scores are computed
+//            (they do not depend on them), one load of E bytes per token and lane; afterwards, token by token,
+//            the group's probabilities are one broadcast read and the row is already in registers.
 // GM bounds the group (registers per head), E = elements per lane; head_dim % 4 == 0, head_dim <= 32 * E.
 // ---------------------------------------------------------------------------------------------
 // Byte i of a word of four INT8 values (already XORed with 0x80808080) as a float, without the conversion unit:
@@ -1190,6 +1195,10 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
 template <int I>
 __device__ __forceinline__ float s8_of_word(uint32_t biased) {
   return __uint_as_float(prmt(biased, 0x4B400000u, 0x7650u | I)) - 12583040.f;  // 12582912 + 128
+}
+
+__device__ __forceinline__ void prefetch_to_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
 
 template <int GM, int E>
@@ -1214,8 +1223,10 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
   int64_t tok_hi = (c + 1) * per * p.block_size;
   if (tok_hi > sl) tok_hi = sl;
 
-  // queries of the group, multiplied by everything that is constant per head, into this warp's shared memory
-  float* qs = q_smem + warp * (GM * 32 * E);
+  // queries of the group, multiplied by everything that is constant per head, into this warp's shared memory;
+  // behind them the step's probabilities [token][GM]
+  float* qs = q_smem + warp * (GM * 32 * E + GM * 32);
+  float* ps = qs + GM * 32 * E;
   const float ksc = p.k_scale ? fmaxf(__ldg(p.k_scale + hkv), 1e-6f) : 1.f;
   const float vsc = p.v_scale ? fmaxf(__ldg(p.v_scale + hkv), 1e-6f) : 1.f;
   for (int g = 0; g < G; ++g) {
@@ -1259,19 +1270,109 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
   }
   const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc);
   const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc);
+  // whole-launch layout facts: K rows readable 16 bytes at a time, V rows E bytes at a time
+  const bool k_vec = D % 16 == 0 && ((reinterpret_cast<uintptr_t>(kc) | static_cast<uintptr_t>(p.kc_st[0]) |
+                                      static_cast<uintptr_t>(p.kc_st[1]) | static_cast<uintptr_t>(p.kc_st[2])) & 15u) == 0;
+  const bool v_vec = D % E == 0 && ((reinterpret_cast<uintptr_t>(vc) | static_cast<uintptr_t>(p.vc_st[0]) |
+                                     static_cast<uintptr_t>(p.vc_st[1]) | static_cast<uintptr_t>(p.vc_st[2])) & (E - 1)) == 0;
+
+  // Where token t's rows start (lane = token); false when the token is outside the part or its table entry is
+  // outside the cache (such a token is never read and gets weight 0).
+  auto locate = [&](int64_t t, int64_t& blk, int& off) -> bool {
+    if (t >= tok_hi) return false;
+    const int64_t lb = t / p.block_size;
+    off = static_cast<int>(t - lb * p.block_size);
+    blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+    return blk >= 0 && blk < p.num_blocks;
+  };
+  auto request_rows = [&](int64_t blk, int off) {
+    const int8_t* kr = kc + blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
+    const int8_t* vr = vc + blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
+    for (int d0 = 0; d0 < D; d0 += 32) {
+      prefetch_to_l2(kr + d0);
+      prefetch_to_l2(vr + d0);
+    }
+  };
+
+  constexpr int VW = E == 8 ? 2 : 1;                             // registers per token of a lane's V elements
+  constexpr int VU = E == 8 ? 8 : (GM >= 16 ? 16 : 32);          // tokens whose V loads are in flight together
+  int64_t blk = -1, blk_next = -1;
+  int off = 0, off_next = 0;
+  bool ok = locate(tok_lo + lane, blk, off);
+  bool ok_next = false;
 
   for (int64_t tok0 = tok_lo; tok0 < tok_hi; tok0 += kWarp) {
+    ok_next = locate(tok0 + kWarp + lane, blk_next, off_next);
+    if (ok_next) request_rows(blk_next, off_next);
+    const int steps = static_cast<int>(min(static_cast<int64_t>(kWarp), tok_hi - tok0));
+    const int64_t voff = ok ? blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2] : -1;
+
+    // V elements [E lane, E lane + E) of tokens j0 .. j0 + VU - 1, as raw bytes
+    uint32_t vr[VU][VW];
+    auto load_v = [&](int j0) {
+#pragma unroll
+      for (int u = 0; u < VU; ++u) {
+        const int64_t vo = __shfl_sync(kFull, voff, (j0 + u) & 31);
+#pragma unroll
+        for (int w = 0; w < VW; ++w) vr[u][w] = 0u;
+        if (vo >= 0 && E * lane < D) {
+          const int8_t* row = vc + vo + E * lane;
+          if (v_vec) {
+            if constexpr (E == 2) vr[u][0] = __ldg(reinterpret_cast<const uint16_t*>(row));
+            if constexpr (E == 4) vr[u][0] = __ldg(reinterpret_cast<const uint32_t*>(row));
+            if constexpr (E == 8) {
+              const uint2 x = __ldg(reinterpret_cast<const uint2*>(row));
+              vr[u][0] = x.x;
+              vr[u][VW - 1] = x.y;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+              if (E * lane + e < D)
+                vr[u][e / 4] |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(row + e))) << (8 * (e & 3));
+          }
+        }
+      }
+    };
+    // O += P . V for those tokens; the probabilities of absent tokens are 0
+    auto use_v = [&](int j0) {
+#pragma unroll
+      for (int u = 0; u < VU; ++u) {
+        const int j = j0 + u;
+        if (j >= steps) break;
+        float pj[GM];
+#pragma unroll
+        for (int g4 = 0; g4 < GM; g4 += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(ps + j * GM + g4);  // same address in every lane
+          pj[g4] = x.x; pj[g4 + 1] = x.y; pj[g4 + 2] = x.z; pj[g4 + 3] = x.w;
+        }
+        float v[E];
+        {
+          const uint32_t w0 = vr[u][0] ^ 0x80808080u;
+          v[0] = s8_of_word<0>(w0);
+          v[1] = s8_of_word<1>(w0);
+          if constexpr (E >= 4) {
+            v[2] = s8_of_word<2>(w0);
+            v[3] = s8_of_word<3>(w0);
+          }
+          if constexpr (E == 8) {
+            const uint32_t w1 = vr[u][VW - 1] ^ 0x80808080u;
+            v[4] = s8_of_word<0>(w1);
+            v[5] = s8_of_word<1>(w1);
+            v[6] = s8_of_word<2>(w1);
+            v[7] = s8_of_word<3>(w1);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+#pragma unroll
+          for (int g = 0; g < GM; ++g) acc[g][e] += pj[g] * v[e];
+        }
+      }
+    };
+    load_v(0);
+
     // ---- scores of token tok0 + lane against every head of the group ----
-    const int64_t t = tok0 + lane;
-    bool ok = t < tok_hi;
-    int64_t blk = -1;
-    int off = 0;
-    if (ok) {
-      const int64_t lb = t / p.block_size;
-      off = static_cast<int>(t - lb * p.block_size);
-      blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
-      ok = blk >= 0 && blk < p.num_blocks;  // never read outside the cache
-    }
     float sc[GM];
 #pragma unroll
     for (int g = 0; g < GM; ++g) sc[g] = 0.f;
@@ -1279,21 +1380,30 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
     if (ok) {
       const int8_t* krow = kc + blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
       const bool aligned = (reinterpret_cast<uintptr_t>(krow) & 3u) == 0;
-      // 64 elements at a time: all sixteen loads are issued before the first is used
+      // 64 elements at a time: all their loads are issued before the first is used
       for (int d0 = 0; d0 < D; d0 += 64) {
         int w[16];
+        if (k_vec) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int d = d0 + 4 * i;
-          w[i] = 0;
-          if (d < D) {
-            if (aligned) {
-              w[i] = __ldg(reinterpret_cast<const int*>(krow + d));
-            } else {
-              w[i] = (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d)))) |
-                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 1))) << 8) |
-                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 2))) << 16) |
-                     (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 3))) << 24);
+          for (int i = 0; i < 4; ++i) {
+            int4 x = make_int4(0, 0, 0, 0);
+            if (d0 + 16 * i < D) x = __ldg(reinterpret_cast<const int4*>(krow + d0 + 16 * i));
+            w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int d = d0 + 4 * i;
+            w[i] = 0;
+            if (d < D) {
+              if (aligned) {
+                w[i] = __ldg(reinterpret_cast<const int*>(krow + d));
+              } else {
+                w[i] = (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d)))) |
+                       (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 1))) << 8) |
+                       (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 2))) << 16) |
+                       (static_cast<int>(static_cast<uint8_t>(__ldg(krow + d + 3))) << 24);
+              }
             }
           }
         }
@@ -1342,37 +1452,21 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
         }
       }
     }
-    // ---- O += P . V, token by token: lane = dims lane + 32 e ----
-    const int steps = static_cast<int>(min(static_cast<int64_t>(kWarp), tok_hi - tok0));
-    constexpr int U = GM >= 16 ? 2 : 4;  // tokens in flight: their V loads are issued together
-    for (int j0 = 0; j0 < steps; j0 += U) {
-      float pj[U][GM], v[U][E];
+    __syncwarp();  // the previous step's probabilities have been read by every lane
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int j = j0 + u;  // lanes beyond `steps` hold ok = false
-        const int64_t bj = __shfl_sync(kFull, blk, j & 31);
-        const int oj = __shfl_sync(kFull, off, j & 31);
-        const bool okj = j < steps && __shfl_sync(kFull, ok ? 1 : 0, j & 31) != 0;
-#pragma unroll
-        for (int g = 0; g < GM; ++g) pj[u][g] = okj ? __shfl_sync(kFull, pr[g], j & 31) : 0.f;
-        const int8_t* vrow = vc + (okj ? bj * p.vc_st[0] + oj * p.vc_st[1] + hkv * p.vc_st[2] : 0);
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const int d = lane + kWarp * e;
-          v[u][e] = 0.f;
-          if (okj && d < D)
-            v[u][e] = s8_of_word<0>(static_cast<uint32_t>(static_cast<uint8_t>(__ldg(vrow + d))) ^ 0x80u);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-#pragma unroll
-          for (int g = 0; g < GM; ++g) acc[g][e] += pj[u][g] * v[u][e];
-        }
-      }
+    for (int g4 = 0; g4 < GM; g4 += 4)
+      *reinterpret_cast<float4*>(ps + lane * GM + g4) = make_float4(pr[g4], pr[g4 + 1], pr[g4 + 2], pr[g4 + 3]);
+    __syncwarp();
+
+    // ---- O += P . V ----
+    use_v(0);
+    for (int j0 = VU; j0 < steps; j0 += VU) {
+      load_v(j0);
+      use_v(j0);
     }
+    blk = blk_next;
+    off = off_next;
+    ok = ok_next;
   }
 
 #pragma unroll
@@ -1383,7 +1477,7 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
     const int64_t row = (static_cast<int64_t>(c) * p.B + b) * p.Hq + hq;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int d = lane + kWarp * e;
+      const int d = E * lane + e;
       if (d >= D) continue;
       if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[g][e] * inv);
       else p.part[row * p.row_floats + d] = acc[g][e] * inv;
@@ -1661,7 +1755,7 @@ int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
     if (gm * e <= 64) {
       const int64_t gitems = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
       const unsigned ggrid = static_cast<unsigned>((gitems + 3) / 4);
-      const size_t smem = static_cast<size_t>(4) * gm * 32 * e * sizeof(float);
+      const size_t smem = static_cast<size_t>(4) * (gm * 32 * e + gm * 32) * sizeof(float);  // queries + probabilities
       auto grouped = [&](auto kernel) { return launch_pdl(kernel, ggrid, 128, smem, stream, p); };
       if (gm == 4 && e == 2) return grouped(paged_attn_grouped_kernel<4, 2>);
       if (gm == 4 && e == 4) return grouped(paged_attn_grouped_kernel<4, 4>);
