@@ -1201,8 +1201,10 @@ __device__ __forceinline__ void prefetch_to_l2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
 
-template <int GM, int E>
+template <int GM, int E, int TPI>
 __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParams p) {
+  static_assert((E == 4 && (TPI == 1 || TPI == 2)) || (E == 8 && TPI == 1), "lane layouts of the P.V phase");
+  constexpr int LPT = kWarp / TPI;  // lanes that share one token in the P.V phase
   extern __shared__ __align__(16) float q_smem[];
   grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1268,57 +1270,72 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
   }
-  const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc);
-  const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc);
-  // whole-launch layout facts: K rows readable 16 bytes at a time, V rows E bytes at a time
-  const bool k_vec = D % 16 == 0 && ((reinterpret_cast<uintptr_t>(kc) | static_cast<uintptr_t>(p.kc_st[0]) |
+  const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc) + hkv * p.kc_st[2];  // this head's column of the caches
+  const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc) + hkv * p.vc_st[2];
+  // whole-launch layout facts: K rows readable 16 bytes at a time, a lane's V elements readable as one word
+  const bool k_vec = D % 16 == 0 && ((reinterpret_cast<uintptr_t>(p.kc) | static_cast<uintptr_t>(p.kc_st[0]) |
                                       static_cast<uintptr_t>(p.kc_st[1]) | static_cast<uintptr_t>(p.kc_st[2])) & 15u) == 0;
-  const bool v_vec = D % E == 0 && ((reinterpret_cast<uintptr_t>(vc) | static_cast<uintptr_t>(p.vc_st[0]) |
+  const bool v_vec = D % E == 0 && ((reinterpret_cast<uintptr_t>(p.vc) | static_cast<uintptr_t>(p.vc_st[0]) |
                                      static_cast<uintptr_t>(p.vc_st[1]) | static_cast<uintptr_t>(p.vc_st[2])) & (E - 1)) == 0;
 
-  // Where token t's rows start (lane = token); false when the token is outside the part or its table entry is
-  // outside the cache (such a token is never read and gets weight 0).
-  auto locate = [&](int64_t t, int64_t& blk, int& off) -> bool {
-    if (t >= tok_hi) return false;
-    const int64_t lb = t / p.block_size;
-    off = static_cast<int>(t - lb * p.block_size);
-    blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
-    return blk >= 0 && blk < p.num_blocks;
+  // lane = token: logical block and offset of the lane's token, advanced by 32 tokens per step without a division
+  const int step_blocks = kWarp / p.block_size, step_rest = kWarp % p.block_size;
+  int64_t lb = (tok_lo + lane) / p.block_size;
+  int off = static_cast<int>(tok_lo + lane - lb * p.block_size);
+  // Physical block of token t (lane = token); -1 when the token is outside the part or its table entry is outside
+  // the cache (such a token is never read and gets weight 0).
+  auto locate = [&](int64_t t) -> int64_t {
+    if (t >= tok_hi) return -1;
+    const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+    return blk >= 0 && blk < p.num_blocks ? blk : -1;
   };
-  auto request_rows = [&](int64_t blk, int off) {
-    const int8_t* kr = kc + blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
-    const int8_t* vr = vc + blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2];
-    for (int d0 = 0; d0 < D; d0 += 32) {
-      prefetch_to_l2(kr + d0);
-      prefetch_to_l2(vr + d0);
+  auto advance = [&]() {
+    lb += step_blocks;
+    off += step_rest;
+    if (off >= p.block_size) {
+      off -= p.block_size;
+      ++lb;
     }
   };
 
-  constexpr int VW = E == 8 ? 2 : 1;                             // registers per token of a lane's V elements
-  constexpr int VU = E == 8 ? 8 : (GM >= 16 ? 16 : 32);          // tokens whose V loads are in flight together
-  int64_t blk = -1, blk_next = -1;
-  int off = 0, off_next = 0;
-  bool ok = locate(tok_lo + lane, blk, off);
-  bool ok_next = false;
+  constexpr int VW = E / 4;                                // registers per load of a lane's V elements
+  constexpr int VI = kWarp / TPI;                          // V loads per step and lane (TPI tokens per load)
+  constexpr int VU = E == 8 ? 8 : (GM >= 16 ? 16 : VI);    // loads in flight together
+  constexpr int NA = GM <= 8 ? 2 : 1;                      // score accumulators per head (shorter FMA chains)
+  const int ts = lane / LPT, wcol = lane % LPT;            // P.V phase: token slot and word column of this lane
+  const bool v_lane = E * wcol < D;
+
+  int64_t blk = locate(tok_lo + lane);
+  int off_cur = off;
 
   for (int64_t tok0 = tok_lo; tok0 < tok_hi; tok0 += kWarp) {
-    ok_next = locate(tok0 + kWarp + lane, blk_next, off_next);
-    if (ok_next) request_rows(blk_next, off_next);
+    // the next step's rows: found now and requested into L2
+    advance();
+    const int64_t blk_next = locate(tok0 + kWarp + lane);
+    const int off_next = off;
+    if (blk_next >= 0) {
+      const int8_t* kr = kc + blk_next * p.kc_st[0] + off_next * p.kc_st[1];
+      const int8_t* vr_next = vc + blk_next * p.vc_st[0] + off_next * p.vc_st[1];
+      for (int d0 = 0; d0 < D; d0 += 32) {
+        prefetch_to_l2(kr + d0);
+        prefetch_to_l2(vr_next + d0);
+      }
+    }
     const int steps = static_cast<int>(min(static_cast<int64_t>(kWarp), tok_hi - tok0));
-    const int64_t voff = ok ? blk * p.vc_st[0] + off * p.vc_st[1] + hkv * p.vc_st[2] : -1;
+    const bool ok = blk >= 0;
+    const int64_t voff = ok ? blk * p.vc_st[0] + off_cur * p.vc_st[1] : -1;
 
-    // V elements [E lane, E lane + E) of tokens j0 .. j0 + VU - 1, as raw bytes
+    // V elements [E wcol, E wcol + E) of tokens i TPI + ts, for loads i0 .. i0 + VU - 1, as raw bytes
     uint32_t vr[VU][VW];
-    auto load_v = [&](int j0) {
+    auto load_v = [&](int i0) {
 #pragma unroll
       for (int u = 0; u < VU; ++u) {
-        const int64_t vo = __shfl_sync(kFull, voff, (j0 + u) & 31);
+        const int64_t vo = __shfl_sync(kFull, voff, ((i0 + u) * TPI + ts) & 31);
 #pragma unroll
         for (int w = 0; w < VW; ++w) vr[u][w] = 0u;
-        if (vo >= 0 && E * lane < D) {
-          const int8_t* row = vc + vo + E * lane;
+        if (vo >= 0 && v_lane) {
+          const int8_t* row = vc + vo + E * wcol;
           if (v_vec) {
-            if constexpr (E == 2) vr[u][0] = __ldg(reinterpret_cast<const uint16_t*>(row));
             if constexpr (E == 4) vr[u][0] = __ldg(reinterpret_cast<const uint32_t*>(row));
             if constexpr (E == 8) {
               const uint2 x = __ldg(reinterpret_cast<const uint2*>(row));
@@ -1328,22 +1345,21 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
           } else {
 #pragma unroll
             for (int e = 0; e < E; ++e)
-              if (E * lane + e < D)
+              if (E * wcol + e < D)
                 vr[u][e / 4] |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(row + e))) << (8 * (e & 3));
           }
         }
       }
     };
-    // O += P . V for those tokens; the probabilities of absent tokens are 0
-    auto use_v = [&](int j0) {
+    // O += P . V for those tokens; absent tokens have probability 0 and V bytes 0
+    auto use_v = [&](int i0) {
 #pragma unroll
       for (int u = 0; u < VU; ++u) {
-        const int j = j0 + u;
-        if (j >= steps) break;
+        const int j = (i0 + u) * TPI + ts;
         float pj[GM];
 #pragma unroll
         for (int g4 = 0; g4 < GM; g4 += 4) {
-          const float4 x = *reinterpret_cast<const float4*>(ps + j * GM + g4);  // same address in every lane
+          const float4 x = *reinterpret_cast<const float4*>(ps + j * GM + g4);  // one address per token slot
           pj[g4] = x.x; pj[g4 + 1] = x.y; pj[g4 + 2] = x.z; pj[g4 + 3] = x.w;
         }
         float v[E];
@@ -1351,10 +1367,8 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
           const uint32_t w0 = vr[u][0] ^ 0x80808080u;
           v[0] = s8_of_word<0>(w0);
           v[1] = s8_of_word<1>(w0);
-          if constexpr (E >= 4) {
-            v[2] = s8_of_word<2>(w0);
-            v[3] = s8_of_word<3>(w0);
-          }
+          v[2] = s8_of_word<2>(w0);
+          v[3] = s8_of_word<3>(w0);
           if constexpr (E == 8) {
             const uint32_t w1 = vr[u][VW - 1] ^ 0x80808080u;
             v[4] = s8_of_word<0>(w1);
@@ -1366,20 +1380,26 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
 #pragma unroll
         for (int e = 0; e < E; ++e) {
 #pragma unroll
-          for (int g = 0; g < GM; ++g) acc[g][e] += pj[g] * v[e];
+          for (int g = 0; g < GM; ++g) acc[g][e] = fmaf(pj[g], v[e], acc[g][e]);
         }
       }
     };
     load_v(0);
 
     // ---- scores of token tok0 + lane against every head of the group ----
-    float sc[GM];
+    float sc[GM][NA];
 #pragma unroll
-    for (int g = 0; g < GM; ++g) sc[g] = 0.f;
-    float vt = 1.f;
+    for (int g = 0; g < GM; ++g)
+#pragma unroll
+      for (int n = 0; n < NA; ++n) sc[g][n] = 0.f;
+    float vt = 1.f, kt = 1.f;
     if (ok) {
-      const int8_t* krow = kc + blk * p.kc_st[0] + off * p.kc_st[1] + hkv * p.kc_st[2];
+      const int8_t* krow = kc + blk * p.kc_st[0] + off_cur * p.kc_st[1];
       const bool aligned = (reinterpret_cast<uintptr_t>(krow) & 3u) == 0;
+      if (dyn) {
+        kt = __ldg(p.ks_cache + blk * p.ks_st[0] + off_cur * p.ks_st[1] + hkv * p.ks_st[2]);
+        vt = __ldg(p.vs_cache + blk * p.vs_st[0] + off_cur * p.vs_st[1] + hkv * p.vs_st[2]);
+      }
       // 64 elements at a time: all their loads are issued before the first is used
       for (int d0 = 0; d0 < D; d0 += 64) {
         int w[16];
@@ -1417,17 +1437,16 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
             for (int g = 0; g < GM; ++g) {
               if (g < G) {
                 const float4 qv = *reinterpret_cast<const float4*>(qs + g * D + d);  // same address in every lane
-                sc[g] += k0 * qv.x + k1 * qv.y + k2 * qv.z + k3 * qv.w;
+                float a = sc[g][i % NA];
+                a = fmaf(k0, qv.x, a);
+                a = fmaf(k1, qv.y, a);
+                a = fmaf(k2, qv.z, a);
+                a = fmaf(k3, qv.w, a);
+                sc[g][i % NA] = a;
               }
             }
           }
         }
-      }
-      if (dyn) {
-        const float kt = __ldg(p.ks_cache + blk * p.ks_st[0] + off * p.ks_st[1] + hkv * p.ks_st[2]);
-        vt = __ldg(p.vs_cache + blk * p.vs_st[0] + off * p.vs_st[1] + hkv * p.vs_st[2]);
-#pragma unroll
-        for (int g = 0; g < GM; ++g) sc[g] *= kt;
       }
     }
     // ---- online softmax per head over the step's 32 tokens ----
@@ -1436,12 +1455,13 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
     for (int g = 0; g < GM; ++g) {
       pr[g] = 0.f;
       if (g < G) {
-        float top = ok ? sc[g] : -INFINITY;
+        const float score = (NA == 2 ? sc[g][0] + sc[g][NA - 1] : sc[g][0]) * kt;
+        float top = ok ? score : -INFINITY;
         for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
         const float mn = fmaxf(m[g], top);
         if (mn != -INFINITY) {
           const float al = exp2f(m[g] - mn);
-          const float pe = ok ? exp2f(sc[g] - mn) : 0.f;
+          const float pe = ok ? exp2f(score - mn) : 0.f;
           float sum = pe;
           for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(kFull, sum, o);
           l[g] = l[g] * al + sum;
@@ -1460,27 +1480,34 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
 
     // ---- O += P . V ----
     use_v(0);
-    for (int j0 = VU; j0 < steps; j0 += VU) {
-      load_v(j0);
-      use_v(j0);
+    for (int i0 = VU; i0 * TPI < steps; i0 += VU) {
+      load_v(i0);
+      use_v(i0);
     }
     blk = blk_next;
-    off = off_next;
-    ok = ok_next;
+    off_cur = off_next;
   }
 
+  if constexpr (TPI == 2) {  // the two token slots hold partial sums of the same dims
+#pragma unroll
+    for (int g = 0; g < GM; ++g)
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[g][e] += __shfl_xor_sync(kFull, acc[g][e], LPT);
+  }
 #pragma unroll
   for (int g = 0; g < GM; ++g) {
     if (g >= G) continue;
     const int hq = hkv * G + g;
     const float inv = l[g] > 0.f ? vsc / l[g] : 0.f;
     const int64_t row = (static_cast<int64_t>(c) * p.B + b) * p.Hq + hq;
+    if (ts == 0) {
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int d = E * lane + e;
-      if (d >= D) continue;
-      if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[g][e] * inv);
-      else p.part[row * p.row_floats + d] = acc[g][e] * inv;
+      for (int e = 0; e < E; ++e) {
+        const int d = E * wcol + e;
+        if (d >= D) continue;
+        if (p.part == nullptr) store_from_float(p.out, p.out_dtype, b * p.o_st[0] + hq * p.o_st[1] + d * p.o_st[2], acc[g][e] * inv);
+        else p.part[row * p.row_floats + d] = acc[g][e] * inv;
+      }
     }
     if (p.part != nullptr && lane == 0)
       p.part[row * p.row_floats + D] = l[g] > 0.f ? (m[g] + log2f(l[g])) * 0.6931471805599453f : -INFINITY;
@@ -1751,20 +1778,21 @@ int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
   // serves the whole group
   if (p.cache_kind == kCacheInt8 && p.D % 4 == 0 && p.D <= 256 && p.G <= 16 && p.kc_st[3] == 1 && p.vc_st[3] == 1) {
     const int gm = p.G <= 4 ? 4 : (p.G <= 8 ? 8 : 16);
-    const int e = p.D <= 64 ? 2 : (p.D <= 128 ? 4 : 8);
+    const int e = p.D <= 128 ? 4 : 8;       // elements per lane in the P.V phase
+    const int tpi = p.D <= 64 ? 2 : 1;      // tokens per V load: half a warp covers a row of up to 64 bytes
     if (gm * e <= 64) {
       const int64_t gitems = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
       const unsigned ggrid = static_cast<unsigned>((gitems + 3) / 4);
       const size_t smem = static_cast<size_t>(4) * (gm * 32 * e + gm * 32) * sizeof(float);  // queries + probabilities
       auto grouped = [&](auto kernel) { return launch_pdl(kernel, ggrid, 128, smem, stream, p); };
-      if (gm == 4 && e == 2) return grouped(paged_attn_grouped_kernel<4, 2>);
-      if (gm == 4 && e == 4) return grouped(paged_attn_grouped_kernel<4, 4>);
-      if (gm == 4 && e == 8) return grouped(paged_attn_grouped_kernel<4, 8>);
-      if (gm == 8 && e == 2) return grouped(paged_attn_grouped_kernel<8, 2>);
-      if (gm == 8 && e == 4) return grouped(paged_attn_grouped_kernel<8, 4>);
-      if (gm == 8 && e == 8) return grouped(paged_attn_grouped_kernel<8, 8>);
-      if (gm == 16 && e == 2) return grouped(paged_attn_grouped_kernel<16, 2>);
-      return grouped(paged_attn_grouped_kernel<16, 4>);
+      if (gm == 4 && tpi == 2) return grouped(paged_attn_grouped_kernel<4, 4, 2>);
+      if (gm == 4 && e == 4) return grouped(paged_attn_grouped_kernel<4, 4, 1>);
+      if (gm == 4 && e == 8) return grouped(paged_attn_grouped_kernel<4, 8, 1>);
+      if (gm == 8 && tpi == 2) return grouped(paged_attn_grouped_kernel<8, 4, 2>);
+      if (gm == 8 && e == 4) return grouped(paged_attn_grouped_kernel<8, 4, 1>);
+      if (gm == 8 && e == 8) return grouped(paged_attn_grouped_kernel<8, 8, 1>);
+      if (tpi == 2) return grouped(paged_attn_grouped_kernel<16, 4, 2>);
+      return grouped(paged_attn_grouped_kernel<16, 4, 1>);
     }
   }
   const unsigned grid = static_cast<unsigned>((items + 3) / 4);
