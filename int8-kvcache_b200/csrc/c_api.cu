@@ -383,7 +383,8 @@ int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads
   const int sm = sm_count > 0 ? sm_count : 148;
   const int64_t tiles = (max_seq_len + 15) / 16;
   int64_t n = ws_bytes(batch, num_q_heads, head_dim, choose_splits(batch, num_kv_heads, max_seq_len, block_size, sm));
-  if (head_dim != 128)  // a shape for the untiled kernels, which split further
+  // a shape for the untiled kernels, which split further
+  if (head_dim != 128 || block_size % 16 != 0 || num_q_heads / num_kv_heads > 8)
     n = std::max(n, ws_bytes(batch, num_q_heads, head_dim, untiled_splits(batch, num_kv_heads, max_seq_len, sm)));
   if (batch > 0 && tiles > 0 && plan_possible(batch, num_kv_heads, sm)) {
     const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm);

@@ -1202,7 +1202,7 @@ __device__ __forceinline__ void prefetch_to_l2(const void* ptr) {
 }
 
 template <int GM, int E, int TPI>
-__global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(128, GM == 4 ? 4 : (GM == 8 ? 3 : 2)) paged_attn_grouped_kernel(const AttnParams p) {
   static_assert((E == 4 && (TPI == 1 || TPI == 2)) || (E == 8 && TPI == 1), "lane layouts of the P.V phase");
   constexpr int LPT = kWarp / TPI;  // lanes that share one token in the P.V phase
   extern __shared__ __align__(16) float q_smem[];
@@ -1225,38 +1225,63 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
   int64_t tok_hi = (c + 1) * per * p.block_size;
   if (tok_hi > sl) tok_hi = sl;
 
-  // queries of the group, multiplied by everything that is constant per head, into this warp's shared memory;
-  // behind them the step's probabilities [token][GM]
-  float* qs = q_smem + warp * (GM * 32 * E + GM * 32);
-  float* ps = qs + GM * 32 * E;
+  // Queries of the group as two INT8 limbs per element, four elements per word, in this warp's shared memory:
+  // q ~= q_mul * (256 * hi + lo), |256 hi + lo| <= 32000 (16-bit fixed point per head, as in the tiled kernel), so
+  // that a K word meets a query word in one dp4a per limb.  With quantize_q the reference's INT8 query (absmax/127,
+  // half away from zero) sits in the low limb alone.  Behind the limbs: the step's probabilities [token][GM].
+  int2* qw = reinterpret_cast<int2*>(q_smem + warp * (GM * 16 * E + GM * 32));
+  float* ps = reinterpret_cast<float*>(qw + GM * 8 * E);
+  const int row_words = D >> 2;
   const float ksc = p.k_scale ? fmaxf(__ldg(p.k_scale + hkv), 1e-6f) : 1.f;
   const float vsc = p.v_scale ? fmaxf(__ldg(p.v_scale + hkv), 1e-6f) : 1.f;
-  for (int g = 0; g < G; ++g) {
+  float hmul[GM];  // score multiplier per head: k_scale * softmax scale * log2(e) * q_mul
+#pragma unroll
+  for (int g = 0; g < GM; ++g) {
+    hmul[g] = 0.f;
+    if (g >= G) {  // unused heads of the template's group: zero limbs, so that the score loop needs no test per head
+#pragma unroll
+      for (int r = 0; r < E / 4; ++r)
+        if (lane + kWarp * r < row_words) qw[g * row_words + lane + kWarp * r] = make_int2(0, 0);
+      continue;
+    }
     const int hq = hkv * G + g;
     float x[E];
     float amax = 0.f;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      const int d = lane + kWarp * e;
+      const int d = 4 * lane + 128 * (e >> 2) + (e & 3);  // word lane + 32 (e / 4), element e % 4
       x[e] = d < D ? load_as_float(p.q, p.q_dtype, b * p.q_st[0] + hq * p.q_st[1] + d * p.q_st[2]) : 0.f;
       amax = fmaxf(amax, fabsf(x[e]));
     }
-    float mul = ksc * p.sm_scale_log2;
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
+    int qi[E];
+    float q_mul;
     if (p.quantize_q) {
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, o));
       const float qscale = fmaxf(amax / 127.f, 1e-6f);
 #pragma unroll
       for (int e = 0; e < E; ++e) {
         const float y = x[e] / qscale;
         const float r = y >= 0.f ? floorf(y + 0.5f) : -floorf(-y + 0.5f);
-        x[e] = fminf(fmaxf(r, -127.f), 127.f);
+        qi[e] = static_cast<int>(fminf(fmaxf(r, -127.f), 127.f));
       }
-      mul *= qscale;
-    }
+      q_mul = qscale;
+    } else {
+      const float inv = amax > 0.f ? 32000.f / amax : 0.f;
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int d = lane + kWarp * e;
-      if (d < D) qs[g * D + d] = x[e] * mul;
+      for (int e = 0; e < E; ++e) qi[e] = __float_as_int(fmaf(x[e], inv, kRoundMagic)) - kRoundMagicBits;
+      q_mul = amax > 0.f ? amax / 32000.f : 0.f;
+    }
+    hmul[g] = ksc * p.sm_scale_log2 * q_mul;
+    // v = 256 * hi + lo with lo in [-128, 127]: lo is the low byte of v, hi the second byte of v + 128
+#pragma unroll
+    for (int r = 0; r < E / 4; ++r) {
+      const uint32_t v0 = static_cast<uint32_t>(qi[4 * r]), v1 = static_cast<uint32_t>(qi[4 * r + 1]);
+      const uint32_t v2 = static_cast<uint32_t>(qi[4 * r + 2]), v3 = static_cast<uint32_t>(qi[4 * r + 3]);
+      const uint32_t lo = prmt(prmt(v0, v1, 0x0040u), prmt(v2, v3, 0x0040u), 0x5410u);
+      const uint32_t hi = p.quantize_q ? 0u
+                                       : prmt(prmt(v0 + 128u, v1 + 128u, 0x0051u), prmt(v2 + 128u, v3 + 128u, 0x0051u), 0x5410u);
+      const int word = lane + kWarp * r;
+      if (word < row_words) qw[g * row_words + word] = make_int2(static_cast<int>(hi), static_cast<int>(lo));
     }
   }
   __syncwarp();
@@ -1300,8 +1325,7 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
 
   constexpr int VW = E / 4;                                // registers per load of a lane's V elements
   constexpr int VI = kWarp / TPI;                          // V loads per step and lane (TPI tokens per load)
-  constexpr int VU = E == 8 ? 8 : (GM >= 16 ? 16 : VI);    // loads in flight together
-  constexpr int NA = GM <= 8 ? 2 : 1;                      // score accumulators per head (shorter FMA chains)
+  constexpr int VU = (E == 8 || GM >= 16) ? 8 : (GM >= 8 && VI > 16 ? 16 : VI);  // loads in flight together
   const int ts = lane / LPT, wcol = lane % LPT;            // P.V phase: token slot and word column of this lane
   const bool v_lane = E * wcol < D;
 
@@ -1387,11 +1411,9 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
     load_v(0);
 
     // ---- scores of token tok0 + lane against every head of the group ----
-    float sc[GM][NA];
+    int sc_hi[GM], sc_lo[GM];  // integer dot products of the K row with the two query limbs
 #pragma unroll
-    for (int g = 0; g < GM; ++g)
-#pragma unroll
-      for (int n = 0; n < NA; ++n) sc[g][n] = 0.f;
+    for (int g = 0; g < GM; ++g) sc_hi[g] = sc_lo[g] = 0;
     float vt = 1.f, kt = 1.f;
     if (ok) {
       const int8_t* krow = kc + blk * p.kc_st[0] + off_cur * p.kc_st[1];
@@ -1427,24 +1449,16 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
             }
           }
         }
+        // Words beyond the row were loaded as 0 and meet whatever limbs follow in shared memory (still inside this
+        // warp's region): no test per word or per head.
+        const int2* qrow = qw + (d0 >> 2);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int d = d0 + 4 * i;
-          if (d < D) {
-            const uint32_t kb = static_cast<uint32_t>(w[i]) ^ 0x80808080u;
-            const float k0 = s8_of_word<0>(kb), k1 = s8_of_word<1>(kb), k2 = s8_of_word<2>(kb), k3 = s8_of_word<3>(kb);
 #pragma unroll
-            for (int g = 0; g < GM; ++g) {
-              if (g < G) {
-                const float4 qv = *reinterpret_cast<const float4*>(qs + g * D + d);  // same address in every lane
-                float a = sc[g][i % NA];
-                a = fmaf(k0, qv.x, a);
-                a = fmaf(k1, qv.y, a);
-                a = fmaf(k2, qv.z, a);
-                a = fmaf(k3, qv.w, a);
-                sc[g][i % NA] = a;
-              }
-            }
+          for (int g = 0; g < GM; ++g) {
+            const int2 qq = qrow[g * row_words + i];  // same address in every lane
+            sc_hi[g] = __dp4a(w[i], qq.x, sc_hi[g]);
+            sc_lo[g] = __dp4a(w[i], qq.y, sc_lo[g]);
           }
         }
       }
@@ -1455,7 +1469,7 @@ __global__ void __launch_bounds__(128) paged_attn_grouped_kernel(const AttnParam
     for (int g = 0; g < GM; ++g) {
       pr[g] = 0.f;
       if (g < G) {
-        const float score = (NA == 2 ? sc[g][0] + sc[g][NA - 1] : sc[g][0]) * kt;
+        const float score = static_cast<float>(sc_hi[g] * 256 + sc_lo[g]) * (hmul[g] * kt);
         float top = ok ? score : -INFINITY;
         for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
         const float mn = fmaxf(m[g], top);
@@ -1783,7 +1797,7 @@ int launch_attn_generic(const AttnParams& p, cudaStream_t stream) {
     if (gm * e <= 64) {
       const int64_t gitems = static_cast<int64_t>(p.B) * p.num_splits * p.Hkv;
       const unsigned ggrid = static_cast<unsigned>((gitems + 3) / 4);
-      const size_t smem = static_cast<size_t>(4) * (gm * 32 * e + gm * 32) * sizeof(float);  // queries + probabilities
+      const size_t smem = static_cast<size_t>(4) * (gm * 16 * e + gm * 32) * sizeof(float);  // query limbs + probabilities
       auto grouped = [&](auto kernel) { return launch_pdl(kernel, ggrid, 128, smem, stream, p); };
       if (gm == 4 && tpi == 2) return grouped(paged_attn_grouped_kernel<4, 4, 2>);
       if (gm == 4 && e == 4) return grouped(paged_attn_grouped_kernel<4, 4, 1>);
