@@ -1179,16 +1179,19 @@ __global__ void __launch_bounds__(128) paged_attn_generic_kernel(const AttnParam
 // Grouped kernel for INT8 caches outside the tiled kernels' shapes (head_dim != 128, odd block sizes): one warp per
 // (sequence, KV head, split) serves the whole GQA group from one read of the pages, with plain loads, 32 tokens
 // per step.
-//   rows:    lane = token.  The rows of the NEXT step are located first and requested into L2, so that every
-//            step but a part's first finds its rows there instead of in DRAM.
+//   rows:    lane = token.  A part's first rows are requested into L2 before the queries are staged, and the rows
+//            of the NEXT step at the top of every step, so that the loads that need them find them there
+//            instead of in DRAM.
 //   scores:  lane = token.  Each lane walks its token's K row (16-byte loads when the layout allows) against the
-//            group's queries, which sit pre-scaled in shared memory and are read as broadcasts: no shuffle per
-//            dot product.
+//            group's queries, which sit in shared memory as two INT8 limbs per element and are read as
+//            broadcasts: one dp4a per K word, head and limb, no shuffle and no conversion per dot product.
 //   softmax: per head over the 32 tokens of the step (warp max and sum); the probabilities go to shared memory.
-//   P.V:     lane = dims [E lane, E lane + E).  The V rows of the step are requested BEFORE the scores are computed
-//            (they do not depend on them), one load of E bytes per token and lane; afterwards, token by token,
-//            the group's probabilities are one broadcast read and the row is already in registers.
-// GM bounds the group (registers per head), E = elements per lane; head_dim % 4 == 0, head_dim <= 32 * E.
+//   P.V:     32 / TPI lanes share a token, each with E consecutive dims (TPI = 2 for head_dim <= 64: two tokens
+//            per load instruction, their partial sums added at the end).  The V rows of the step are requested
+//            BEFORE the scores are computed (they do not depend on them), one load of E bytes per token and
+//            lane; afterwards, token by token, the group's probabilities are one broadcast read and the row is
+//            already in registers.
+// GM bounds the group (registers per head); head_dim % 4 == 0, head_dim <= 32 * E / TPI.
 // ---------------------------------------------------------------------------------------------
 // Byte i of a word of four INT8 values (already XORed with 0x80808080) as a float, without the conversion unit:
 // the byte becomes the low mantissa of 2^23 * 1.5 and the offset is subtracted on the FP32 adder.
@@ -1224,6 +1227,47 @@ __global__ void __launch_bounds__(128, GM == 4 ? 4 : (GM == 8 ? 3 : 2)) paged_at
   const int64_t tok_lo = c * per * p.block_size;
   int64_t tok_hi = (c + 1) * per * p.block_size;
   if (tok_hi > sl) tok_hi = sl;
+
+  const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc) + hkv * p.kc_st[2];  // this head's column of the caches
+  const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc) + hkv * p.vc_st[2];
+  // whole-launch layout facts: K rows readable 16 bytes at a time, a lane's V elements readable as one word
+  const bool k_vec = D % 16 == 0 && ((reinterpret_cast<uintptr_t>(p.kc) | static_cast<uintptr_t>(p.kc_st[0]) |
+                                      static_cast<uintptr_t>(p.kc_st[1]) | static_cast<uintptr_t>(p.kc_st[2])) & 15u) == 0;
+  const bool v_vec = D % E == 0 && ((reinterpret_cast<uintptr_t>(p.vc) | static_cast<uintptr_t>(p.vc_st[0]) |
+                                     static_cast<uintptr_t>(p.vc_st[1]) | static_cast<uintptr_t>(p.vc_st[2])) & (E - 1)) == 0;
+
+  // lane = token: logical block and offset of the lane's token, advanced by 32 tokens per step without a division
+  const int step_blocks = kWarp / p.block_size, step_rest = kWarp % p.block_size;
+  int64_t lb = (tok_lo + lane) / p.block_size;
+  int off = static_cast<int>(tok_lo + lane - lb * p.block_size);
+  // Physical block of token t (lane = token); -1 when the token is outside the part or its table entry is outside
+  // the cache (such a token is never read and gets weight 0).
+  auto locate = [&](int64_t t) -> int64_t {
+    if (t >= tok_hi) return -1;
+    const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
+    return blk >= 0 && blk < p.num_blocks ? blk : -1;
+  };
+  auto advance = [&]() {
+    lb += step_blocks;
+    off += step_rest;
+    if (off >= p.block_size) {
+      off -= p.block_size;
+      ++lb;
+    }
+  };
+
+  // The first step's rows are located and requested into L2 before anything else, so that the query staging below
+  // runs under their latency.
+  int64_t blk = locate(tok_lo + lane);
+  int off_cur = off;
+  if (blk >= 0) {
+    const int8_t* kr = kc + blk * p.kc_st[0] + off_cur * p.kc_st[1];
+    const int8_t* vr_first = vc + blk * p.vc_st[0] + off_cur * p.vc_st[1];
+    for (int d0 = 0; d0 < D; d0 += 32) {
+      prefetch_to_l2(kr + d0);
+      prefetch_to_l2(vr_first + d0);
+    }
+  }
 
   // Queries of the group as two INT8 limbs per element, four elements per word, in this warp's shared memory:
   // q ~= q_mul * (256 * hi + lo), |256 hi + lo| <= 32000 (16-bit fixed point per head, as in the tiled kernel), so
@@ -1295,42 +1339,12 @@ __global__ void __launch_bounds__(128, GM == 4 ? 4 : (GM == 8 ? 3 : 2)) paged_at
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
   }
-  const int8_t* kc = reinterpret_cast<const int8_t*>(p.kc) + hkv * p.kc_st[2];  // this head's column of the caches
-  const int8_t* vc = reinterpret_cast<const int8_t*>(p.vc) + hkv * p.vc_st[2];
-  // whole-launch layout facts: K rows readable 16 bytes at a time, a lane's V elements readable as one word
-  const bool k_vec = D % 16 == 0 && ((reinterpret_cast<uintptr_t>(p.kc) | static_cast<uintptr_t>(p.kc_st[0]) |
-                                      static_cast<uintptr_t>(p.kc_st[1]) | static_cast<uintptr_t>(p.kc_st[2])) & 15u) == 0;
-  const bool v_vec = D % E == 0 && ((reinterpret_cast<uintptr_t>(p.vc) | static_cast<uintptr_t>(p.vc_st[0]) |
-                                     static_cast<uintptr_t>(p.vc_st[1]) | static_cast<uintptr_t>(p.vc_st[2])) & (E - 1)) == 0;
-
-  // lane = token: logical block and offset of the lane's token, advanced by 32 tokens per step without a division
-  const int step_blocks = kWarp / p.block_size, step_rest = kWarp % p.block_size;
-  int64_t lb = (tok_lo + lane) / p.block_size;
-  int off = static_cast<int>(tok_lo + lane - lb * p.block_size);
-  // Physical block of token t (lane = token); -1 when the token is outside the part or its table entry is outside
-  // the cache (such a token is never read and gets weight 0).
-  auto locate = [&](int64_t t) -> int64_t {
-    if (t >= tok_hi) return -1;
-    const int64_t blk = load_index(p.bt, p.bt_is_i64, b * p.bt_st[0] + lb * p.bt_st[1]);
-    return blk >= 0 && blk < p.num_blocks ? blk : -1;
-  };
-  auto advance = [&]() {
-    lb += step_blocks;
-    off += step_rest;
-    if (off >= p.block_size) {
-      off -= p.block_size;
-      ++lb;
-    }
-  };
-
   constexpr int VW = E / 4;                                // registers per load of a lane's V elements
   constexpr int VI = kWarp / TPI;                          // V loads per step and lane (TPI tokens per load)
   constexpr int VU = (E == 8 || GM >= 16) ? 8 : (GM >= 8 && VI > 16 ? 16 : VI);  // loads in flight together
   const int ts = lane / LPT, wcol = lane % LPT;            // P.V phase: token slot and word column of this lane
   const bool v_lane = E * wcol < D;
 
-  int64_t blk = locate(tok_lo + lane);
-  int off_cur = off;
 
   for (int64_t tok0 = tok_lo; tok0 < tok_hi; tok0 += kWarp) {
     // the next step's rows: found now and requested into L2
