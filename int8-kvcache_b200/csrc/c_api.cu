@@ -112,15 +112,20 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   return static_cast<int>(s);
 }
 
-// Split count for the kernels outside the tiled shapes: they hide their load latency with warps, not with a
-// ring, so they want about 32 warps per SM in total (measured on a head_dim-64 layer: 8 x 4096 tokens 230 GB/s at
-// 16 parts, 364 GB/s at 32), but parts of at least 8 blocks of 16 tokens.
-int untiled_splits(int B, int Hkv, int64_t max_seq, int sm_count) {
-  const int64_t items = std::max<int64_t>(1, static_cast<int64_t>(B) * Hkv);
+// Split count for the kernels outside the tiled shapes.  They hide their load latency with resident warps, not
+// with a ring, and every part pays a prologue (query staging) and a partial row, so the best count is the one that
+// fills ONE resident wave: as many one-warp items as the SMs hold at the kernel's register cap (16 warps per SM for
+// groups up to 4, 12 up to 8, 8 up to 16; the generic kernel has one item per query head).  Measured on a
+// head_dim-64 layer of 64 x 2048 tokens with 8 KV heads (512 items): 2 parts 174 us, 4 parts (2048 warps, one wave)
+// 98 us, 8 parts 104 us, 16 parts 116 us, 32 parts 128 us.  Parts stay at least 8 blocks of 16 tokens long.
+int untiled_splits(int B, int Hq, int Hkv, int D, bool int8_cache, int64_t max_seq, int sm_count) {
+  const int G = Hq / std::max(1, Hkv);
+  const bool grouped = int8_cache && D % 4 == 0 && D <= 256 && G <= 16 && !(G > 8 && D > 128);
+  const int64_t items = std::max<int64_t>(1, static_cast<int64_t>(B) * (grouped ? Hkv : Hq));
+  const int per_sm = !grouped || G <= 4 ? 16 : (G <= 8 ? 12 : 8);
   const int64_t tiles = (max_seq + 15) / 16;
-  int64_t s = 1;
-  while (s * items < static_cast<int64_t>(sm_count) * 32) s *= 2;
-  s = std::min<int64_t>(s, pow2_floor(std::max<int64_t>(1, tiles / 8)));
+  int64_t s = static_cast<int64_t>(sm_count) * per_sm / items;
+  s = std::min<int64_t>(s, std::max<int64_t>(1, tiles / 8));
   return static_cast<int>(std::min<int64_t>(std::max<int64_t>(s, 1), kMaxSplits));
 }
 
@@ -248,7 +253,7 @@ int run_attention(const AttnCall& a) {
                      (rf % 4 == 0);
   if (!tiled && a.num_splits == 0) {
     // the automatic count above is fitted to the tiled kernels; use the untiled one if the workspace allows it
-    int su = untiled_splits(a.B, a.Hkv, max_seq, sm);
+    int su = untiled_splits(a.B, a.Hq, a.Hkv, a.D, a.cache_kind == kCacheInt8, max_seq, sm);
     if (su > tiles) su = tiles > 0 ? static_cast<int>(tiles) : 1;
     if (su <= 1 || (a.ws != nullptr && a.ws_bytes >= ws_bytes(a.B, a.Hq, a.D, su))) S = su;
   }
@@ -383,9 +388,11 @@ int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads
   const int sm = sm_count > 0 ? sm_count : 148;
   const int64_t tiles = (max_seq_len + 15) / 16;
   int64_t n = ws_bytes(batch, num_q_heads, head_dim, choose_splits(batch, num_kv_heads, max_seq_len, block_size, sm));
-  // a shape for the untiled kernels, which split further
+  // a shape for the untiled kernels, which have their own split rule
   if (head_dim != 128 || block_size % 16 != 0 || num_q_heads / num_kv_heads > 8)
-    n = std::max(n, ws_bytes(batch, num_q_heads, head_dim, untiled_splits(batch, num_kv_heads, max_seq_len, sm)));
+    for (const bool int8_cache : {true, false})
+      n = std::max(n, ws_bytes(batch, num_q_heads, head_dim,
+                               untiled_splits(batch, num_q_heads, num_kv_heads, head_dim, int8_cache, max_seq_len, sm)));
   if (batch > 0 && tiles > 0 && plan_possible(batch, num_kv_heads, sm)) {
     const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm);
     n = std::max(n, plan_layout(batch, num_q_heads, num_kv_heads, head_dim, ps.max_items).total);
