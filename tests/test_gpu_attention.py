@@ -208,6 +208,32 @@ def test_generic_path_shapes(kv, workloads):
     assert kv.device_status() == 0
 
 
+@pytest.mark.parametrize("hq,hkv,d,bs", [
+    (14, 2, 128, 8),    # group 7 on a block size the tiled kernels do not take
+    (14, 2, 64, 16),    # group 7, two tokens per V load
+    (32, 2, 64, 16),    # group 16, two tokens per V load
+    (8, 2, 256, 16),    # eight dims per lane
+    (16, 2, 256, 16),   # group 8 with eight dims per lane
+    (4, 2, 132, 16),    # head_dim % 8 == 4 and % 16 != 0: word K loads, byte V loads
+    (4, 2, 32, 16),     # half of the lanes idle in P.V
+    (2, 1, 16, 16),     # one K load per row
+    (8, 2, 64, 24),     # block sizes that do not divide a 32-token step
+    (8, 2, 64, 5),
+    (8, 2, 96, 48),
+])
+def test_grouped_kernel_variants(kv, workloads, hq, hkv, d, bs):
+    """Every instantiation and lane layout of the kernel that serves INT8 caches outside the tiled shapes, over
+    ragged lengths (a part that ends inside a step, a one-token sequence) and several split counts."""
+    shape = workloads.LayerShape(hq, hkv, d, bs)
+    lens = [1, 5, 64, 131, 300]
+    case, kc, vc = _case_on_gpu(kv, workloads, lens, shape=shape, seed=hq + d + bs)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    args = _dev(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
+    for splits in (None, 1, 3, 16):
+        _check(kv.int8_paged_attention(*args, num_splits=splits), want)
+    assert kv.device_status() == 0
+
+
 def test_larger_block_size_and_group_of_8(kv, workloads):
     shape = workloads.LayerShape(64, 8, 128, 32)  # 72B-style GQA 8:1, 32-token blocks
     lens = [31, 32, 33, 700]
