@@ -113,16 +113,19 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
 }
 
 // Split count for the kernels outside the tiled shapes.  They hide their load latency with resident warps, not
-// with a ring, and every part pays a prologue (query staging) and a partial row, so the best count is the one that
-// fills ONE resident wave: as many one-warp items as the SMs hold at the kernel's register cap (16 warps per SM for
-// groups up to 4, 12 up to 8, 8 up to 16; the generic kernel has one item per query head).  Measured on a
-// head_dim-64 layer of 64 x 2048 tokens with 8 KV heads (512 items): 2 parts 174 us, 4 parts (2048 warps, one wave)
-// 98 us, 8 parts 104 us, 16 parts 116 us, 32 parts 128 us.  Parts stay at least 8 blocks of 16 tokens long.
+// with a ring, and every part pays a prologue (query staging) and a partial row.
+//  - grouped INT8 kernel: the best count fills ONE resident wave, as many one-warp items as the SMs hold at the
+//    kernel's register cap (16 warps per SM for groups up to 4, 12 up to 8, 8 up to 16).  Measured on a head_dim-64
+//    layer of 64 x 2048 tokens with 8 KV heads (512 items): 2 parts 174 us, 4 parts (2048 warps, one wave) 98 us,
+//    8 parts 104 us, 16 parts 116 us, 32 parts 128 us.
+//  - generic kernel: one item per query head, fewer registers and more waiting per instruction, so it keeps about
+//    32 warps per SM (head_dim 66, 512 items: 2 parts 813 us, 4 parts 544 us, 8 parts 456 us).
+// Parts stay at least 8 blocks of 16 tokens long.
 int untiled_splits(int B, int Hq, int Hkv, int D, bool int8_cache, int64_t max_seq, int sm_count) {
   const int G = Hq / std::max(1, Hkv);
   const bool grouped = int8_cache && D % 4 == 0 && D <= 256 && G <= 16 && !(G > 8 && D > 128);
   const int64_t items = std::max<int64_t>(1, static_cast<int64_t>(B) * (grouped ? Hkv : Hq));
-  const int per_sm = !grouped || G <= 4 ? 16 : (G <= 8 ? 12 : 8);
+  const int per_sm = !grouped ? 32 : (G <= 4 ? 16 : (G <= 8 ? 12 : 8));
   const int64_t tiles = (max_seq + 15) / 16;
   int64_t s = static_cast<int64_t>(sm_count) * per_sm / items;
   s = std::min<int64_t>(s, std::max<int64_t>(1, tiles / 8));
