@@ -72,6 +72,20 @@ def test_automatic_workspace_covers_the_planned_path(lib):
     assert lib.int8kv_workspace_bytes_auto(0, 28, 4, 128, 512, 16, 148) == 16
 
 
+def test_automatic_workspace_covers_the_untiled_kernels(lib):
+    """Shapes the tiled kernels refuse (head_dim, block size or group) split by their own rule, one resident wave
+    of warps; the automatic size has to hold that many partial rows whichever of the three refuses."""
+    rows = lambda B, Hq, D, S: lib.int8kv_workspace_bytes(B, Hq, D, S)
+    # head_dim 64, group 4: 16 warps per SM on 148 SMs over 64 x 8 items = 4 parts
+    assert lib.int8kv_workspace_bytes_auto(64, 32, 8, 64, 2048, 16, 148) >= rows(64, 32, 64, 4)
+    # block size 8 at head_dim 128, group 7: 12 warps per SM over 32 x 4 items = 13 parts
+    assert lib.int8kv_workspace_bytes_auto(32, 28, 4, 128, 2048, 8, 148) >= rows(32, 28, 128, 13)
+    # group 16 at head_dim 128: 8 warps per SM over 32 x 4 items = 9 parts
+    assert lib.int8kv_workspace_bytes_auto(32, 64, 4, 128, 2048, 16, 148) >= rows(32, 64, 128, 9)
+    # parts stay at least 128 tokens long
+    assert lib.int8kv_workspace_bytes_auto(1, 32, 8, 64, 512, 16, 148) >= rows(1, 32, 64, 4)
+
+
 def test_split_heuristic(lib):
     cap = lib.int8kv_max_splits()
     assert cap >= 16
