@@ -13,6 +13,7 @@ reference prototype cjsmt/Int8-kvcache:
   * slot_mapping scatter write                           src/triton_ops/int8_cache_write.py:152-183
   * fp32 decode attention with contiguous GQA groups     src/attention_ref.py:11-28
   * paged INT8 attention loop reference                  src/triton_ops/int8_paged_attention.py:776-814
+  * optional per-head INT8 query (quantize_q)            src/triton_ops/int8_paged_attention.py:798-802
   * per-(slot, head) dequantisation                      vllm_int8/vllm_int8_cache_ops.py:250-256
   * split-KV partial merge                               src/triton_ops/int8_paged_attention.py:330-388
 
@@ -37,6 +38,7 @@ from .paged_cache import (  # noqa: F401
 from .attention_ref import (  # noqa: F401
     decode_attention,
     int8_paged_attention_oracle,
+    quantize_query_per_head,
     float_paged_attention_oracle,
     dynamic_int8_paged_attention_oracle,
     partial_attention_with_lse,

@@ -60,6 +60,17 @@ def merge_partials(outs: torch.Tensor, lses: torch.Tensor) -> torch.Tensor:
     return (outs * w.unsqueeze(-1)).sum(dim=0) / denom.unsqueeze(-1)
 
 
+def quantize_query_per_head(q: torch.Tensor) -> torch.Tensor:
+    """The reference's optional INT8 query (src/triton_ops/int8_paged_attention.py:798-802, kernel side :137-146):
+    per query head, scale = max(absmax / 127, 1e-6), q8 = clamp(round_half_away_from_zero(q / scale), -127, 127),
+    and the dot product uses q8 * scale.  q [..., D] -> fp32 of the same shape."""
+    qf = q.to(torch.float32)
+    scale = torch.clamp(qf.abs().amax(dim=-1, keepdim=True) / 127.0, min=1e-6)
+    x = qf / scale
+    q8 = torch.where(x >= 0, torch.floor(x + 0.5), -torch.floor(-x + 0.5))
+    return torch.clamp(q8, -127, 127) * scale
+
+
 def int8_paged_attention_oracle(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -68,14 +79,17 @@ def int8_paged_attention_oracle(
     seq_lens: Sequence[int],
     k_scale: torch.Tensor,
     v_scale: torch.Tensor,
+    quantize_q: bool = False,
 ) -> torch.Tensor:
-    """[B, Hq, D] fp32: gather pages -> int8 * scale[head] -> fp32 attention."""
+    """[B, Hq, D] fp32: gather pages -> int8 * scale[head] -> fp32 attention.  quantize_q: the query is first
+    replaced by its per-head INT8 quantisation (quantize_query_per_head)."""
     ks, vs = gather_paged_cache(key_cache, value_cache, block_tables, seq_lens)
     rows = []
     for b in range(query.shape[0]):
         k = dequant_per_head(ks[b], k_scale, head_axis=0)
         v = dequant_per_head(vs[b], v_scale, head_axis=0)
-        rows.append(decode_attention(query[b], k, v))
+        q = quantize_query_per_head(query[b]) if quantize_q else query[b]
+        rows.append(decode_attention(q, k, v))
     return torch.stack(rows)
 
 

@@ -18,7 +18,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 PACKAGE = "int8-kvcache_b200"
 
 # payload dtypes of the uint16-encoded arrays in the golden files
-_BF16_KEYS = {"query", "key", "value", "out_loop_bf16", "out_unquantised_bf16"}
+_BF16_KEYS = {"query", "key", "value", "out_loop_bf16", "out_loop_quantize_q_bf16", "out_unquantised_bf16"}
 _FP16_KEYS = {"k", "v"}
 
 

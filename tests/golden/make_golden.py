@@ -128,11 +128,14 @@ def main() -> None:
         vc = torch.zeros_like(kc)
         wr.torch_int8_kv_cache_write_reference(torch.cat(keys), torch.cat(values), kc, vc, slots, k_scale, v_scale)
         out_loop = pa.torch_int8_paged_attention_reference(query, kc, vc, tables, seq_lens, k_scale, v_scale)
+        out_loop_qq = pa.torch_int8_paged_attention_reference(query, kc, vc, tables, seq_lens, k_scale, v_scale,
+                                                              quantize_q=True)
         out_chain = chain_attention(ref, query, kc, vc, tables, seq_lens, k_scale, v_scale)
         out_bf16 = rtests.torch_bf16_attention_reference(query, keys, values)
         save(name, query=query, key=torch.cat(keys), value=torch.cat(values), k_scale=k_scale, v_scale=v_scale,
              block_tables=tables, seq_lens=seq_lens, slot_mapping=slots, key_cache=kc, value_cache=vc,
-             out_loop_bf16=out_loop, out_chain_f32=out_chain, out_unquantised_bf16=out_bf16)
+             out_loop_bf16=out_loop, out_loop_quantize_q_bf16=out_loop_qq, out_chain_f32=out_chain,
+             out_unquantised_bf16=out_bf16)
 
     # 5. config 1: B=1, 512 context tokens + 1 written token, outlier keys, calibrated scales, 64-block pool
     case = workloads.config1_case(seed=0)

@@ -193,12 +193,9 @@ def test_generic_path_shapes(kv, workloads):
     wide_k[..., 1:65], wide_v[..., 1:65] = kc.cuda(), vc.cuda()
     q, bt, sl, ks, vs = _dev(case.query, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)
     _check(kv.int8_paged_attention(q, wide_k[..., 1:65], wide_v[..., 1:65], bt, sl, ks, vs), want)
-    from conftest import package
-
-    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
-    wantq = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
-    outq = kv.int8_paged_attention(q, kc.cuda(), vc.cuda(), bt, sl, ks, vs, quantize_q=True).float().cpu()
-    assert cosine(outq, wantq.float()) >= MIN_COS and max_abs(outq, wantq.float()) <= MAX_ABS
+    wantq = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale,
+                                               quantize_q=True)
+    _check(kv.int8_paged_attention(q, kc.cuda(), vc.cuda(), bt, sl, ks, vs, quantize_q=True), wantq)
     kb = torch.zeros(case.num_blocks, 16, 2, 64, dtype=torch.bfloat16)
     vb = torch.zeros_like(kb)
     s_ = case.slot_mapping
@@ -246,17 +243,27 @@ def test_larger_block_size_and_group_of_8(kv, workloads):
     assert kv.device_status() == 0
 
 
-def test_quantize_q_matches_its_definition(kv, workloads):
-    from conftest import package
+@pytest.mark.parametrize("name", ["attn_127_301", "attn_97_256"])
+def test_quantize_q_matches_the_reference_vectors(kv, name):
+    """quantize_q=True against what the reference's own loop returned for it on the golden cases (generated by
+    tests/golden/make_golden.py from src/triton_ops/int8_paged_attention.py:776-814), for the automatic split and
+    forced ones, and against the oracle's restatement on a seeded case."""
+    g = load_golden(name)
+    want = oracle.int8_paged_attention_oracle(g["query"], g["key_cache"], g["value_cache"], g["block_tables"],
+                                              g["seq_lens"].tolist(), g["k_scale"], g["v_scale"], quantize_q=True)
+    for splits in (None, 1, 4):
+        out = _run_int8(kv, g, quantize_q=True, num_splits=splits)
+        _check(out, want, g["out_loop_quantize_q_bf16"])
 
-    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
+
+def test_quantize_q_on_a_seeded_case(kv, workloads):
     lens = [200, 45]
     case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=10)
-    want = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
+    want = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale,
+                                              quantize_q=True)
     out = kv.int8_paged_attention(*_dev(case.query, kc, vc, case.block_tables, case.seq_lens,
                                         case.k_scale, case.v_scale), quantize_q=True)
-    assert cosine(out.float().cpu(), want.float()) >= MIN_COS
-    assert max_abs(out.float().cpu(), want.float()) <= MAX_ABS
+    _check(out, want)
 
 
 def test_max_seq_len_hint_skips_validation_and_zero_length_is_safe(kv, workloads):
@@ -454,12 +461,9 @@ def test_device_planned_splits(kv, workloads):
     kb[s_ // 16, s_ % 16], vb[s_ // 16, s_ % 16] = case.key, case.value
     wantb = oracle.float_paged_attention_oracle(case.query, kb, vb, case.block_tables, lens)
     _check(kv.bf16_paged_attention(q, kb.cuda(), vb.cuda(), bt, sl, num_splits="planned"), wantb)
-    from conftest import package
-
-    ref = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
-    wantq = ref(case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale, quantize_q=True)
-    outq = kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits="planned", quantize_q=True).float().cpu()
-    assert cosine(outq, wantq.float()) >= MIN_COS and max_abs(outq, wantq.float()) <= MAX_ABS
+    wantq = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale,
+                                               quantize_q=True)
+    _check(kv.int8_paged_attention(q, kcd, vcd, bt, sl, ks, vs, num_splits="planned", quantize_q=True), wantq)
     assert kv.device_status() == 0
 
 
@@ -622,7 +626,9 @@ def _dynamic_case(workloads, lens, shape, seed, v_gain=None):
 
 
 def test_dynamic_scale_attention_tiled_path(kv, workloads):
-    """Attention over the per-(token, head) scale scheme equals the fp32 attention of the dequantised cache."""
+    """Attention over the per-(token, head) scale scheme equals the fp32 attention of the dequantised cache.
+    Parity unpinned (no CPU definition in the reference): it has a writer and a dequantiser for this scheme but no
+    attention over it; the expectation is fp32 attention over what its dequantize_int8_cache formula reconstructs."""
     lens = [513, 97, 1030, 16, 1, 31, 2048]
     case, kc, vc, ksc, vsc = _dynamic_case(workloads, lens, workloads.QWEN25_7B, seed=21)
     want = oracle.dynamic_int8_paged_attention_oracle(case.query, kc, vc, ksc, vsc, case.block_tables, lens)
@@ -641,7 +647,8 @@ def test_dynamic_scale_attention_tiled_path(kv, workloads):
 
 def test_dynamic_scale_attention_wide_value_range(kv, workloads):
     """Token scales that differ by orders of magnitude inside one sequence (tiny first tokens, huge later ones and
-    the reverse) keep their precision through the fp16 P.V product."""
+    the reverse) keep their precision through the fp16 P.V product.  Parity unpinned (no CPU definition in the
+    reference), as for the test above."""
     lens = [700, 700, 64]
     g = torch.Generator().manual_seed(5)
     total = sum(lens)
@@ -668,7 +675,8 @@ def test_dynamic_scale_attention_wide_value_range(kv, workloads):
 
 def test_dynamic_scale_attention_generic_path_and_write_chain(kv, workloads):
     """Shapes outside the tiled kernel (D=64, BS=8, group 4), and the whole chain on the device:
-    reshape_and_cache_int8 writes the caches and scale caches that the attention then reads."""
+    reshape_and_cache_int8 writes the caches and scale caches that the attention then reads.  Parity unpinned (no
+    CPU definition in the reference), as for the tests above."""
     from conftest import package
 
     ops = package("vllm_int8.vllm_int8_cache_ops")

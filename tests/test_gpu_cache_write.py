@@ -158,7 +158,9 @@ def test_empty_and_argument_errors(kv):
 
 def test_dynamic_per_token_head_write(kv):
     """The reference's alternative scheme: bit-exact against the restated kernel arithmetic, and the
-    reference test's own bound (mean abs dequantisation error < 0.02; tests/test_vllm_int8_cache_ops.py)."""
+    reference test's own bound (mean abs dequantisation error < 0.02; tests/test_vllm_int8_cache_ops.py).
+    Parity unpinned: the reference defines this scheme only as a Triton kernel (no CPU definition to run), so the
+    byte-level expectation is this repository's restatement of that kernel; the MAE bound is all the reference holds."""
     from conftest import package
 
     ops = package("vllm_int8.vllm_int8_cache_ops")

@@ -62,8 +62,12 @@ def test_large_ragged_batch(kv, workloads):
     assert kv.device_status() == 0
     # peaked rows reach magnitudes of 2-4, where one bf16 ulp is already 0.016: the bound scales with the output
     bound = 2e-2 * max(1.0, float(auto.float().abs().max()))
+    worst = 0.0
     for other in (one, many):
+        worst = max(worst, max_abs(auto.float(), other.float()))
         assert max_abs(auto.float(), other.float()) <= bound and cosine(auto.float(), other.float()) >= 0.9999
+    print(f"split invariance on the 256-sequence ragged batch: worst max-abs between split counts {worst:.4g} "
+          f"(bound {bound:.4g}, largest |out| {float(auto.float().abs().max()):.4g})")
     rows = [0, 255, int(torch.tensor(seq_lens).argmax()), int(torch.tensor(seq_lens).argmin())]
     for b, want in _oracle_rows(q, kc, vc, tables, seq_lens, ks, vs, rows).items():
         got = auto[b].float().cpu()

@@ -73,6 +73,30 @@ def test_attention_97_256():
     _attention_case("attn_97_256")
 
 
+def test_quantize_q_definition_matches_the_reference_loop():
+    """The optional INT8 query: the oracle, and the debug helper of the drop-in module that carries the reference's
+    name, must both reproduce what the reference's torch_int8_paged_attention_reference(..., quantize_q=True)
+    returned (src/triton_ops/int8_paged_attention.py:776-814), to one bf16 ulp."""
+    from conftest import package
+
+    helper = package("triton_ops.int8_paged_attention").torch_int8_paged_attention_reference
+    for name in ("attn_127_301", "attn_97_256"):
+        g = load_golden(name)
+        want = g["out_loop_quantize_q_bf16"].float()
+        ulp = 2 ** -8 * float(want.abs().max())
+        out = oracle.int8_paged_attention_oracle(g["query"], g["key_cache"], g["value_cache"], g["block_tables"],
+                                                 g["seq_lens"].tolist(), g["k_scale"], g["v_scale"], quantize_q=True)
+        assert max_abs(out.to(torch.bfloat16).float(), want) <= ulp
+        # the quantised query is not the plain one: the two references differ by more than rounding
+        assert max_abs(want, g["out_loop_bf16"].float()) > 0
+        got = helper(g["query"], g["key_cache"], g["value_cache"], g["block_tables"], g["seq_lens"], g["k_scale"],
+                     g["v_scale"], quantize_q=True)
+        assert got.dtype == torch.bfloat16 and max_abs(got.float(), want) <= ulp
+        plain = helper(g["query"], g["key_cache"], g["value_cache"], g["block_tables"], g["seq_lens"], g["k_scale"],
+                       g["v_scale"])
+        assert max_abs(plain.float(), g["out_loop_bf16"].float()) <= ulp
+
+
 def test_config1_chain():
     g = load_golden("config1")
     key, value = g["key"], g["value"]
