@@ -463,6 +463,7 @@ def leg_sweep(ctx, variants=True):
     over enough distinct layer caches to exceed the L2."""
     kv, wl, device = ctx.kv, ctx.wl, ctx.device
     hq, hkv = wl.QWEN25_7B.num_q_heads, wl.QWEN25_7B.num_kv_heads
+    ready = not ctx.args.ordered  # every input of a step is resident before the step starts
     cells = []
     for B in (1, 2, 4, 8):
         for seq in (512, 1024, 2048, 4096):
@@ -473,11 +474,12 @@ def leg_sweep(ctx, variants=True):
             def int8_step(**kw):
                 for x in L:
                     kv.int8_paged_attention(x.query, x.kc, x.vc, x.block_tables, x.seq_lens, x.k_scale, x.v_scale,
-                                            max_seq_len=seq, out=x.out, **kw)
+                                            max_seq_len=seq, out=x.out, inputs_ready=ready, **kw)
 
             def bf16_step():
                 for x in L:
-                    kv.bf16_paged_attention(x.query, x.kb, x.vb, x.block_tables, x.seq_lens, max_seq_len=seq, out=x.out)
+                    kv.bf16_paged_attention(x.query, x.kb, x.vb, x.block_tables, x.seq_lens, max_seq_len=seq, out=x.out,
+                                            inputs_ready=ready)
 
             i8 = ctx.time_device(int8_step) / layers * 1e3
             bf = ctx.time_device(bf16_step) / layers * 1e3
@@ -524,15 +526,22 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
             L.ksc = torch.rand(L.kc.shape[:3], device=device, generator=gen_s) * 0.02 + 0.005
             L.vsc = torch.rand(L.kc.shape[:3], device=device, generator=gen_s) * 0.02 + 0.005
     nbytes_step = nbytes_call * layers
+    # Every input of a step (queries, caches, tables, lengths, scales) is resident before the step starts and no
+    # layer reads what another writes, so the calls carry the inputs-ready promise: each may start streaming its
+    # pages while the previous call's split-KV merge finishes.  --ordered turns the promise off.
+    ready = not args.ordered
+    config["call_ordering"] = ("inputs-ready promise (INT8KV_FLAG_INPUTS_READY) on every call, INT8 and BF16 alike"
+                               if ready else "every call fully ordered behind the previous one")
 
     def device_step():
         for L in layers_data:
             if dynamic:
                 kv.int8_paged_attention_dynamic(L.query, L.kc, L.vc, L.ksc, L.vsc, L.block_tables, L.seq_lens,
-                                                num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
+                                                num_splits=args.num_splits, max_seq_len=max_seq, out=L.out,
+                                                inputs_ready=ready)
             else:
                 kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
-                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L.out)
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L.out, inputs_ready=ready)
 
     lib = kv._lib.load()
     splits = args.num_splits or lib.int8kv_choose_splits(B, hkv, max_seq, 16, ctx.sm)
@@ -569,7 +578,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         def warm_step():
             for _ in range(layers):
                 kv.int8_paged_attention(L0.query, L0.kc, L0.vc, L0.block_tables, L0.seq_lens, L0.k_scale, L0.v_scale,
-                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L0.out)
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L0.out, inputs_ready=ready)
 
         warm_ms = ctx.time_device(warm_step)
 
@@ -578,7 +587,8 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
     if want_bf16:
         def bf16_step():
             for L in layers_data:
-                kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens, max_seq_len=max_seq, out=L.out)
+                kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens, max_seq_len=max_seq, out=L.out,
+                                        inputs_ready=ready)
 
         bf16_ms = ctx.time_device(bf16_step)
         for L in layers_data:
@@ -639,8 +649,10 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
             d_in.copy_(h_in, non_blocking=True)
             for i, L in enumerate(layers_data):
                 q, k, v = dv[i]
+                # the first layer's kernel follows the host-to-device copy and orders itself behind it
                 kv.int8_decode_step(q, k, v, L.kc, L.vc, d_slots, d_bt, d_sl, L.k_scale, L.v_scale,
-                                    num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i])
+                                    num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i],
+                                    inputs_ready=ready and i > 0)
             h_out.copy_(d_out, non_blocking=True)
 
         def eager_step():
@@ -654,7 +666,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
                                        [dv[i][2] for i in range(layers)], [L.kc for L in layers_data],
                                        [L.vc for L in layers_data], d_slots, d_bt, d_sl,
                                        [L.k_scale for L in layers_data], [L.v_scale for L in layers_data],
-                                       num_splits=args.num_splits, max_seq_len=max_seq, out=d_out)
+                                       num_splits=args.num_splits, max_seq_len=max_seq, out=d_out, inputs_ready=ready)
 
         def layers_step():
             d_in.copy_(h_in, non_blocking=True)
@@ -817,6 +829,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
     ap.add_argument("--no-bf16", dest="bf16_baseline", action="store_false", help="skip the same-run BF16 baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--ordered", action="store_true",
+                    help="do not pass the inputs-ready promise: every call waits for the previous one to finish")
     ap.add_argument("--scales", default="static", choices=["static", "dynamic"],
                     help="dynamic: time the attention over per-(token, head) scale caches (device leg only)")
     ap.add_argument("--sweep", action="store_true",

@@ -28,7 +28,7 @@
 extern "C" {
 #endif
 
-#define INT8KV_ABI_VERSION 1
+#define INT8KV_ABI_VERSION 2
 
 /* status codes */
 #define INT8KV_OK 0
@@ -53,6 +53,23 @@ extern "C" {
 #define INT8KV_SPLITS_PLANNED (-1) /* always plan on the device; INT8KV_E_UNSUPPORTED for shapes outside the tiled
                                       kernels, more than 512 sequences or more (sequence, head) pairs than resident
                                       warps; INT8KV_E_WORKSPACE below int8kv_workspace_bytes_auto() bytes */
+
+/*
+ * `flags` of the attention entry points (a bit set; 0 = none).
+ *   INT8KV_FLAG_QUANTIZE_Q    quantise each query head to INT8 (absmax/127, round half away from zero) before the
+ *                             dot product, the reference's QUANTIZE_Q option (src/triton_ops/int8_paged_attention.py
+ *                             :137-146).  INT8 caches with static scales only.
+ *   INT8KV_FLAG_INPUTS_READY  a promise by the caller: nothing this call READS (query, new K/V rows, slot mapping,
+ *                             block tables, sequence lengths, caches, scales) is written by the kernel that
+ *                             precedes the call on `stream`.  The tiled kernels then start streaming pages while
+ *                             that kernel (typically the previous layer's split-KV merge) is still running, and
+ *                             order themselves behind it only before their first write.  Results are identical;
+ *                             a call of about 10 us gets 2-3 us shorter in a chain of such calls.  Breaking the
+ *                             promise gives stale reads, not a fault.  Shapes outside the tiled kernels ignore it.
+ *                             No counterpart in the reference (one Triton launch per call, fully ordered).
+ */
+#define INT8KV_FLAG_QUANTIZE_Q 1
+#define INT8KV_FLAG_INPUTS_READY 2
 
 int int8kv_abi_version(void);
 const char* int8kv_status_str(int status);
@@ -84,8 +101,7 @@ int int8kv_cache_write(const void* key, const void* value, int in_dtype,
  *               int8kv_workspace_bytes_auto() bytes), -1 = always plan on the device, >= 1 = exactly that many
  *   max_seq_len_hint  upper bound of seq_lens used only to size the grid; <= 0 means width*BS
  *   workspace   required when the effective split count is > 1: int8kv_workspace_bytes() bytes
- *   quantize_q  non-zero: quantise each query head to INT8 (absmax/127, round half away from zero) before
- *               the dot product, as the reference's QUANTIZE_Q option (:137-146)
+ *   flags       INT8KV_FLAG_* bits (INT8KV_FLAG_QUANTIZE_Q = 1, so a plain 0/1 "quantize_q" still means the same)
  */
 int int8kv_paged_attn_int8(const void* query, int q_dtype, const int64_t q_strides[3],
                            int batch, int num_q_heads, int num_kv_heads, int head_dim,
@@ -97,11 +113,12 @@ int int8kv_paged_attn_int8(const void* query, int q_dtype, const int64_t q_strid
                            const float* k_scale, const float* v_scale,
                            void* out, int out_dtype, const int64_t out_strides[3],
                            int num_splits, void* workspace, int64_t workspace_bytes,
-                           int quantize_q, void* stream);
+                           int flags, void* stream);
 
 /*
  * BF16/FP16 paged decode attention, the same-run baseline.  Replaces bf16_paged_attention
  * (reference src/triton_ops/bf16_paged_attention.py:9-165).  `cache_dtype` is INT8KV_BF16 or INT8KV_FP16.
+ * flags: INT8KV_FLAG_INPUTS_READY only.
  */
 int int8kv_paged_attn_bf16(const void* query, int q_dtype, const int64_t q_strides[3],
                            int batch, int num_q_heads, int num_kv_heads, int head_dim,
@@ -112,7 +129,7 @@ int int8kv_paged_attn_bf16(const void* query, int q_dtype, const int64_t q_strid
                            const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                            void* out, int out_dtype, const int64_t out_strides[3],
                            int num_splits, void* workspace, int64_t workspace_bytes,
-                           void* stream);
+                           int flags, void* stream);
 
 /*
  * Variants that return unmerged partial attention for a sequence-parallel split: every rank attends to its own
@@ -131,7 +148,7 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
                            const float* k_scale, const float* v_scale,
                            float* partial,
                            int num_splits, void* workspace, int64_t workspace_bytes,
-                           int quantize_q, void* stream);
+                           int flags, void* stream);
 
 /*
  * Dynamic per-(token, head) INT8 cache write.  Replaces reshape_and_cache_int8 and its Triton kernel (reference
@@ -156,7 +173,7 @@ int int8kv_cache_write_dynamic(const void* key, const void* value, int in_dtype,
  * static scale per head.  out = softmax(q . (K8 * ks)^T / sqrt(D)) . (V8 * vs), the attention of the cache that
  * dequantize_int8_cache (vllm_int8/vllm_int8_cache_ops.py:250-277) reconstructs.  The reference stops at that
  * write/dequantise pair and has no attention kernel for this scheme; this entry point is the reader that pairs
- * with its writer.  Other arguments as int8kv_paged_attn_int8 (no quantize_q).
+ * with its writer.  Other arguments as int8kv_paged_attn_int8 (flags: INT8KV_FLAG_INPUTS_READY only).
  */
 int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t q_strides[3],
                                    int batch, int num_q_heads, int num_kv_heads, int head_dim,
@@ -168,7 +185,7 @@ int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t
                                    const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
                                    const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                                    void* out, int out_dtype, const int64_t out_strides[3],
-                                   int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+                                   int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
  * One decode step of one layer in a single call: the step's `batch` new K/V rows (one per sequence) are quantised
@@ -180,7 +197,8 @@ int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t
  * covers the write happens inside the attention kernel (no separate launch): the warp that owns a sequence's
  * last tile quantises the row, stores it to the cache and patches its staged copy.  A slot that is not the last
  * token's is still written, but attention may not see it and INT8KV_DEV_SLOT_MISMATCH is set in the status word.
- * Other shapes run int8kv_cache_write followed by int8kv_paged_attn_int8.
+ * Other shapes run int8kv_cache_write followed by int8kv_paged_attn_int8.  flags: INT8KV_FLAG_INPUTS_READY (the new
+ * rows and the slot mapping count as inputs of the call).
  */
 int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
                        const int64_t key_strides[3], const int64_t value_strides[3],
@@ -194,7 +212,7 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
                        const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                        const float* k_scale, const float* v_scale,
                        void* out, int out_dtype, const int64_t out_strides[3],
-                       int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+                       int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
  * The decode step of `num_layers` layers in one call: int8kv_decode_step once per entry of `layers`, in order, on
@@ -204,6 +222,10 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
  * layer's cache pair and scales, and the step's new K/V rows (key == NULL: attention only, nothing is written, and
  * slot_mapping may be NULL).  Stops at the first layer that fails and returns its status; *failed_layer (optional)
  * then holds its index, else -1.
+ * flags: with INT8KV_FLAG_INPUTS_READY the promise is about the layers of this call: no layer reads what an earlier
+ * layer of the call writes (all queries and new rows were produced before the call, every layer has its own cache
+ * and output).  Layers after the first then overlap the previous layer's merge; the first layer orders itself behind
+ * whatever precedes the call in the ordinary way.
  */
 typedef struct int8kv_layer_args {
   const void* query;      /* [batch, Hq, D] */
@@ -226,7 +248,7 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
                               const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
                               const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                               int out_dtype, const int64_t out_strides[3],
-                              int num_splits, void* workspace, int64_t workspace_bytes, void* stream);
+                              int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream);
 
 /*
  * INT8 paged decode attention for callers that must not allocate device memory.  No counterpart in the
@@ -239,14 +261,19 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
  * bytes of device memory, held by every GPU that loads the library until the process exits.
  *
  * Limits and rules:
- *   - the call is rejected with INT8KV_E_WORKSPACE, before anything is launched, when the split-KV rows of this
- *     shape (int8kv_workspace_bytes) do not fit in INT8KV_STATIC_WS_BYTES; pass a smaller num_splits (1 needs
- *     almost nothing) or use int8kv_paged_attn_int8 with a workspace of your own;
+ *   - num_splits means what it means for int8kv_paged_attn_int8 called with a workspace of INT8KV_STATIC_WS_BYTES
+ *     bytes: 0 picks the count from the shape (the rule of the tiled kernels or of the kernels for other shapes,
+ *     or parts planned on the device where those fit the buffer), -1 insists on the device plan, n >= 1 is taken
+ *     as given.  The call is rejected with INT8KV_E_WORKSPACE, before anything is launched, when the split-KV rows
+ *     of the chosen count (int8kv_workspace_bytes) do not fit in INT8KV_STATIC_WS_BYTES; pass a smaller num_splits
+ *     (1 needs almost nothing) or use int8kv_paged_attn_int8 with a workspace of your own;
  *   - the first call on each device looks up the device address of the buffer (with that device current);
  *     make that first call outside any stream capture;
  *   - all calls on a device share the one buffer, which keeps whatever the previous call left in it.  Nothing in
  *     it has to start at zero (every row is written before it is read), but two calls of one process whose
  *     kernels overlap on the GPU (different streams or host threads) race on it: serialise them;
+ *   - the device status word (INT8KV_DEV_* bits, set when a bounded wait ran out: the result is then invalid)
+ *     lives at the end of that buffer; int8kv_static_ws_status copies it out, again without allocating;
  *   - it never calls cudaMalloc, cudaFree or any allocating library routine.
  * Arguments and result are those of int8kv_paged_attn_int8 without the workspace pair.
  */
@@ -260,7 +287,23 @@ int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64
                            const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                            const float* k_scale, const float* v_scale,
                            void* out, int out_dtype, const int64_t out_strides[3],
-                           int num_splits, int quantize_q, void* stream);
+                           int num_splits, int flags, void* stream);
+
+/*
+ * Status word of the library's own workspace, for callers of int8kv_paged_attn_int8_static_ws (no counterpart in
+ * the reference, which has no failure detection).  Enqueues on `stream` an asynchronous 4-byte copy of the word to
+ * `dst` (device memory or pinned host memory of the caller; read it after synchronising the stream) and, with
+ * `clear` non-zero, a reset of the word to 0 behind it.  The bits are only ever OR-ed by the kernels, so without a
+ * clear they stay set across later calls.  Allocates nothing.
+ */
+int int8kv_static_ws_status(void* dst, int clear, void* stream);
+
+/*
+ * Device address of the library's own workspace (INT8KV_STATIC_WS_BYTES bytes) on the current device, for tools
+ * that want to hand it to an entry point taking a workspace, such as int8kv_selftest_bounded_wait.  The first call
+ * on a device looks the address up; make it outside any stream capture.
+ */
+int int8kv_static_ws_address(void** device_ptr);
 
 /*
  * Merge `num_parts` partial results.  Replaces _merge_split_kv_kernel (reference

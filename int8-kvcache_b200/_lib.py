@@ -16,7 +16,7 @@ _PKG_DIR = Path(__file__).resolve().parent
 _LIB = None
 _LOCK = threading.Lock()
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK = 0
 E_NULLPTR, E_BAD_SHAPE, E_BAD_DTYPE, E_UNSUPPORTED, E_LAUNCH, E_WORKSPACE = -1, -2, -3, -4, -5, -6
@@ -24,6 +24,7 @@ DEV_WAIT_TIMEOUT = 1
 DEV_SLOT_MISMATCH = 2
 STATIC_WS_BYTES = 8 * 1024 * 1024
 SPLITS_AUTO, SPLITS_PLANNED = 0, -1
+FLAG_QUANTIZE_Q, FLAG_INPUTS_READY = 1, 2
 PLAN_HEADER_TAG = 0x504C414E
 
 BF16, FP16, FP32 = 0, 1, 2
@@ -65,7 +66,7 @@ _SIGNATURES = {
         C.c_int,
         [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, C.c_int, _I64P, _I64P, C.c_int64, C.c_int,
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, C.c_int, _I64P,
-         C.c_int, _VP, C.c_int64, _VP],
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
     ),
     "int8kv_paged_attn_int8_partial": (
         C.c_int,
@@ -88,22 +89,24 @@ _SIGNATURES = {
         C.c_int,
         [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, _VP, _VP, _I64P, _I64P,
          C.c_int64, C.c_int, _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, C.c_int, _I64P,
-         C.c_int, _VP, C.c_int64, _VP],
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
     ),
     "int8kv_decode_step": (
         C.c_int,
         [_VP, _VP, C.c_int, _I64P, _I64P, _VP, C.c_int,
          _VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, _VP, C.c_int, _I64P,
-         C.c_int, _VP, C.c_int64, _VP],
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
     ),
     "int8kv_decode_step_layers": (
         C.c_int,
         [C.POINTER(LayerArgs), C.c_int, C.POINTER(C.c_int), C.c_int, _I64P, _I64P, _VP, C.c_int, C.c_int, _I64P,
          C.c_int, C.c_int, C.c_int, C.c_int, _I64P, _I64P, C.c_int64, C.c_int,
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, C.c_int, _I64P,
-         C.c_int, _VP, C.c_int64, _VP],
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
     ),
+    "int8kv_static_ws_status": (C.c_int, [_VP, C.c_int, _VP]),
+    "int8kv_static_ws_address": (C.c_int, [C.POINTER(_VP)]),
     "int8kv_selftest_bounded_wait": (C.c_int, [_VP, C.c_int64, C.c_int, _VP]),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),
 }
@@ -146,8 +149,19 @@ def status_str(code: int) -> str:
     return load().int8kv_status_str(int(code)).decode()
 
 
+_I64_CACHE: dict = {}
+
+
 def i64(values) -> "C.Array":
-    return (C.c_int64 * len(values))(*[int(v) for v in values])
+    """A ctypes int64 array of `values` (sizes or strides).  Arrays are immutable to the library and tensor
+    geometries repeat from call to call, so they are built once per distinct tuple."""
+    key = tuple(values)
+    arr = _I64_CACHE.get(key)
+    if arr is None:
+        if len(_I64_CACHE) > 4096:
+            _I64_CACHE.clear()
+        arr = _I64_CACHE[key] = (C.c_int64 * len(key))(*[int(v) for v in key])
+    return arr
 
 
 class Int8KVError(RuntimeError):

@@ -213,7 +213,7 @@ struct AttnCall {
   void* out; int out_dtype; const int64_t* o_st;
   float* partial_out;  // non-null: emit merged partial rows instead of `out`
   int num_splits; void* ws; int64_t ws_bytes;
-  int quantize_q; cudaStream_t stream;
+  int flags; cudaStream_t stream;  // INT8KV_FLAG_* bits
   // fused decode step (null new_k = plain attention)
   const void* new_k = nullptr; const void* new_v = nullptr; int new_dtype = 0;
   const int64_t* nk_st = nullptr; const int64_t* nv_st = nullptr;
@@ -228,6 +228,9 @@ int run_attention(const AttnCall& a) {
     return INT8KV_E_BAD_SHAPE;
   if (a.Hq % a.Hkv != 0) return INT8KV_E_BAD_SHAPE;
   if (a.num_splits < INT8KV_SPLITS_PLANNED || a.num_splits > kMaxSplits) return INT8KV_E_BAD_SHAPE;
+  if (a.flags & ~(INT8KV_FLAG_QUANTIZE_Q | INT8KV_FLAG_INPUTS_READY)) return INT8KV_E_BAD_SHAPE;
+  const int quantize_q = (a.flags & INT8KV_FLAG_QUANTIZE_Q) ? 1 : 0;
+  if (quantize_q && (a.cache_kind != kCacheInt8 || a.ks_cache != nullptr || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
   if (!valid_float_dtype(a.q_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.partial_out == nullptr && !valid_float_dtype(a.out_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.B == 0) return INT8KV_OK;
@@ -307,7 +310,8 @@ int run_attention(const AttnCall& a) {
   p.num_splits = S;
   p.per_longest = static_cast<int>(std::max<int64_t>(1, (tiles + S - 1) / S));
   p.row_floats = rf;
-  p.quantize_q = a.quantize_q;
+  p.quantize_q = quantize_q;
+  p.defer_wait = (a.flags & INT8KV_FLAG_INPUTS_READY) ? 1 : 0;
   p.sm_scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(a.D)));
   p.status = status;
   if (S > 1) p.part = reinterpret_cast<float*>(a.ws);
@@ -342,7 +346,6 @@ int run_attention(const AttnCall& a) {
     rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, sm, a.stream)
                                     : launch_attn_tiled_f16(p, tmK, tmV, sm, a.stream);
   } else {
-    if (a.cache_kind != kCacheInt8 && a.quantize_q) return INT8KV_E_UNSUPPORTED;
     rc = launch_attn_generic(p, a.stream);
   }
   if (rc != INT8KV_OK || S == 1) return rc;
@@ -353,6 +356,7 @@ int run_attention(const AttnCall& a) {
   m.out = a.out; m.out_dtype = a.out_dtype;
   if (a.o_st) for (int i = 0; i < 3; ++i) m.o_st[i] = a.o_st[i];
   m.part_out = a.partial_out;
+  m.inputs_ready = p.defer_wait;
   if (planned) m.seq_table = reinterpret_cast<const int2*>(static_cast<char*>(a.ws) + pl.table_off);
   return launch_merge(m, a.stream);
 }
@@ -447,12 +451,12 @@ int int8kv_paged_attn_int8(const void* query, int q_dtype, const int64_t q_strid
                            const int64_t bt_strides[2], int64_t bt_width, const void* seq_lens, int sl_is_i64,
                            int64_t max_seq_len_hint, const float* k_scale, const float* v_scale, void* out,
                            int out_dtype, const int64_t out_strides[3], int num_splits, void* workspace,
-                           int64_t workspace_bytes, int quantize_q, void* stream) {
+                           int64_t workspace_bytes, int flags, void* stream) {
   AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              k_scale, v_scale, out, out_dtype, out_strides, nullptr,
-             num_splits, workspace, workspace_bytes, quantize_q, static_cast<cudaStream_t>(stream)};
+             num_splits, workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream)};
   return run_attention(a);
 }
 
@@ -463,14 +467,14 @@ int int8kv_paged_attn_bf16(const void* query, int q_dtype, const int64_t q_strid
                            const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
                            const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint, void* out, int out_dtype,
                            const int64_t out_strides[3], int num_splits, void* workspace, int64_t workspace_bytes,
-                           void* stream) {
+                           int flags, void* stream) {
   if (cache_dtype != INT8KV_BF16 && cache_dtype != INT8KV_FP16) return INT8KV_E_BAD_DTYPE;
   AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
              key_cache, value_cache, cache_dtype == INT8KV_BF16 ? kCacheBf16 : kCacheFp16,
              key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              nullptr, nullptr, out, out_dtype, out_strides, nullptr,
-             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+             num_splits, workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream)};
   return run_attention(a);
 }
 
@@ -481,14 +485,14 @@ int int8kv_paged_attn_int8_partial(const void* query, int q_dtype, const int64_t
                                    const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
                                    int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                                    const float* k_scale, const float* v_scale, float* partial, int num_splits,
-                                   void* workspace, int64_t workspace_bytes, int quantize_q, void* stream) {
+                                   void* workspace, int64_t workspace_bytes, int flags, void* stream) {
   if (partial == nullptr) return INT8KV_E_NULLPTR;
   if (reinterpret_cast<uintptr_t>(partial) & 15u) return INT8KV_E_BAD_SHAPE;
   AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              k_scale, v_scale, nullptr, INT8KV_FP32, nullptr, partial,
-             num_splits, workspace, workspace_bytes, quantize_q, static_cast<cudaStream_t>(stream)};
+             num_splits, workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream)};
   return run_attention(a);
 }
 
@@ -501,13 +505,13 @@ int int8kv_paged_attn_int8_dynamic(const void* query, int q_dtype, const int64_t
                                    const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
                                    int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                                    void* out, int out_dtype, const int64_t out_strides[3], int num_splits,
-                                   void* workspace, int64_t workspace_bytes, void* stream) {
+                                   void* workspace, int64_t workspace_bytes, int flags, void* stream) {
   if (batch > 0 && (!k_scale_cache || !v_scale_cache || !k_scale_strides || !v_scale_strides)) return INT8KV_E_NULLPTR;
   AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              nullptr, nullptr, out, out_dtype, out_strides, nullptr,
-             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+             num_splits, workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream)};
   a.ks_cache = k_scale_cache; a.vs_cache = v_scale_cache; a.ks_st = k_scale_strides; a.vs_st = v_scale_strides;
   return run_attention(a);
 }
@@ -577,7 +581,7 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
                        int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
                        const float* k_scale, const float* v_scale, void* out, int out_dtype,
                        const int64_t out_strides[3], int num_splits, void* workspace, int64_t workspace_bytes,
-                       void* stream) {
+                       int flags, void* stream) {
   if (!key || !value || !slot_mapping || !key_strides || !value_strides) return batch == 0 ? INT8KV_OK : INT8KV_E_NULLPTR;
   if (!valid_float_dtype(kv_dtype)) return INT8KV_E_BAD_DTYPE;
   // Shapes the tiled kernel covers: one launch does both.  For any other shape run_attention refuses with
@@ -586,7 +590,7 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              k_scale, v_scale, out, out_dtype, out_strides, nullptr,
-             num_splits, workspace, workspace_bytes, 0, static_cast<cudaStream_t>(stream)};
+             num_splits, workspace, workspace_bytes, flags, static_cast<cudaStream_t>(stream)};
   a.new_k = key; a.new_v = value; a.new_dtype = kv_dtype; a.nk_st = key_strides; a.nv_st = value_strides;
   a.new_slots = slot_mapping; a.new_slot_is_i64 = slot_is_i64;
   int rc = run_attention(a);
@@ -599,7 +603,7 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
                                 value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
                                 block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
                                 max_seq_len_hint, k_scale, v_scale, out, out_dtype, out_strides, num_splits,
-                                workspace, workspace_bytes, 0, stream);
+                                workspace, workspace_bytes, flags & ~INT8KV_FLAG_INPUTS_READY, stream);
 }
 
 int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer, int kv_dtype,
@@ -610,13 +614,16 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
                               int64_t num_blocks, int block_size, const void* block_tables, int bt_is_i64,
                               const int64_t bt_strides[2], int64_t bt_width, const void* seq_lens, int sl_is_i64,
                               int64_t max_seq_len_hint, int out_dtype, const int64_t out_strides[3],
-                              int num_splits, void* workspace, int64_t workspace_bytes, void* stream) {
+                              int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream) {
   if (failed_layer) *failed_layer = -1;
   if (num_layers < 0) return INT8KV_E_BAD_SHAPE;
   if (num_layers == 0) return INT8KV_OK;
   if (!layers) return INT8KV_E_NULLPTR;
   for (int l = 0; l < num_layers; ++l) {
     const int8kv_layer_args& L = layers[l];
+    // the promise is about the layers of this call; what precedes the call on the stream is unknown here, so the
+    // first layer orders itself behind it in the ordinary way
+    const int lf = l == 0 ? (flags & ~INT8KV_FLAG_INPUTS_READY) : flags;
     int rc;
     if (L.key != nullptr) {
       rc = int8kv_decode_step(L.key, L.value, kv_dtype, key_strides, value_strides, slot_mapping, slot_is_i64,
@@ -624,13 +631,13 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
                               L.value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
                               block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
                               L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits, workspace,
-                              workspace_bytes, stream);
+                              workspace_bytes, lf, stream);
     } else {
       rc = int8kv_paged_attn_int8(L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
                                   L.key_cache, L.value_cache, key_cache_strides, value_cache_strides, num_blocks,
                                   block_size, block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
                                   max_seq_len_hint, L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits,
-                                  workspace, workspace_bytes, 0, stream);
+                                  workspace, workspace_bytes, lf, stream);
     }
     if (rc != INT8KV_OK) {
       if (failed_layer) *failed_layer = l;
@@ -679,18 +686,13 @@ int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64
                                      int64_t bt_width, const void* seq_lens, int sl_is_i64,
                                      int64_t max_seq_len_hint, const float* k_scale, const float* v_scale,
                                      void* out, int out_dtype, const int64_t out_strides[3], int num_splits,
-                                     int quantize_q, void* stream) {
+                                     int flags, void* stream) {
+  // The same selection and the same checks as int8kv_paged_attn_int8 given a workspace of INT8KV_STATIC_WS_BYTES
+  // bytes: run_attention picks the split count (the tiled or the untiled rule, or the device plan when its rows
+  // and table fit) and refuses with INT8KV_E_WORKSPACE, before it launches anything, what does not fit.
   if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || block_size <= 0 || bt_width < 0 ||
-      num_splits < 0 || num_splits > kMaxSplits)
+      num_splits < INT8KV_SPLITS_PLANNED || num_splits > kMaxSplits)
     return INT8KV_E_BAD_SHAPE;
-  // Size check first, with the same split count the launch would use, so that an oversized request is refused
-  // before any CUDA call is made.
-  int64_t max_seq = max_seq_len_hint > 0 ? max_seq_len_hint : bt_width * block_size;
-  if (max_seq > bt_width * block_size) max_seq = bt_width * block_size;
-  int splits = num_splits > 0 ? num_splits : choose_splits(batch, num_kv_heads, max_seq, block_size, device_sm_count());
-  const int64_t tiles = (max_seq + 15) / 16;
-  if (splits > tiles) splits = tiles > 0 ? static_cast<int>(tiles) : 1;
-  if (ws_bytes(batch, num_q_heads, head_dim, splits) > INT8KV_STATIC_WS_BYTES) return INT8KV_E_WORKSPACE;
   void* ws = nullptr;
   const int rc = static_ws_address(&ws);
   if (rc != INT8KV_OK) return rc;
@@ -698,8 +700,25 @@ int int8kv_paged_attn_int8_static_ws(const void* query, int q_dtype, const int64
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
              k_scale, v_scale, out, out_dtype, out_strides, nullptr,
-             splits, ws, INT8KV_STATIC_WS_BYTES, quantize_q, static_cast<cudaStream_t>(stream)};
+             num_splits, ws, INT8KV_STATIC_WS_BYTES, flags, static_cast<cudaStream_t>(stream)};
   return run_attention(a);
+}
+
+int int8kv_static_ws_address(void** device_ptr) {
+  if (device_ptr == nullptr) return INT8KV_E_NULLPTR;
+  return static_ws_address(device_ptr);
+}
+
+int int8kv_static_ws_status(void* dst, int clear, void* stream) {
+  if (dst == nullptr) return INT8KV_E_NULLPTR;
+  void* ws = nullptr;
+  const int rc = static_ws_address(&ws);
+  if (rc != INT8KV_OK) return rc;
+  char* word = static_cast<char*>(ws) + int8kv_workspace_status_offset(INT8KV_STATIC_WS_BYTES);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(dst, word, 4, cudaMemcpyDefault, st) != cudaSuccess) return INT8KV_E_LAUNCH;
+  if (clear && cudaMemsetAsync(word, 0, 4, st) != cudaSuccess) return INT8KV_E_LAUNCH;
+  return INT8KV_OK;
 }
 
 }  // extern "C"

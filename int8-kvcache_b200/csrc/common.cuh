@@ -182,6 +182,24 @@ __device__ __forceinline__ int quant1(float x, float scale, float rscale) {
   return __float_as_int(t) - kRoundMagicBits;
 }
 
+// One element of the dynamic scheme and of the optional INT8 query: clamp(x / scale, +-127) rounded half away from zero, bit-identical to the
+// fp32 sequence divide, clamp, floor(q + 0.5) / ceil(q - 0.5).  Away from a tie, rounding half away equals rounding
+// to nearest, which the 1.5 * 2^23 addition does on a quotient formed with the reciprocal; within 1e-3 of a
+// half-integer (where the few ulp between that quotient and the IEEE one could decide, and where the two rounding
+// rules differ) the division and the reference sequence itself run.  The integer is returned unclamped; packing
+// saturates it, which equals clamping the quotient first.
+__device__ __forceinline__ int quant_half_away(float x, float scale, float rscale) {
+  float q = x * rscale;
+  const float t = q + kRoundMagic;
+  const float n = t - kRoundMagic;
+  if (!(fabsf(q - n) < 0.5f - 1e-3f) || !(fabsf(q) < 4.0e6f)) {
+    q = fminf(fmaxf(__fdiv_rn(x, scale), -127.f), 127.f);
+    const float r = q >= 0.f ? floorf(q + 0.5f) : ceilf(q - 0.5f);
+    return x != x ? 0 : static_cast<int>(r);
+  }
+  return __float_as_int(t) - kRoundMagicBits;
+}
+
 // Four such integers saturated to int8 and packed little-endian; -128 is raised to -127.
 __device__ __forceinline__ uint32_t pack4_sat(int n0, int n1, int n2, int n3) {
   uint32_t hi, w;

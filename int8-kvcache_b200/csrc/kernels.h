@@ -79,6 +79,10 @@ struct AttnParams {
   int quantize_q;
   float sm_scale_log2;   // log2(e) / sqrt(D)
   unsigned int* status;  // device status word, may be null
+  // Caller's promise that nothing this call reads is written by the kernel that precedes it on the stream: the
+  // tiled kernels then start reading at once and resolve the grid dependency only before their first global write
+  // (the split-KV workspace may still be in use by the preceding call's merge until then).
+  int defer_wait;
   // fused decode step: the step's new K/V row of every sequence ([B, Hkv, D]) is quantised and written at
   // new_slots[b] by the warp that owns the sequence's last tile, which also patches its staged copy of the tile
   const void* new_k;  // null = plain attention
@@ -115,6 +119,7 @@ struct MergeParams {
   float* part_out;  // [rows, row_floats] merged partial rows (out | lse), or null
   const int2* seq_table;  // device-planned splits: parts of row (b, hq) are rows (row0 + c) * Hq + hq, c < used
   int early_trigger;  // call griddepcontrol.launch_dependents right after the dependency wait
+  int inputs_ready;   // the call that produced the parts carried the inputs-ready promise: always trigger early
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);

@@ -236,7 +236,28 @@ constexpr int kPlanRun = 16;  // sequences per lane: a plan covers up to 32 * 16
 constexpr int kPlanShortestPart = 8;
 constexpr int kPlanHeaderTag = 0x504c414e;  // marks the 16 bytes before the status word as a plan header
 
-__device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, int lane, ItemCoord& it, int64_t& row0) {
+// What a planning warp has to leave in the workspace: the plan header (item 0) and its sequence's {first part, parts}
+// entry (the warp of part 0, head 0).  The stores are made by plan_commit, which the kernels call once the grid
+// dependency is resolved: with a deferred wait the preceding call's merge may still be reading the same bytes.
+struct PlanNote {
+  int count, part_tiles, waves;  // header, written when count >= 0
+  int table_b;                   // sequence whose table entry this warp writes, or -1
+  int2 table_entry;
+};
+
+__device__ __forceinline__ void plan_commit(const AttnParams& p, const PlanNote& note, int lane) {
+  if (lane != 0) return;
+  if (note.count >= 0 && p.plan_header != nullptr) {
+    p.plan_header[0] = note.count;
+    p.plan_header[1] = note.part_tiles;
+    p.plan_header[2] = note.waves;
+    p.plan_header[3] = kPlanHeaderTag;
+  }
+  if (note.table_b >= 0) p.plan_table[note.table_b] = note.table_entry;
+}
+
+__device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, int lane, ItemCoord& it, int64_t& row0,
+                                             PlanNote& note) {
   // lane l holds the lengths of sequences [l * run, (l + 1) * run) in registers; every pass below works on them
   const int cap = static_cast<int>(p.bt_width * p.block_size);
   const int run = (p.B + kWarp - 1) / kWarp;
@@ -296,12 +317,10 @@ __device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, 
   }
   const int all_parts = __shfl_sync(kFull, upto, kWarp - 1);
   const long long count = static_cast<long long>(all_parts) * p.Hkv;
-  if (item == 0 && lane == 0 && p.plan_header != nullptr) {
-    p.plan_header[0] = static_cast<int>(count);
-    p.plan_header[1] = P;
-    p.plan_header[2] = k;
-    p.plan_header[3] = kPlanHeaderTag;
-  }
+  note.count = item == 0 ? static_cast<int>(count) : -1;
+  note.part_tiles = P;
+  note.waves = k;
+  note.table_b = -1;
   if (item >= count) return false;
 
   // the item in the order (sequence, part, kv head): its part index falls into exactly one lane's run
@@ -331,7 +350,10 @@ __device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, 
   it.t0 = min(it.c * per, tiles);
   it.t1 = min(it.t0 + per, tiles);
   row0 = used == 1 ? -1 : static_cast<int64_t>(part) * p.Hq + it.h * p.G;
-  if (it.c == 0 && it.h == 0 && lane == 0) p.plan_table[it.b] = make_int2(part, used);
+  if (it.c == 0 && it.h == 0) {
+    note.table_b = it.b;
+    note.table_entry = make_int2(part, used);
+  }
   return true;
 }
 
@@ -494,17 +516,38 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   }
   ring.init_barriers(lane);
   // Everything above used kernel parameters and shared memory only.  From here on global memory is read, which
-  // the kernel launched just before this one may have written.
-  grid_dependency_wait();
+  // the kernel launched just before this one may have written, unless the caller promised otherwise (defer_wait):
+  // then the dependency is resolved only before this warp's first global write, see resolve_dependency below.
+  const bool defer_wait = p.defer_wait != 0;
+  if (!defer_wait) grid_dependency_wait();
   // Only now may the next kernel in the stream be scheduled (it waits for this grid before it reads): triggering
-  // before the wait would let a whole chain of future kernels pile up on the SMs.
+  // before the wait would let a whole chain of future kernels pile up on the SMs.  (With a deferred wait the
+  // chain still ends at the merge kernel that follows, which triggers only after its own wait.)
   grid_launch_dependents();
   int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
+  PlanNote note;
+  note.count = -1;
+  note.table_b = -1;
+  // Every path that writes global memory (results, partial rows, the plan's notes) goes through here first.
+  auto resolve_dependency = [&]() {
+    if (defer_wait) grid_dependency_wait();
+    if constexpr (planned) plan_commit(p, note, lane);
+  };
   if constexpr (planned) {
-    if (!plan_in_warp(p, item, lane, it, row0)) return;
+    if (!plan_in_warp(p, item, lane, it, row0, note)) {
+      resolve_dependency();
+      return;
+    }
   }
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.head = it.h;
+  // the head's scales are requested with the first loads of the warp; their first use is after the query's
+  // conversion (k) and in the epilogue (v)
+  float k_scale_head = 1.f, v_scale_head = 1.f;
+  if constexpr (!DYN) {
+    k_scale_head = __ldg(p.k_scale + it.h);
+    v_scale_head = __ldg(p.v_scale + it.h);
+  }
   if constexpr (DYN) ring.sc_src = lane >= 16 ? p.vs_cache + it.h * p.vs_st[2] : p.ks_cache + it.h * p.ks_st[2];
   if constexpr (planned) {
     ring.prefetch_tables(it.t0 / p.tiles_per_block);
@@ -515,6 +558,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   }
   float* const prow = result_row(p, it, row0);
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
+    resolve_dependency();
     write_empty(p, it, lane, prow);
     return;
   }
@@ -569,13 +613,12 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
     int qi[32];
     if constexpr (QQ) {
+      // clamp(round_half_away(q / qs), +-127), bit-identical to the division sequence of the reference's kernel
+      // (:137-146) but formed with the reciprocal away from rounding boundaries (quant_half_away)
       const float qs = fmaxf(amax / 127.f, 1e-6f);
+      const float rq = __frcp_rn(qs);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float x = qv[i] / qs;
-        const float r = x >= 0.f ? floorf(x + 0.5f) : -floorf(-x + 0.5f);  // half away from zero
-        qi[i] = static_cast<int>(fminf(fmaxf(r, -127.f), 127.f));
-      }
+      for (int i = 0; i < 32; ++i) qi[i] = max(-127, min(127, quant_half_away(qv[i], qs, rq)));
       q_mul = qs;
     } else {
       const float inv = amax > 0.f ? 32000.f / amax : 0.f;
@@ -596,10 +639,11 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     }
   }
   // score multipliers for the two head columns (2t, 2t+1) this lane sees in the C fragment
-  const float k_scale_head = DYN ? 1.f : fmaxf(__ldg(p.k_scale + it.h), 1e-6f);
+  if constexpr (!DYN) {
+    k_scale_head = fmaxf(k_scale_head, 1e-6f);
+    v_scale_head = fmaxf(v_scale_head, 1e-6f);
+  }
   const float kmul = k_scale_head * p.sm_scale_log2;
-  // requested here, used in the epilogue: a load issued there would put its whole latency on the critical path
-  const float v_scale_head = DYN ? 1.f : fmaxf(__ldg(p.v_scale + it.h), 1e-6f);
   const float sc0 = kmul * __shfl_sync(kFull, q_mul, (2 * t) * 4);
   const float sc1 = kmul * __shfl_sync(kFull, q_mul, (2 * t + 1) * 4);
 
@@ -633,6 +677,8 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     const uint32_t sA = ring.stage(i), sB = ring.stage(i + 1);
 
     if constexpr (FUSED_WRITE) {
+      // (The row's store to the cache does not need the grid dependency resolved: under the inputs-ready promise
+      // nothing that precedes this call on the stream still touches this layer's cache.)
       if (owns_new && (last_rel == i || last_rel == i + 1)) {
         fused_row_write(p.kc, p.vc, p.kc_st[0], p.kc_st[1], it.h * p.kc_st[2], p.vc_st[0], p.vc_st[1], it.h * p.vc_st[2],
                         p.num_blocks, p.block_size, it.seq_len - 1, new_slot, last_blk, nk[0], nk[1], nk[2], nk[3],
@@ -750,6 +796,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   }
 
   // ---- epilogue: reduce the row sums over the token lanes, normalise, apply v_scale ----------------------
+  resolve_dependency();
   l0 += __shfl_xor_sync(kFull, l0, 4);
   l1 += __shfl_xor_sync(kFull, l1, 4);
   l0 += __shfl_xor_sync(kFull, l0, 8);
@@ -831,14 +878,28 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   }
   ring.init_barriers(lane);
   // Everything above used kernel parameters and shared memory only.  From here on global memory is read, which
-  // the kernel launched just before this one may have written.
-  grid_dependency_wait();
+  // the kernel launched just before this one may have written, unless the caller promised otherwise (defer_wait):
+  // then the dependency is resolved only before this warp's first global write, see resolve_dependency below.
+  const bool defer_wait = p.defer_wait != 0;
+  if (!defer_wait) grid_dependency_wait();
   // Only now may the next kernel in the stream be scheduled (it waits for this grid before it reads): triggering
-  // before the wait would let a whole chain of future kernels pile up on the SMs.
+  // before the wait would let a whole chain of future kernels pile up on the SMs.  (With a deferred wait the
+  // chain still ends at the merge kernel that follows, which triggers only after its own wait.)
   grid_launch_dependents();
   int64_t row0;  // first partial row of this item's query-head group, -1 = write `out`
+  PlanNote note;
+  note.count = -1;
+  note.table_b = -1;
+  // Every path that writes global memory (results, partial rows, the plan's notes) goes through here first.
+  auto resolve_dependency = [&]() {
+    if (defer_wait) grid_dependency_wait();
+    if constexpr (planned) plan_commit(p, note, lane);
+  };
   if constexpr (planned) {
-    if (!plan_in_warp(p, item, lane, it, row0)) return;
+    if (!plan_in_warp(p, item, lane, it, row0, note)) {
+      resolve_dependency();
+      return;
+    }
   }
   ring.bt_row = reinterpret_cast<const char*>(p.bt) + it.b * p.bt_st[0] * (p.bt_is_i64 ? 8 : 4);
   ring.head = it.h;
@@ -851,6 +912,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   }
   float* const prow = result_row(p, it, row0);
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
+    resolve_dependency();
     write_empty(p, it, lane, prow);
     return;
   }
@@ -982,6 +1044,7 @@ paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     return;
   }
 
+  resolve_dependency();
   l0 += __shfl_xor_sync(kFull, l0, 4);
   l1 += __shfl_xor_sync(kFull, l1, 4);
   l0 += __shfl_xor_sync(kFull, l0, 8);
@@ -1841,7 +1904,7 @@ int launch_merge(const MergeParams& p_in, cudaStream_t stream) {
   MergeParams p = p_in;
   // A short merge lets the next kernel in the stream be scheduled while it runs (measured: 0.4-0.8 us per call on
   // small decode calls); a long one would only have that kernel's CTAs crowd the SMs it still needs.
-  p.early_trigger = p.rows * p.R <= 4096;
+  p.early_trigger = p.inputs_ready || p.rows * p.R <= 4096;
   if (p.rows <= 0) return INT8KV_OK;
   return launch_pdl(merge_partials_kernel, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p);
 }

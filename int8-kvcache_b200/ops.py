@@ -26,6 +26,11 @@ _FLOAT_CODES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.FP16, torch.float
 # partial_out/partial_m/partial_l tensors that the reference allocates per call (:595-597)
 # ---------------------------------------------------------------------------------------------------
 _WS: Dict[Tuple[int, int], torch.Tensor] = {}
+# Buffers that a larger one has replaced.  They are kept alive: a CUDA graph captured while one of them was current
+# still holds its address, and handing that memory back to the allocator would let someone else's tensor land under
+# the graph's partial rows.  Growth is geometric, so all retired buffers of a stream together are smaller than its
+# current one.
+_WS_RETIRED: Dict[Tuple[int, int], list] = {}
 _WS_LOCK = threading.Lock()
 
 
@@ -35,16 +40,26 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     with _WS_LOCK:
         buf = _WS.get(key)
         if buf is None or buf.numel() < nbytes:
-            grow = max(nbytes, 1 << 20)
+            if torch.cuda.is_current_stream_capturing():
+                # an allocation made now would come from the capturing graph's private pool and be handed out again
+                # by later captures while this module still used it
+                raise RuntimeError(
+                    f"the split-KV workspace of this stream must grow to {nbytes} bytes during a CUDA-graph capture; "
+                    "run the call once eagerly on this stream before capturing it")
+            grow = max(nbytes, 1 << 20, 2 * buf.numel() if buf is not None else 0)
+            if buf is not None:
+                _WS_RETIRED.setdefault(key, []).append(buf)
             buf = torch.zeros(grow, dtype=torch.uint8, device=device)
             _WS[key] = buf
         return buf
 
 
 def release_workspaces() -> None:
-    """Drop every cached split-KV workspace."""
+    """Drop every cached split-KV workspace, current and retired.  Only when no CUDA graph that was captured over
+    calls of this module is going to be replayed any more: such a graph keeps using the addresses."""
     with _WS_LOCK:
         _WS.clear()
+        _WS_RETIRED.clear()
 
 
 def device_status(device=None) -> int:
@@ -88,6 +103,10 @@ def _as_f32_scale(scale: torch.Tensor) -> torch.Tensor:
 
 def _require_lib():
     return _lib.load()
+
+
+def _flags(quantize_q: bool = False, inputs_ready: bool = False) -> int:
+    return (_lib.FLAG_QUANTIZE_Q if quantize_q else 0) | (_lib.FLAG_INPUTS_READY if inputs_ready else 0)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -280,13 +299,16 @@ def int8_paged_attention(
     num_splits: Optional[int] = None,
     max_seq_len: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    inputs_ready: bool = False,
 ) -> torch.Tensor:
     """Decode attention of query [B, Hq, D] over an INT8 paged cache; returns [B, Hq, D] in query.dtype.
 
     impl: "auto", "v3" or "v4" are accepted (the reference's two kernel generations); one kernel
     family serves all of them here.  num_splits: None picks the KV split count from the shape, an int
-    is honoured.  max_seq_len / out are extensions: an upper bound of seq_lens that avoids the host
-    synchronisation, and a preallocated output.
+    is honoured.  max_seq_len / out / inputs_ready are extensions: an upper bound of seq_lens that avoids
+    the host synchronisation, a preallocated output, and the caller's promise that nothing the call reads
+    is written by the kernel that precedes it on the stream (INT8KV_FLAG_INPUTS_READY: the call then
+    overlaps that kernel's tail; same results).
     """
     B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
     assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
@@ -320,7 +342,7 @@ def int8_paged_attention(
         k_scale.data_ptr(), v_scale.data_ptr(),
         out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
         splits, ws.data_ptr(), ws.numel(),
-        int(bool(quantize_q)), _stream_ptr(query.device),
+        _flags(quantize_q, inputs_ready), _stream_ptr(query.device),
     )
     _lib.check("int8kv_paged_attn_int8", rc)
     return out
@@ -338,6 +360,7 @@ def int8_paged_attention_dynamic(
     num_splits: Optional[int] = None,
     max_seq_len: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    inputs_ready: bool = False,
 ) -> torch.Tensor:
     """Decode attention over an INT8 paged cache whose scales are per (block, slot, head) — the caches that
     reshape_and_cache_int8 fills (k_scale_cache / v_scale_cache [num_blocks, BS, Hkv] fp32).  Returns [B, Hq, D] in
@@ -371,7 +394,7 @@ def int8_paged_attention_dynamic(
         seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
         out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
         splits, ws.data_ptr(), ws.numel(),
-        _stream_ptr(query.device),
+        _flags(False, inputs_ready), _stream_ptr(query.device),
     )
     _lib.check("int8kv_paged_attn_int8_dynamic", rc)
     return out
@@ -387,6 +410,7 @@ def bf16_paged_attention(
     num_splits: Optional[int] = None,
     max_seq_len: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    inputs_ready: bool = False,
 ) -> torch.Tensor:
     """Decode attention over a bf16 (or fp16) paged cache: the same-run baseline for the INT8 path.
 
@@ -419,7 +443,7 @@ def bf16_paged_attention(
         seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
         out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
         splits, ws.data_ptr(), ws.numel(),
-        _stream_ptr(query.device),
+        _flags(False, inputs_ready), _stream_ptr(query.device),
     )
     _lib.check("int8kv_paged_attn_bf16", rc)
     return out
@@ -440,6 +464,7 @@ def int8_decode_step(
     max_seq_len: int,
     num_splits: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    inputs_ready: bool = False,
 ) -> torch.Tensor:
     """One layer's decode step in one library call: write the step's new K/V rows [B, Hkv, D] at slot_mapping,
     then attend with query [B, Hq, D] over the updated cache (seq_lens already count the new tokens).  Equivalent
@@ -480,7 +505,7 @@ def int8_decode_step(
         k_scale.data_ptr(), v_scale.data_ptr(),
         out.data_ptr(), _FLOAT_CODES[out.dtype], _lib.i64(out.stride()),
         splits, ws.data_ptr(), ws.numel(),
-        _stream_ptr(query.device),
+        _flags(False, inputs_ready), _stream_ptr(query.device),
     )
     _lib.check("int8kv_decode_step", rc)
     return out
@@ -493,11 +518,12 @@ class DecodeStepLayers:
     under CUDA-graph replay), so everything the binding needs — L pointer records, strides, table geometry, the
     workspace — is fixed when this object is built; calling it costs one ctypes crossing and no per-layer Python.
     Arguments as int8_decode_step_layers.  The tensors are kept alive by the object; their contents may change
-    between calls, their addresses may not."""
+    between calls, their addresses may not.  inputs_ready: no layer reads what an earlier layer of the call writes
+    (INT8KV_FLAG_INPUTS_READY), so every layer after the first overlaps the previous layer's merge."""
 
     def __init__(self, queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens,
                  k_scales, v_scales, *, max_seq_len: int, num_splits: Optional[int] = None,
-                 out: Optional[torch.Tensor] = None):
+                 out: Optional[torch.Tensor] = None, inputs_ready: bool = False):
         L = len(key_caches)
         assert len(value_caches) == L and len(queries) == L and len(k_scales) == L and len(v_scales) == L
         assert (keys is None) == (values is None)
@@ -574,7 +600,7 @@ class DecodeStepLayers:
             _lib.i64(block_tables.stride()), block_tables.shape[1],
             seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), int(max_seq_len),
             _FLOAT_CODES[out.dtype], _lib.i64(out[0].stride()),
-            splits, ws.data_ptr(), ws.numel(),
+            splits, ws.data_ptr(), ws.numel(), _flags(False, inputs_ready),
         )
 
     def __call__(self) -> torch.Tensor:
@@ -605,6 +631,7 @@ def int8_decode_step_layers(
     max_seq_len: int,
     num_splits: Optional[int] = None,
     out: Optional[torch.Tensor] = None,
+    inputs_ready: bool = False,
 ) -> torch.Tensor:
     """The decode step of L layers in one library call (one binding crossing per model step instead of one per
     layer).  queries / keys / values: [L, B, ...] tensors or sequences of L same-shaped, same-strided tensors
@@ -613,7 +640,8 @@ def int8_decode_step_layers(
     exactly what int8_decode_step (or int8_paged_attention) computes for its arguments.  A loop that reuses its
     buffers should build a DecodeStepLayers once and call that instead."""
     return DecodeStepLayers(queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens,
-                            k_scales, v_scales, max_seq_len=max_seq_len, num_splits=num_splits, out=out)()
+                            k_scales, v_scales, max_seq_len=max_seq_len, num_splits=num_splits, out=out,
+                            inputs_ready=inputs_ready)()
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -658,7 +686,7 @@ def int8_paged_attention_partial(
         k_scale.data_ptr(), v_scale.data_ptr(),
         out.data_ptr(),
         splits, ws.data_ptr(), ws.numel(),
-        int(bool(quantize_q)), _stream_ptr(query.device),
+        _flags(quantize_q), _stream_ptr(query.device),
     )
     _lib.check("int8kv_paged_attn_int8_partial", rc)
     return out

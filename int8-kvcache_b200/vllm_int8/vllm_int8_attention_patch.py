@@ -4,7 +4,9 @@ attention implementation's `forward` in the reference's three modes:
 
   shadow     run the original, run INT8 beside it, record cosine / relative L2 / MAE, return the original
   takeover   same comparison, but the INT8 result overwrites the output
-  int8_only  INT8 alone (no comparison, no extra synchronisation), counted in ATTN_INT8_HITS
+  int8_only  INT8 alone (no comparison, no host synchronisation: the reference's operator reads seq_lens back on
+             the host twice per call, src/triton_ops/int8_paged_attention.py:720-721, this call site passes an upper
+             bound instead, so a decode step can be captured in a CUDA graph), counted in ATTN_INT8_HITS
 
 Anything that is not a decode step, or a layer without an INT8 cache, goes to the original forward.
 """
@@ -48,19 +50,32 @@ def _is_supported_decode(query, attn_metadata) -> bool:
     return max_query_len is None or int(max_query_len) == 1
 
 
+def _max_seq_len_bound(attn_metadata, block_table, block_size: int) -> int:
+    """An upper bound of seq_lens that costs no device read: the engine's own max_seq_len when its metadata carries
+    one (a host integer), else what the block table can address."""
+    bound = getattr(attn_metadata, "max_seq_len", None)
+    limit = int(block_table.shape[1]) * int(block_size)
+    if bound is None or isinstance(bound, torch.Tensor):  # a device tensor would have to be read back
+        return limit
+    return max(1, min(int(bound), limit))
+
+
 def _run_int8_attention(layer, query, attn_metadata):
-    """query may be padded beyond num_actual_tokens; the slice is a view and is passed on as such."""
+    """query may be padded beyond num_actual_tokens; the slice is a view and is passed on as such.  No device value
+    is read on the host: the sequence-length bound comes from the metadata or from the table's width."""
     shadow = get_layer_cache(layer.layer_name)
     tokens = int(getattr(attn_metadata, "num_actual_tokens", query.shape[0]))
+    block_table = _get_block_table(attn_metadata)
     return int8_paged_attention(
         query[:tokens],
         shadow.key_cache,
         shadow.value_cache,
-        _get_block_table(attn_metadata).contiguous(),
-        attn_metadata.seq_lens.contiguous(),
+        block_table,
+        attn_metadata.seq_lens,
         shadow.k_scale,
         shadow.v_scale,
         quantize_q=False,
+        max_seq_len=_max_seq_len_bound(attn_metadata, block_table, shadow.key_cache.shape[1]),
     )
 
 

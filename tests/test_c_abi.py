@@ -120,9 +120,9 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert lib.int8kv_cache_write(None, None, 0, 1, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.E_NULLPTR
     assert lib.int8kv_cache_write(None, None, 0, 0, 4, 128, st3, st3, None, None, st4, st4, 1, 16, None, 1, None, None, None) == _lib.OK
     # attention: Hq not a multiple of Hkv, bad dtype, null pointers, too many splits
-    def attn(q_dtype=0, B=1, Hq=28, Hkv=4, splits=0):
+    def attn(q_dtype=0, B=1, Hq=28, Hkv=4, splits=0, flags=0):
         return lib.int8kv_paged_attn_int8(None, q_dtype, st3, B, Hq, Hkv, 128, None, None, st4, st4, 4, 16, None, 0, st2, 4,
-                                          None, 0, 64, None, None, None, 0, st3, splits, None, 0, 0, None)
+                                          None, 0, 64, None, None, None, 0, st3, splits, None, 0, flags, None)
     assert attn(Hq=30) == _lib.E_BAD_SHAPE
     assert attn(q_dtype=5) == _lib.E_BAD_DTYPE
     assert attn() == _lib.E_NULLPTR
@@ -130,26 +130,35 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert attn(splits=10 ** 6) == _lib.E_BAD_SHAPE
     assert attn(splits=-2) == _lib.E_BAD_SHAPE
     assert attn(splits=_lib.SPLITS_PLANNED) == _lib.E_NULLPTR  # -1 is a valid request; the null pointers are not
+    # flags: the two defined bits pass validation (and then meet the null pointers), any other bit is refused
+    assert attn(flags=_lib.FLAG_QUANTIZE_Q | _lib.FLAG_INPUTS_READY) == _lib.E_NULLPTR
+    assert attn(flags=4) == _lib.E_BAD_SHAPE
     assert lib.int8kv_merge_partials(None, 0, 1, 28, 128, None, 0, st3, None) == _lib.E_BAD_SHAPE
     assert lib.int8kv_merge_partials(None, 2, 1, 28, 128, None, 0, st3, None) == _lib.E_NULLPTR
     assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 2, st4, st4, 4, 16, None, 0, st2, 4,
-                                      None, 0, 64, None, 0, st3, 0, None, 0, None) == _lib.E_BAD_DTYPE
+                                      None, 0, 64, None, 0, st3, 0, None, 0, 0, None) == _lib.E_BAD_DTYPE
+    # the INT8 query option does not exist for float caches
+    assert lib.int8kv_paged_attn_bf16(None, 0, st3, 1, 28, 4, 128, None, None, 0, st4, st4, 4, 16, None, 0, st2, 4,
+                                      None, 0, 64, None, 0, st3, 0, None, 0, _lib.FLAG_QUANTIZE_Q, None) == _lib.E_UNSUPPORTED
     # dynamic-scale attention: scale caches are required
     def dyn(ksc, B=1):
         return lib.int8kv_paged_attn_int8_dynamic(None, 0, st3, B, 28, 4, 128, None, None, st4, st4, ksc, None, st3, st3,
-                                                  4, 16, None, 0, st2, 4, None, 0, 64, None, 0, st3, 0, None, 0, None)
+                                                  4, 16, None, 0, st2, 4, None, 0, 64, None, 0, st3, 0, None, 0, 0, None)
     assert dyn(None) == _lib.E_NULLPTR
     assert dyn(None, B=0) == _lib.OK
     # the L-layer decode step: no layers is a no-op, a null array is refused, a failing layer is named
     failed = C.c_int(7)
     def layers_call(arr, n):
         return lib.int8kv_decode_step_layers(arr, n, C.byref(failed), 0, st3, st3, None, 0, 0, st3, 1, 28, 4, 128, st4, st4,
-                                             4, 16, None, 0, st2, 4, None, 0, 64, 0, st3, 0, None, 0, None)
+                                             4, 16, None, 0, st2, 4, None, 0, 64, 0, st3, 0, None, 0, 0, None)
     assert layers_call(None, 0) == _lib.OK and failed.value == -1
     assert layers_call(None, -1) == _lib.E_BAD_SHAPE
     assert layers_call(None, 2) == _lib.E_NULLPTR
     arr = (_lib.LayerArgs * 2)()  # all-null per-layer pointers: the first layer fails its own null check
     assert layers_call(arr, 2) == _lib.E_NULLPTR and failed.value == 0
+    # the library's own workspace: its accessors refuse null destinations before touching the device
+    assert lib.int8kv_static_ws_status(None, 0, None) == _lib.E_NULLPTR
+    assert lib.int8kv_static_ws_address(None) == _lib.E_NULLPTR
 
 
 def test_error_type_carries_the_status(lib):

@@ -424,6 +424,108 @@ def test_decode_step_layers_equals_per_layer_calls(kv, workloads):
         kv.int8_decode_step_layers(queries, None, None, bad, vcs, None, bt, sl, kscales, vscales, max_seq_len=max(lens))
 
 
+def test_inputs_ready_promise_changes_timing_not_results(kv, workloads):
+    """A chain of calls that carry the inputs-ready promise (each starts reading while the previous call's merge is
+    still running, and orders itself behind it only before its first write) returns bit for bit what the fully ordered
+    chain returns: INT8 with fixed, automatic and device-planned splits, the BF16 baseline, the fused decode step and
+    the L-layer entry point, launched eagerly and replayed as a CUDA graph.  All inputs are resident before the
+    chain starts and every call has its own cache and output, which is what the promise asks for."""
+    dev = "cuda"
+    lens = [700, 45, 260, 1, 2048, 130]
+    layers = []
+    for li in range(6):
+        case, kc, vc = _case_on_gpu(kv, workloads, lens, seed=50 + li)
+        kb = torch.zeros(case.num_blocks, 16, 4, 128, dtype=torch.bfloat16)
+        vb = torch.zeros_like(kb)
+        s_ = case.slot_mapping
+        kb[s_ // 16, s_ % 16], vb[s_ // 16, s_ % 16] = case.key, case.value
+        layers.append(dict(case=case, q=case.query.to(dev), kc=kc.to(dev), vc=vc.to(dev), kb=kb.to(dev), vb=vb.to(dev),
+                           bt=case.block_tables.to(dev), sl=case.seq_lens.to(dev), ks=case.k_scale.to(dev),
+                           vs=case.v_scale.to(dev)))
+    mx = max(lens)
+    split_modes = [None, 1, 4, "planned", 16, None]
+
+    def chain(ready, outs):
+        for i, (L, sp) in enumerate(zip(layers, split_modes)):
+            kv.int8_paged_attention(L["q"], L["kc"], L["vc"], L["bt"], L["sl"], L["ks"], L["vs"], num_splits=sp,
+                                    max_seq_len=mx, out=outs[0][i], inputs_ready=ready)
+        for i, (L, sp) in enumerate(zip(layers, split_modes)):
+            kv.bf16_paged_attention(L["q"], L["kb"], L["vb"], L["bt"], L["sl"], num_splits=sp, max_seq_len=mx,
+                                    out=outs[1][i], inputs_ready=ready)
+
+    def fresh():
+        return [torch.full((6, len(lens), 28, 128), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+
+    want = fresh()
+    chain(False, want)
+    torch.cuda.synchronize()
+    for L, o in zip(layers, want[0]):
+        c = L["case"]
+        _check(o, oracle.int8_paged_attention_oracle(c.query, L["kc"].cpu(), L["vc"].cpu(), c.block_tables, lens,
+                                                     c.k_scale, c.v_scale))
+    got = fresh()
+    for _ in range(3):  # back to back, so that calls really overlap their predecessors
+        chain(True, got)
+    torch.cuda.synchronize()
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    # the same chain replayed as a CUDA graph
+    got2 = fresh()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        chain(True, got2)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            chain(True, got2)
+        for o in got2:
+            o.fill_(float("nan"))
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+    assert torch.equal(got2[0], want[0]) and torch.equal(got2[1], want[1])
+    del g
+    # fused decode step per layer and the L-layer entry point: the new rows rewrite each sequence's last token
+    last = torch.tensor([sum(lens[: b + 1]) - 1 for b in range(len(lens))])
+    c0 = layers[0]["case"]
+    slots = c0.slot_mapping[last].to(dev)
+
+    def step_chain(ready, outs, caches):
+        for i, L in enumerate(layers):
+            c = L["case"]
+            kv.int8_decode_step(L["q"], c.key[last].to(dev), c.value[last].to(dev), caches[i][0], caches[i][1],
+                                c.slot_mapping[last].to(dev), L["bt"], L["sl"], L["ks"], L["vs"], max_seq_len=mx,
+                                out=outs[i], inputs_ready=ready and i > 0)
+
+    caches_a = [(L["kc"].clone(), L["vc"].clone()) for L in layers]
+    caches_b = [(L["kc"].clone(), L["vc"].clone()) for L in layers]
+    wa, wb = fresh()[0], fresh()[0]
+    step_chain(False, wa, caches_a)
+    for _ in range(2):
+        step_chain(True, wb, caches_b)
+    torch.cuda.synchronize()
+    assert torch.equal(wa, wb)
+    for (ka, va), (kb_, vb_) in zip(caches_a, caches_b):
+        assert torch.equal(ka, kb_) and torch.equal(va, vb_)
+    # L layers behind one call, attention only, planned splits
+    del slots
+    outs = fresh()[0]
+    plan = kv.DecodeStepLayers([L["q"] for L in layers], None, None, [L["kc"] for L in layers],
+                               [L["vc"] for L in layers], None, layers[0]["bt"], layers[0]["sl"],
+                               [L["ks"] for L in layers], [L["vs"] for L in layers], max_seq_len=mx,
+                               num_splits="planned", out=outs, inputs_ready=True)
+    ordered = fresh()[0]
+    plain = kv.DecodeStepLayers([L["q"] for L in layers], None, None, [L["kc"] for L in layers],
+                                [L["vc"] for L in layers], None, layers[0]["bt"], layers[0]["sl"],
+                                [L["ks"] for L in layers], [L["vs"] for L in layers], max_seq_len=mx,
+                                num_splits="planned", out=ordered)
+    plain()
+    for _ in range(3):
+        plan()
+    torch.cuda.synchronize()
+    assert torch.equal(outs, ordered)
+    assert kv.device_status() == 0
+
+
 def test_device_planned_splits(kv, workloads):
     """num_splits="planned": the kernel reads seq_lens and cuts the sequences into parts of one common length that
     fill whole waves of warps; every operator that takes the tiled path accepts it."""
@@ -756,11 +858,68 @@ def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
         _check(res[:2], want)
         if mode == "int8_only":
             assert ap.ATTN_INT8_HITS[Layer.layer_name] == 1 and ap.ATTN_INT8_STATS["last_batch"] == 2
+            # the INT8-only forward reads nothing back on the host, so a decode step can be captured in a CUDA
+            # graph (a host read of a device value during capture raises) and replayed
+            out2 = torch.zeros(4, 28, 128, dtype=torch.bfloat16, device=dev)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    impl.forward(Layer(), padded_q, None, None, native, Meta(), out2)
+                out2.zero_()
+                g.replay()
+                stream.synchronize()
+            _check(out2[:2], want)
+            del g
         else:
             m = ap.ATTN_METRICS[Layer.layer_name][0]
             assert m["cosine"] > 0.9999 and m["relative_l2"] < 0.02
     pool.clear_cache_pool()
     sc.clear_static_scales()
+
+
+def test_workspace_growth_keeps_captured_graphs_valid(kv, workloads):
+    """A CUDA graph captured over a small call keeps the address of the split-KV workspace of that time.  A later,
+    larger call makes the operator module switch to a bigger buffer; the old one must stay allocated, or the
+    graph's partial rows would land in memory that now belongs to someone else.  Growth during a capture is
+    refused with an explanation instead of allocating from the graph's private pool."""
+    kv.release_workspaces()
+    dev = "cuda"
+    small, kc_s, vc_s = _case_on_gpu(kv, workloads, [600, 90], seed=61)
+    want_small = oracle.int8_paged_attention_oracle(small.query, kc_s, vc_s, small.block_tables, [600, 90],
+                                                    small.k_scale, small.v_scale)
+    args_s = _dev(small.query, kc_s, vc_s, small.block_tables, small.seq_lens, small.k_scale, small.v_scale)
+    out_s = torch.zeros(2, 28, 128, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        kv.int8_paged_attention(*args_s, num_splits=4, max_seq_len=600, out=out_s)  # sizes the workspace: 1 MiB
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            kv.int8_paged_attention(*args_s, num_splits=4, max_seq_len=600, out=out_s)
+        # a call that needs more than the current buffer, inside a capture: refused, nothing allocated
+        big, kc_b, vc_b = _case_on_gpu(kv, workloads, [3000] * 12, seed=62)
+        args_b = _dev(big.query, kc_b, vc_b, big.block_tables, big.seq_lens, big.k_scale, big.v_scale)
+        g2 = torch.cuda.CUDAGraph()
+        with pytest.raises(RuntimeError, match="before capturing"):
+            with torch.cuda.graph(g2, stream=stream):
+                kv.int8_paged_attention(*args_b, num_splits=64, max_seq_len=3000)
+        del g2
+        # the same call eagerly: the module moves to a bigger buffer (12 * 28 * 64 rows of 528 B = 11 MB)
+        out_b = kv.int8_paged_attention(*args_b, num_splits=64, max_seq_len=3000)
+        stream.synchronize()
+        _check(out_b, oracle.int8_paged_attention_oracle(big.query, kc_b, vc_b, big.block_tables, [3000] * 12,
+                                                         big.k_scale, big.v_scale))
+        # memory pressure of the kind that would reuse a freed megabyte, then the old graph again
+        junk = [torch.full((1 << 20,), 0x7F, dtype=torch.uint8, device=dev) for _ in range(8)]
+        out_s.zero_()
+        g.replay()
+        stream.synchronize()
+        assert all(int(j[0]) == 0x7F and int(j[-1]) == 0x7F and int(j.min()) == 0x7F for j in junk)
+    _check(out_s, want_small)
+    del g
+    kv.release_workspaces()
+    assert kv.device_status() == 0
 
 
 def test_long_parts_and_sink_plus_crowd_distributions(kv, workloads):

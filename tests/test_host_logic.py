@@ -266,6 +266,48 @@ def test_attention_patch_falls_back_outside_decode_and_rejects_unknown_modes():
     assert res is out and float(out.min()) == 3.0 and ap.ATTN_INT8_HITS.get(Layer.layer_name, 0) == 0
 
 
+def test_attention_call_site_passes_a_length_bound_instead_of_reading_seq_lens(monkeypatch):
+    """The reference's operator reads seq_lens back on the host twice per call
+    (src/triton_ops/int8_paged_attention.py:720-721); the call site here hands the operator an upper bound taken from
+    the engine's metadata, or from the block table's width, so that no device value is read."""
+    ap = package("vllm_int8.vllm_int8_attention_patch")
+    pool = package("vllm_int8.cache_manager")
+    pool.clear_cache_pool()
+    seen = {}
+
+    def fake_attention(query, kc, vc, block_tables, seq_lens, ks, vs, **kw):
+        seen.update(kw, query_shape=tuple(query.shape), table_is_same=block_tables)
+        return torch.zeros_like(query)
+
+    monkeypatch.setattr(ap, "int8_paged_attention", fake_attention)
+
+    class Layer:
+        layer_name = "model.layers.3.self_attn.attn"
+
+    pool.INT8_CACHE_POOL[Layer.layer_name] = pool.LayerInt8Cache(
+        key_cache=torch.zeros(6, 16, 2, 8, dtype=torch.int8), value_cache=torch.zeros(6, 16, 2, 8, dtype=torch.int8),
+        k_scale=torch.ones(2), v_scale=torch.ones(2))
+
+    class Meta:
+        seq_lens = torch.tensor([40, 17])
+        block_table = torch.zeros(2, 5, dtype=torch.int32)
+        num_actual_tokens = 2
+
+    q = torch.zeros(4, 4, 8)
+    ap._run_int8_attention(Layer(), q, Meta())
+    assert seen["max_seq_len"] == 5 * 16 and seen["query_shape"] == (2, 4, 8) and seen["table_is_same"] is Meta.block_table
+    Meta.max_seq_len = 40  # the engine's own bound wins when it is a host integer ...
+    ap._run_int8_attention(Layer(), q, Meta())
+    assert seen["max_seq_len"] == 40
+    Meta.max_seq_len = 10 ** 6  # ... and never exceeds what the table can address
+    ap._run_int8_attention(Layer(), q, Meta())
+    assert seen["max_seq_len"] == 80
+    Meta.max_seq_len = torch.tensor(40)  # a tensor would have to be read back: the table's width is used
+    ap._run_int8_attention(Layer(), q, Meta())
+    assert seen["max_seq_len"] == 80
+    pool.clear_cache_pool()
+
+
 def test_scale_calibration_accumulates_running_maxima(tmp_path):
     cal_mod = package("calibration")
     sc = package("vllm_int8.static_scales")
