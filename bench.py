@@ -24,7 +24,8 @@ Printed JSON (one line, rank 0):
   c5            long context B=32 x 65536, Hq=64/Hkv=8: whole on one GPU; on N GPUs head-parallel (no collective)
                 and sequence-parallel (partial rows exchanged over NVLink, then merged), the latter checked
                 against single-device attention over the same tokens
-`--impl reference` times the CPU path alone with all host threads.
+`--impl reference` times the CPU path alone with all host threads.  `--shape Hq,Hkv,D,BLOCK[,BATCH,SEQ]` times one
+layer of any other shape (head_dim 64, 96, 256 ..., larger groups, odd block sizes) instead.
 """
 
 from __future__ import annotations
@@ -456,6 +457,39 @@ def leg_cache_write(ctx):
     }
 
 
+def leg_shape(ctx, spec: str):
+    """int8_paged_attention on one layer of an arbitrary shape, "--shape Hq,Hkv,D,block[,batch,seq]": the layers outside
+    the headline workloads (all of them head_dim 128), which the library serves with its non-tiled kernels.  The
+    cache holds random INT8 bytes (the kernels' time does not depend on the values), the block table is the
+    identity, and two distinct caches are visited in turn so that every call reads its pages from DRAM; launched
+    eagerly.  GB/s counts the K and V bytes of the tokens attended, once."""
+    kv, dev, args = ctx.kv, ctx.device, ctx.args
+    vals = [int(x) for x in spec.split(",")]
+    hq, hkv, d, bs = vals[:4]
+    batch = vals[4] if len(vals) > 4 else 64
+    seq = vals[5] if len(vals) > 5 else 2048
+    per_seq = (seq + bs - 1) // bs
+    nblk = per_seq * batch
+    gen = torch.Generator(device=dev).manual_seed(1)
+    caches = [tuple(torch.randint(-127, 128, (nblk, bs, hkv, d), device=dev, dtype=torch.int8, generator=gen)
+                    for _ in range(2)) for _ in range(2)]
+    bt = torch.arange(nblk, device=dev, dtype=torch.int32).view(batch, per_seq)
+    sl = torch.full((batch,), seq, device=dev, dtype=torch.int32)
+    q = torch.randn(batch, hq, d, device=dev, generator=gen).to(torch.bfloat16)
+    ks = torch.full((hkv,), 0.02, device=dev)
+    out = torch.empty_like(q)
+
+    def calls():
+        for kc, vc in caches:
+            kv.int8_paged_attention(q, kc, vc, bt, sl, ks, ks, max_seq_len=seq, out=out, num_splits=args.num_splits)
+
+    us = ctx.time_device(calls, graph=False) * 1e3 / len(caches)
+    nbytes = batch * seq * hkv * d * 2
+    return {"shape": {"q_heads": hq, "kv_heads": hkv, "head_dim": d, "block_size": bs, "batch": batch, "seq": seq},
+            "caches": len(caches), "num_splits": args.num_splits, "us_per_call": round(us, 2), "bytes_per_call": nbytes,
+            "gb_per_s": round(nbytes / us / 1e3, 1), "device_status": kv.device_status(dev)}
+
+
 def leg_sweep(ctx, variants=True):
     """The single-GPU sweep B in {1,2,4,8} x seq in {512,1024,2048,4096} at Hq=28/Hkv=4 (the grid of the reference's
     bench/bench_paged_attention.py): microseconds per call for INT8 (automatic split), the same-run BF16 baseline
@@ -645,15 +679,38 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         h2d, d2h = h_in.numel(), h_out.numel() * 2
         stream = ctx.stream
 
+        # Copies and compute overlap layer by layer, as a serving engine's copy engines would run them: the inputs
+        # of layer l+1 travel to the device and the output of layer l-1 travels back while layer l computes.
+        # Every byte of the step still moves inside the timed region.
+        s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        meta_h, meta_d = h_in[layers * per_layer:], d_in[layers * per_layer:]
+
         def e2e_enqueue():
-            d_in.copy_(h_in, non_blocking=True)
+            main = torch.cuda.current_stream(device)
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+            ready_in = []
+            with torch.cuda.stream(s_in):
+                meta_d.copy_(meta_h, non_blocking=True)
+                for i in range(layers):
+                    d_in[i * per_layer:(i + 1) * per_layer].copy_(h_in[i * per_layer:(i + 1) * per_layer], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                    ready_in.append(ev)
             for i, L in enumerate(layers_data):
                 q, k, v = dv[i]
+                main.wait_event(ready_in[i])
                 # the first layer's kernel follows the host-to-device copy and orders itself behind it
                 kv.int8_decode_step(q, k, v, L.kc, L.vc, d_slots, d_bt, d_sl, L.k_scale, L.v_scale,
                                     num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i],
                                     inputs_ready=ready and i > 0)
-            h_out.copy_(d_out, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    h_out[i].copy_(d_out[i], non_blocking=True)
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
 
         def eager_step():
             e2e_enqueue()
@@ -717,11 +774,13 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
                 "eager_value": total_step_bytes / (e2e_eager_ms * 1e-3) / 1e9,
                 "one_call_ms_per_step": e2e_layers_ms,
                 "one_call_value": total_step_bytes / (e2e_layers_ms * 1e-3) / 1e9,
-                "what": "per step and rank: one pinned-host buffer (all layers' new q/k/v rows, block tables, seq_lens, "
+                "what": "per step and rank: pinned-host inputs (every layer's new q/k/v rows; block tables, seq_lens, "
                         "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python "
-                        "operators, all outputs -> pinned host, stream synchronised; `value` replays those calls as one "
-                        "CUDA graph, `eager_value` launches them from Python every step, `one_call_value` launches them "
-                        "every step through one int8kv_decode_step_layers call (no graph); bytes are summed over ranks"},
+                        "operators, every layer's output -> pinned host, all streams synchronised; the copies run on "
+                        "their own streams, layer by layer, beside the compute of the neighbouring layers; `value` "
+                        "replays the step as one CUDA graph, `eager_value` launches it from Python every step, "
+                        "`one_call_value` copies everything in, runs one int8kv_decode_step_layers call and copies "
+                        "everything out (no graph, no overlap); bytes are summed over ranks"},
         "l2_warm": {"us_per_call": warm_ms * 1e3 / layers,
                     "what": "the same calls repeated on one layer's cache (re-read from L2 when it fits): not the "
                             "headline, which reads a different cache per call"},
@@ -758,10 +817,13 @@ def leg_sequence_parallel(ctx, hq, hkv, seq_lens):
             max_seq_len=max_local)
 
     variants = [("nccl_all_gather", nccl_step, "nccl")]
-    exchange = getattr(sh, "PeerExchange", None)
     peer = None
-    if exchange is not None and not args.no_peer_exchange:
-        peer = exchange(len(seq_lens), hq, 128, device)
+    if not args.no_peer_exchange:
+        try:
+            peer = sh.PeerExchange(len(seq_lens), hq, 128, device)
+        except Exception as e:  # no symmetric-memory mapping on this box: the NCCL variant stands alone
+            result["peer_stores"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    if peer is not None:
 
         def peer_step():
             merged["peer"] = sh.sequence_parallel_int8_attention(
@@ -835,6 +897,8 @@ def main():
                     help="dynamic: time the attention over per-(token, head) scale caches (device leg only)")
     ap.add_argument("--sweep", action="store_true",
                     help="c2 only, one GPU: time all 16 cells of the sweep and list them under `cells`")
+    ap.add_argument("--shape", default=None, metavar="Hq,Hkv,D,BLOCK[,BATCH,SEQ]",
+                    help="time int8_paged_attention on one layer of any shape (one GPU) and print that record alone")
     ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
     ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
     args = ap.parse_args()
@@ -887,6 +951,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the kernels)")
     ctx = Ctx(args, rank, local_rank, world)
     try:
+        if args.shape:
+            print(json.dumps(leg_shape(ctx, args.shape)))
+            return
         if args.workload == "c3":
             rec = leg_cache_write(ctx)
             line = {"metric": rec.pop("metric"), "value": rec["value"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,

@@ -315,6 +315,50 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
                           void* out, int out_dtype, const int64_t out_strides[3], void* stream);
 
 /*
+ * Sequence-parallel exchange over peer memory (NVLink / NVSwitch), for the split of one long sequence across GPUs
+ * with one process per GPU.  The reference has no multi-GPU path; the math is its split-KV merge (:330-388) across
+ * devices, as with int8kv_paged_attn_int8_partial + int8kv_merge_partials, but the partial rows travel by plain
+ * 16-byte stores into the other ranks' memory instead of through a collective library:
+ *   - every rank owns one exchange buffer of int8kv_exchange_bytes() bytes, 256-byte aligned, ZEROED before first
+ *     use, and mapped into every other rank's address space (CUDA IPC or a symmetric-memory allocator; the library
+ *     allocates and maps nothing).  `peer_buffers[r]` is rank r's buffer as seen from THIS process; entry `rank`
+ *     is the local one.  All ranks must agree on world, batch, num_q_heads, head_dim;
+ *   - int8kv_paged_attn_int8_partial_push computes this rank's partial rows (arguments of
+ *     int8kv_paged_attn_int8_partial) and stores them, with an arrival flag behind them, into every rank's buffer;
+ *     it never waits for another GPU;
+ *   - int8kv_merge_exchanged, enqueued behind it on the same stream, waits until every rank's rows of the current
+ *     step have arrived and merges them from LOCAL memory.  The wait is bounded (about a second); if it runs out,
+ *     INT8KV_DEV_WAIT_TIMEOUT is set in the status word of `workspace` (optional) and the output is left unwritten.
+ * Both keep their step count on the device, so the pair can be captured in a CUDA graph and replayed.  Every rank must
+ * make the same sequence of push / merge pairs; buffers alternate between two slabs so that a fast rank's next step
+ * does not overwrite what a slow rank is still merging.
+ */
+typedef struct int8kv_exchange {
+  int world;                 /* ranks, 1..16 */
+  int rank;                  /* this process's rank */
+  void* peer_buffers[16];    /* [world] device addresses valid in this process */
+  int64_t buffer_bytes;      /* size of each buffer */
+} int8kv_exchange;
+
+int64_t int8kv_exchange_bytes(int world, int batch, int num_q_heads, int head_dim);
+
+int int8kv_paged_attn_int8_partial_push(const void* query, int q_dtype, const int64_t q_strides[3],
+                           int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                           const int8_t* key_cache, const int8_t* value_cache,
+                           const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                           int64_t num_blocks, int block_size,
+                           const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                           const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                           const float* k_scale, const float* v_scale,
+                           const int8kv_exchange* exchange,
+                           int num_splits, void* workspace, int64_t workspace_bytes,
+                           int flags, void* stream);
+
+int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q_heads, int head_dim,
+                           void* out, int out_dtype, const int64_t out_strides[3],
+                           void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * Self-test of the failure path.  Every wait for staged data inside the kernels is bounded; when one runs out the
  * kernel sets INT8KV_DEV_WAIT_TIMEOUT in the workspace's status word and returns.  This entry point launches one warp
  * that waits, with at most `attempts` (1..65536) attempts of about a microsecond, for data that nothing sends, so a

@@ -24,6 +24,8 @@ from .ops import (  # noqa: F401
     int8_kv_cache_write,
     int8_paged_attention,
     int8_paged_attention_partial,
+    int8_paged_attention_partial_push,
+    merge_exchanged,
     merge_partials,
     partial_row_floats,
     release_workspaces,
@@ -36,6 +38,8 @@ __all__ = [
     "int8_paged_attention",
     "bf16_paged_attention",
     "int8_paged_attention_partial",
+    "int8_paged_attention_partial_push",
+    "merge_exchanged",
     "int8_paged_attention_dynamic",
     "int8_decode_step",
     "int8_decode_step_layers",

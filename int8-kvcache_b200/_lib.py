@@ -42,6 +42,12 @@ class LayerArgs(C.Structure):
     ]
 
 
+class Exchange(C.Structure):
+    """int8kv_exchange of include/int8kv_b200.h: the peer-mapped buffers of the sequence-parallel exchange."""
+
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("peer_buffers", _VP * 16), ("buffer_bytes", C.c_int64)]
+
+
 _SIGNATURES = {
     "int8kv_abi_version": (C.c_int, []),
     "int8kv_status_str": (C.c_char_p, [C.c_int]),
@@ -107,6 +113,16 @@ _SIGNATURES = {
     ),
     "int8kv_static_ws_status": (C.c_int, [_VP, C.c_int, _VP]),
     "int8kv_static_ws_address": (C.c_int, [C.POINTER(_VP)]),
+    "int8kv_exchange_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "int8kv_paged_attn_int8_partial_push": (
+        C.c_int,
+        [_VP, C.c_int, _I64P, C.c_int, C.c_int, C.c_int, C.c_int, _VP, _VP, _I64P, _I64P, C.c_int64, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, _VP, _VP, C.POINTER(Exchange),
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
+    ),
+    "int8kv_merge_exchanged": (
+        C.c_int, [C.POINTER(Exchange), C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP, C.c_int64, _VP],
+    ),
     "int8kv_selftest_bounded_wait": (C.c_int, [_VP, C.c_int64, C.c_int, _VP]),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),
 }

@@ -134,8 +134,7 @@ int untiled_splits(int B, int Hq, int Hkv, int D, bool int8_cache, int64_t max_s
 
 // ---- device-planned splits ----------------------------------------------------------------------------
 // Large calls (HBM-bound, up to a few resident waves of warps) choose the part length on the device from the
-// actual sequence lengths, so that the parts fill whole waves; see plan_in_warp.  INT8KV_PLAN=0 turns it off,
-// INT8KV_PLAN_MIN_TILES sets the shortest part the plan may choose when it aims for more than one wave.
+// actual sequence lengths, so that the parts fill whole waves; see plan_in_warp.  INT8KV_PLAN=0 turns it off.
 struct PlanShape {
   int k_max;       // most waves the plan may aim for
   int max_items;   // capacity of the item list = item numbers the attention launch covers
@@ -169,7 +168,7 @@ bool plan_pays(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
 }
 
 PlanShape plan_shape(int B, int Hkv, int64_t tiles, int sm_count) {
-  static const int min_part = std::max(1, env_int_or("INT8KV_PLAN_MIN_TILES", 48));
+  constexpr int min_part = 48;  // shortest part (16-token tiles) a plan aiming for more than one wave may choose
   const int64_t slots = static_cast<int64_t>(sm_count) * 12;
   const int64_t items = static_cast<int64_t>(B) * Hkv;
   PlanShape s{1, 0, min_part};
@@ -531,6 +530,78 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
   m.out = out; m.out_dtype = out_dtype;
   for (int i = 0; i < 3; ++i) m.o_st[i] = out_strides[i];
   m.part_out = nullptr;
+  return launch_merge(m, static_cast<cudaStream_t>(stream));
+}
+
+int64_t int8kv_exchange_bytes(int world, int batch, int num_q_heads, int head_dim) {
+  if (world <= 0 || world > kMaxPeers || batch < 0 || num_q_heads <= 0 || head_dim <= 0) return -1;
+  const int64_t slab = static_cast<int64_t>(batch) * num_q_heads * partial_row_floats(head_dim) * 4;
+  return kExchCtrlBytes + slab * (1 + 2 * static_cast<int64_t>(world));
+}
+
+static int exchange_params(const int8kv_exchange* ex, int batch, int num_q_heads, int head_dim, ExchangeParams* e) {
+  if (ex == nullptr) return INT8KV_E_NULLPTR;
+  if (ex->world <= 0 || ex->world > kMaxPeers || ex->rank < 0 || ex->rank >= ex->world) return INT8KV_E_BAD_SHAPE;
+  if (ex->buffer_bytes < int8kv_exchange_bytes(ex->world, batch, num_q_heads, head_dim)) return INT8KV_E_WORKSPACE;
+  std::memset(e, 0, sizeof(*e));
+  e->world = ex->world;
+  e->rank = ex->rank;
+  for (int r = 0; r < ex->world; ++r) {
+    if (ex->peer_buffers[r] == nullptr) return INT8KV_E_NULLPTR;
+    if (reinterpret_cast<uintptr_t>(ex->peer_buffers[r]) & 255u) return INT8KV_E_WORKSPACE;
+    e->peer[r] = static_cast<char*>(ex->peer_buffers[r]);
+  }
+  e->rows = static_cast<int64_t>(batch) * num_q_heads;
+  e->row_floats = partial_row_floats(head_dim);
+  return INT8KV_OK;
+}
+
+int int8kv_paged_attn_int8_partial_push(const void* query, int q_dtype, const int64_t q_strides[3], int batch,
+                                        int num_q_heads, int num_kv_heads, int head_dim, const int8_t* key_cache,
+                                        const int8_t* value_cache, const int64_t key_cache_strides[4],
+                                        const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                                        const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                                        int64_t bt_width, const void* seq_lens, int sl_is_i64,
+                                        int64_t max_seq_len_hint, const float* k_scale, const float* v_scale,
+                                        const int8kv_exchange* exchange, int num_splits, void* workspace,
+                                        int64_t workspace_bytes, int flags, void* stream) {
+  if (batch < 0 || num_q_heads <= 0 || head_dim <= 0) return INT8KV_E_BAD_SHAPE;
+  ExchangeParams e;
+  int rc = exchange_params(exchange, batch, num_q_heads, head_dim, &e);
+  if (rc != INT8KV_OK) return rc;
+  if (batch == 0) return INT8KV_OK;
+  float* staging = reinterpret_cast<float*>(e.peer[e.rank] + kExchCtrlBytes);
+  rc = int8kv_paged_attn_int8_partial(query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, key_cache,
+                                      value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
+                                      block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
+                                      max_seq_len_hint, k_scale, v_scale, staging, num_splits, workspace,
+                                      workspace_bytes, flags, stream);
+  if (rc != INT8KV_OK) return rc;
+  return launch_exchange_push(e, static_cast<cudaStream_t>(stream));
+}
+
+int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q_heads, int head_dim, void* out,
+                           int out_dtype, const int64_t out_strides[3], void* workspace, int64_t workspace_bytes,
+                           void* stream) {
+  if (batch < 0 || num_q_heads <= 0 || head_dim <= 0) return INT8KV_E_BAD_SHAPE;
+  if (!valid_float_dtype(out_dtype)) return INT8KV_E_BAD_DTYPE;
+  ExchangeParams e;
+  const int rc = exchange_params(exchange, batch, num_q_heads, head_dim, &e);
+  if (rc != INT8KV_OK) return rc;
+  if (batch == 0) return INT8KV_OK;
+  if (!out || !out_strides) return INT8KV_E_NULLPTR;
+  MergeParams m;
+  std::memset(&m, 0, sizeof(m));
+  const int64_t slab_rows = e.rows * e.row_floats;  // floats of one rank's rows
+  m.parts = reinterpret_cast<const float*>(e.peer[e.rank] + kExchCtrlBytes) + slab_rows;  // slab 0 follows the staging
+  m.R = e.world; m.rows = e.rows; m.Hq = num_q_heads; m.D = head_dim; m.row_floats = e.row_floats;
+  m.out = out; m.out_dtype = out_dtype;
+  for (int i = 0; i < 3; ++i) m.o_st[i] = out_strides[i];
+  m.exchange_ctrl = reinterpret_cast<const int*>(e.peer[e.rank]);
+  m.exchange_world = e.world;
+  m.slab_floats = slab_rows * e.world;
+  if (workspace != nullptr && workspace_bytes >= 16)
+    m.status = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + int8kv_workspace_status_offset(workspace_bytes));
   return launch_merge(m, static_cast<cudaStream_t>(stream));
 }
 

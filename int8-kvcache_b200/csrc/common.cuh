@@ -242,6 +242,19 @@ inline int launch_pdl(void (*kernel)(KArgs...), unsigned grid, unsigned block, s
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? INT8KV_OK : INT8KV_E_LAUNCH;
 }
 
+// Flags that another GPU writes into this GPU's memory (and the other way round) are read and written with
+// system-scope acquire / release, so that the rows stored before a flag are visible to whoever sees the flag.
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Attempts of a wait for another GPU's flag: 100 ns to 1 us apart, so the limit gives up after about a second.
+constexpr uint32_t kFlagSpinLimit = 1u << 20;
+
 __host__ __device__ __forceinline__ int dtype_bytes(int dtype) { return dtype == INT8KV_FP32 ? 4 : 2; }
 
 // ---------------------------------------------------------------------------------------------

@@ -107,6 +107,21 @@ struct AttnParams {
   int plan_min_part;    // shortest part (tiles) the plan may choose when it aims for more than one wave
 };
 
+// Cross-GPU exchange of partial rows through peer-mapped buffers (sequence-parallel attention).  Every rank owns one
+// buffer of the same layout, mapped into every other rank's address space:
+//   [0, 64)     control words of the owner: {ticket of the push kernel's CTAs, epoch = pushes completed}
+//   [64, 256)   arrival flags: flag[q] = epoch of the last push of rank q whose rows have landed in this buffer
+//   [256, ...)  staging [rows, row_floats]: the owner's own partial rows before they are pushed
+//   then        2 slabs x [world, rows, row_floats] fp32, used alternately (epoch parity): slab[s][q] = rows of rank q
+constexpr int kMaxPeers = 16;
+constexpr int kExchCtrlBytes = 256;
+struct ExchangeParams {
+  int world, rank;
+  char* peer[kMaxPeers];  // base of every rank's buffer as mapped here; peer[rank] is the local buffer
+  int64_t rows;           // B * Hq
+  int row_floats;
+};
+
 struct MergeParams {
   const float* parts;  // [R, rows, row_floats]
   int R;
@@ -120,6 +135,13 @@ struct MergeParams {
   const int2* seq_table;  // device-planned splits: parts of row (b, hq) are rows (row0 + c) * Hq + hq, c < used
   int early_trigger;  // call griddepcontrol.launch_dependents right after the dependency wait
   int inputs_ready;   // the call that produced the parts carried the inputs-ready promise: always trigger early
+  // Parts that other GPUs pushed into the local exchange buffer (exchange_ctrl != null): the kernel first waits,
+  // with a bound, until every rank's arrival flag has reached the owner's epoch, and reads the slab of that epoch;
+  // `parts` then points at slab 0 and slab_floats is the distance to slab 1.
+  const int* exchange_ctrl;
+  int exchange_world;
+  int64_t slab_floats;
+  unsigned int* status;
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
@@ -130,6 +152,7 @@ int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUt
                           cudaStream_t stream);
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
+int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream);
 int launch_bounded_wait_selftest(unsigned int* status, unsigned int attempts, cudaStream_t stream);
 
 // resident warps per SM the tiled int8 kernel is sized for (used by the split heuristic)

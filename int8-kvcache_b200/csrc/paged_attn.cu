@@ -31,6 +31,7 @@
 // way to fp16.  v_scale and 1/l are applied once in the epilogue.  The kDynScales mode reads one K and one V scale
 // per (token, head) instead: they travel with the tile through the ring (cp.async, same mbarrier), K scales
 // multiply the score rows, V scales ride on P behind a running power-of-two normalisation.
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -613,20 +614,27 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
     amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
     int qi[32];
     if constexpr (QQ) {
-      // clamp(round_half_away(q / qs), +-127), bit-identical to the division sequence of the reference's kernel
-      // (:137-146) but formed with the reciprocal away from rounding boundaries (quant_half_away)
+      // The reference's INT8 query: q8 = clamp(round(q / qs), +-127) with qs = max(absmax / 127, 1e-6) (:137-146).
+      // The quotient is formed with the reciprocal and rounded to nearest by the 1.5 * 2^23 addition: an IEEE division
+      // and the reference's half-away-from-zero rule would give a different integer only for a quotient within two
+      // ulp of a tie, where one query element moves by one INT8 step (far inside the attention tolerance); a chain of
+      // 32 divisions, or a branch per element, costs a warp that runs alone on its SM more than a microsecond.
       const float qs = fmaxf(amax / 127.f, 1e-6f);
       const float rq = __frcp_rn(qs);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) qi[i] = max(-127, min(127, quant_half_away(qv[i], qs, rq)));
+      for (int i = 0; i < 32; ++i)
+        qi[i] = max(-127, min(127, __float_as_int(fmaf(qv[i], rq, kRoundMagic)) - kRoundMagicBits));
       q_mul = qs;
     } else {
-      const float inv = amax > 0.f ? 32000.f / amax : 0.f;
+      // the exact value of the factor is immaterial as long as q_mul undoes it: approximate reciprocal, no division
+      // (a head whose largest element is below 1e-20 is treated as zero: its scores could not move the softmax)
+      const bool live_q = amax > 1e-20f;
+      const float inv = live_q ? __fdividef(32000.f, amax) : 0.f;
 #pragma unroll
-      // |q * inv| <= 32000: adding 1.5 * 2^23 rounds to nearest and leaves the integer in the low mantissa bits (an
-      // FMA on the full-rate pipe instead of a conversion)
+      // |q * inv| <= 32000 (+ rounding): adding 1.5 * 2^23 rounds to nearest and leaves the integer in the low
+      // mantissa bits (an FMA on the full-rate pipe instead of a conversion)
       for (int i = 0; i < 32; ++i) qi[i] = __float_as_int(fmaf(qv[i], inv, kRoundMagic)) - kRoundMagicBits;
-      q_mul = amax > 0.f ? amax / 32000.f : 0.f;
+      q_mul = live_q ? __fdividef(1.f, inv) : 0.f;
     }
     // v = 256 * hi + lo with lo in [-128, 127]: lo is the low byte of v, hi the second byte of v + 128 (two's
     // complement), so four values pack into the two limb words with byte permutes
@@ -1627,6 +1635,33 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 
   grid_dependency_wait();    // the partial rows come from the attention kernel launched just before
   if (p.early_trigger) grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before reading
+  if (p.exchange_ctrl != nullptr) {
+    // Rows pushed by other GPUs: wait until every rank's push of the current epoch has landed.  The epoch was
+    // advanced by this rank's own push kernel, which precedes this kernel on the stream.  Waits are bounded; a rank
+    // that never arrives is reported in the status word and the row is left unwritten.
+    __shared__ int arrived_s;
+    if (threadIdx.x == 0) arrived_s = 1;
+    __syncthreads();
+    const int epoch = ld_acquire_sys(p.exchange_ctrl + 1);
+    if (static_cast<int>(threadIdx.x) < p.exchange_world) {
+      const int* flag = p.exchange_ctrl + 16 + threadIdx.x;  // byte 64 onwards
+      bool ok = false;
+      for (uint32_t spin = 0; spin < kFlagSpinLimit; ++spin) {
+        if (ld_acquire_sys(flag) - epoch >= 0) {
+          ok = true;
+          break;
+        }
+        __nanosleep(spin < 64 ? 100 : 1000);
+      }
+      if (!ok) arrived_s = 0;
+    }
+    __syncthreads();
+    if (!arrived_s) {
+      if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
+      return;
+    }
+    base += static_cast<int64_t>(epoch & 1) * p.slab_floats;
+  }
   if (p.seq_table != nullptr) {
     // device-planned splits: this sequence's parts are consecutive part indices; a single part was written to
     // `out` by the attention kernel itself
@@ -1637,7 +1672,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
     base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
   }
   float lse = -INFINITY;
-  if (static_cast<int>(threadIdx.x) < R) lse = base[threadIdx.x * stride_r + p.D];  // R <= kMaxSplits = blockDim
+  if (static_cast<int>(threadIdx.x) < R) lse = __ldcg(base + threadIdx.x * stride_r + p.D);  // R <= kMaxSplits = blockDim
   // The first batch of rows is requested before the weights exist, so that both reads share one latency.
   // Rows of empty parts were never written: whatever they hold is discarded by the weight test below.
   float4 pre[4];
@@ -1645,7 +1680,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   for (int u = 0; u < 4; ++u) {
     const int r = warp + u * kMergeWarps;
     pre[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < R && 4 * lane < p.D) pre[u] = *reinterpret_cast<const float4*>(base + r * stride_r + 4 * lane);
+    if (r < R && 4 * lane < p.D) pre[u] = __ldcg(reinterpret_cast<const float4*>(base + r * stride_r + 4 * lane));
   }
   float top = lse;
   for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
@@ -1672,7 +1707,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
         const int r = r0 + u * kMergeWarps;
         w[u] = r < R ? w_s[r] : 0.f;
         o[u] = pre[u];
-        if (!have && live && r < R && w[u] > 0.f) o[u] = *reinterpret_cast<const float4*>(base + r * stride_r + d);
+        if (!have && live && r < R && w[u] > 0.f) o[u] = __ldcg(reinterpret_cast<const float4*>(base + r * stride_r + d));
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -1714,6 +1749,48 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 }
 
 // ---------------------------------------------------------------------------------------------
+// Push of this rank's partial rows into every rank's exchange buffer (sequence-parallel attention over NVLink).
+// The rows sit in the local buffer's staging area; every CTA copies a share of them into slab[epoch & 1][rank] of
+// every peer with plain 16-byte stores to peer-mapped memory (no TMA, no multicast), makes its stores visible
+// system-wide, and takes a ticket; the CTA that draws the last ticket advances the local epoch and raises this
+// rank's arrival flag in every peer's buffer.  Nothing here waits for another GPU.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams e) {
+  grid_dependency_wait();  // the staged rows come from the kernel launched just before
+  grid_launch_dependents();
+  int* ctrl = reinterpret_cast<int*>(e.peer[e.rank]);
+  const int epoch = ld_acquire_sys(ctrl + 1) + 1;
+  const int64_t slab_floats = static_cast<int64_t>(e.world) * e.rows * e.row_floats;
+  const int64_t n4 = e.rows * e.row_floats / 4;  // row_floats is a multiple of 4
+  const float4* src = reinterpret_cast<const float4*>(e.peer[e.rank] + kExchCtrlBytes);
+  const int64_t dst_off = kExchCtrlBytes + (e.rows * e.row_floats + (epoch & 1) * slab_floats +
+                                            static_cast<int64_t>(e.rank) * e.rows * e.row_floats) * 4;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 v = __ldcg(src + i);
+    for (int r = 0; r < e.world; ++r) reinterpret_cast<float4*>(e.peer[r] + dst_off)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(ctrl, 1);
+    if (ticket == static_cast<int>(gridDim.x) - 1) {
+      ctrl[0] = 0;
+      st_release_sys(ctrl + 1, epoch);
+      __threadfence_system();
+      for (int r = 0; r < e.world; ++r) st_release_sys(reinterpret_cast<int*>(e.peer[r] + 64) + e.rank, epoch);
+    }
+  }
+}
+
+int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream) {
+  const int64_t n4 = e.rows * e.row_floats / 4;
+  if (n4 <= 0) return INT8KV_OK;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n4 + 255) / 256, 148 * 4));
+  return launch_pdl(exchange_push_kernel, grid, 256, 0, stream, e);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Self-test of the bounded wait: one warp arms an mbarrier for bytes that no copy will ever deliver, waits with a
 // small attempt limit, and reports the timeout in the status word exactly as the attention kernels do.  It
 // returns normally; the context stays usable.
@@ -1742,28 +1819,6 @@ int launch_bounded_wait_selftest(unsigned int* status, unsigned int attempts, cu
 constexpr int kInt8Stages = 4;
 constexpr int kF16Stages = 3;
 
-static int env_int(const char* name, int fallback) {
-  const char* e = std::getenv(name);
-  return e ? std::atoi(e) : fallback;
-}
-
-// Tuning switches, read once from the environment: INT8KV_STAGES (ring depth of the INT8 kernel),
-// INT8KV_WPC (warps per CTA: 1 or 4, 0 = choose from the grid size).
-struct Tuning {
-  int stages, wpc;
-};
-static const Tuning& tuning() {
-  static const Tuning t = []() {
-    Tuning x;
-    x.stages = env_int("INT8KV_STAGES", kInt8Stages);
-    if (x.stages != 2 && x.stages != 4 && x.stages != 6 && x.stages != 8) x.stages = kInt8Stages;
-    x.wpc = env_int("INT8KV_WPC", 0);
-    if (x.wpc != 1 && x.wpc != 4) x.wpc = 0;
-    return x;
-  }();
-  return t;
-}
-
 // The dynamic shared-memory limit is raised once per (kernel, device); later calls, which may sit inside a
 // stream capture, launch without touching function attributes.
 template <int KERNEL_TAG, typename K>  // the tag keeps one flag array per kernel: the kernels share a signature
@@ -1787,7 +1842,6 @@ static int64_t grid_items(const AttnParams& p) {
 // Warps per CTA: a grid that cannot fill the machine with 4-warp CTAs is launched as 1-warp CTAs so that its
 // warps spread over all SMs instead of stacking four to an SM.
 static int pick_wpc(int64_t items, int sm_count) {
-  if (tuning().wpc) return tuning().wpc;
   return items <= static_cast<int64_t>(sm_count) * 12 ? 1 : kTiledWarpsPerCta;
 }
 
@@ -1807,15 +1861,6 @@ static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, cons
   return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
 }
 
-template <int NST>
-static int launch_int8_stages(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                              cudaStream_t stream) {
-  return p.new_k != nullptr ? launch_int8_variant<NST, kFusedWrite, false>(p, tmK, tmV, sm_count, stream)
-                            : launch_int8_variant<NST, kPlain, false>(p, tmK, tmV, sm_count, stream);
-}
-
-// The ring depth can be changed from the environment for the plain and fused kernels; the dynamic-scale and the
-// planned instantiations exist with the default depth only.
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                            cudaStream_t stream) {
   constexpr int N = kInt8Stages;
@@ -1829,12 +1874,8 @@ int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CU
   if (planned)
     return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, true>(p, tmK, tmV, sm_count, stream)
                               : launch_int8_variant<N, kPlain, true>(p, tmK, tmV, sm_count, stream);
-  switch (tuning().stages) {
-    case 2: return launch_int8_stages<2>(p, tmK, tmV, sm_count, stream);
-    case 6: return launch_int8_stages<6>(p, tmK, tmV, sm_count, stream);
-    case 8: return launch_int8_stages<8>(p, tmK, tmV, sm_count, stream);
-    default: return launch_int8_stages<4>(p, tmK, tmV, sm_count, stream);
-  }
+  return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, false>(p, tmK, tmV, sm_count, stream)
+                            : launch_int8_variant<N, kPlain, false>(p, tmK, tmV, sm_count, stream);
 }
 
 template <bool IS_BF16, bool PLANNED>

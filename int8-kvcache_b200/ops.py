@@ -692,6 +692,57 @@ def int8_paged_attention_partial(
     return out
 
 
+def int8_paged_attention_partial_push(
+    query, key_cache, value_cache, block_tables, seq_lens, k_scale, v_scale, exchange,
+    *, quantize_q: bool = False, num_splits: Optional[int] = None, max_seq_len: Optional[int] = None,
+) -> None:
+    """Unmerged attention over the tokens this cache holds, with the rows stored straight into every rank's exchange
+    buffer (`exchange`: a _lib.Exchange describing the peer-mapped buffers, see sharding.PeerExchange) instead of
+    being returned.  merge_exchanged, called behind it on the same stream, combines what all ranks pushed."""
+    B, Hq, Hkv, D, block_size = _check_decode_args(query, key_cache, value_cache, block_tables, seq_lens)
+    assert key_cache.dtype == torch.int8 and value_cache.dtype == torch.int8
+    lib = _require_lib()
+    k_scale = _as_f32_scale(k_scale)
+    v_scale = _as_f32_scale(v_scale)
+    max_seq = _max_seq_len(seq_lens, block_tables, block_size, max_seq_len, validate=False)
+    max_seq = min(max_seq, block_tables.shape[1] * block_size)
+    if seq_lens.stride(0) != 1:
+        seq_lens = seq_lens.contiguous()
+    splits, ws = _plan_workspace(lib, query.device, B, Hq, Hkv, D, block_size, max(max_seq, 1), num_splits)
+    rc = lib.int8kv_paged_attn_int8_partial_push(
+        query.data_ptr(), _FLOAT_CODES[query.dtype], _lib.i64(query.stride()),
+        B, Hq, Hkv, D,
+        key_cache.data_ptr(), value_cache.data_ptr(),
+        _lib.i64(key_cache.stride()), _lib.i64(value_cache.stride()),
+        key_cache.shape[0], block_size,
+        block_tables.data_ptr(), int(block_tables.dtype == torch.int64),
+        _lib.i64(block_tables.stride()), block_tables.shape[1],
+        seq_lens.data_ptr(), int(seq_lens.dtype == torch.int64), max_seq,
+        k_scale.data_ptr(), v_scale.data_ptr(),
+        C.byref(exchange),
+        splits, ws.data_ptr(), ws.numel(),
+        _flags(quantize_q), _stream_ptr(query.device),
+    )
+    _lib.check("int8kv_paged_attn_int8_partial_push", rc)
+
+
+def merge_exchanged(exchange, batch: int, num_q_heads: int, head_dim: int, dtype=torch.bfloat16,
+                    out: Optional[torch.Tensor] = None, device=None) -> torch.Tensor:
+    """Wait (bounded, on the device) for every rank's pushed rows of the current step and merge them -> [B, Hq, D].
+    A wait that runs out is reported through device_status()."""
+    lib = _require_lib()
+    if out is None:
+        out = torch.empty((batch, num_q_heads, head_dim), device=device, dtype=dtype)
+    assert out.is_cuda and out.dtype in _FLOAT_CODES and out.shape == (batch, num_q_heads, head_dim)
+    ws = _workspace(out.device, 16)
+    rc = lib.int8kv_merge_exchanged(
+        C.byref(exchange), batch, num_q_heads, head_dim, out.data_ptr(), _FLOAT_CODES[out.dtype],
+        _lib.i64(out.stride()), ws.data_ptr(), ws.numel(), _stream_ptr(out.device),
+    )
+    _lib.check("int8kv_merge_exchanged", rc)
+    return out
+
+
 def merge_partials(parts: torch.Tensor, head_dim: int, dtype=torch.bfloat16, out: Optional[torch.Tensor] = None):
     """parts: fp32 [R, B, Hq, row] partial rows (as produced above, one slab per rank) -> [B, Hq, D]."""
     assert parts.is_cuda and parts.dtype == torch.float32 and parts.ndim == 4 and parts.is_contiguous()

@@ -7,8 +7,11 @@ model before the output projection.
 
 The third partition splits the SEQUENCE across ranks for very long contexts: rank r holds a
 contiguous range of every sequence's logical blocks in its own cache, computes unmerged partial
-attention rows (normalised out | log-sum-exp), the rows of all ranks are all-gathered into LOCAL
-memory with NCCL, and a local merge kernel combines them.  The merge reads local memory only.
+attention rows (normalised out | log-sum-exp), the rows of all ranks are brought into LOCAL memory,
+and a local merge kernel combines them.  The merge reads local memory only.  Two exchanges exist:
+an NCCL all-gather, and PeerExchange, where every rank stores its rows straight into the other
+ranks' buffers over NVLink (plain stores to peer-mapped memory, an arrival flag behind them) and
+the merge kernel itself waits, with a bound, for the flags.
 
 The reference prototype is single-GPU (its README states TP=1); the split-KV partial/merge math that
 this generalises is its src/triton_ops/int8_paged_attention.py:293-388.
@@ -105,15 +108,66 @@ def gather_partials(local_rows: torch.Tensor, group=None) -> torch.Tensor:
     return flat.view((world,) + shape)
 
 
+class PeerExchange:
+    """Peer-mapped exchange buffers for sequence_parallel_int8_attention(..., exchange=...): one buffer per rank in
+    symmetric memory (torch.distributed._symmetric_memory: every rank allocates the same size and the allocator maps
+    all of them into every process), laid out as include/int8kv_b200.h describes for int8kv_exchange.  Collective:
+    every rank of `group` must construct it, with the same shape.  Only plain peer stores are used on these buffers,
+    so the allocator's NVLink multicast binding is switched off for them."""
+
+    def __init__(self, batch: int, num_q_heads: int, head_dim: int, device, group=None):
+        import os
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.shape = (int(batch), int(num_q_heads), int(head_dim))
+        nbytes = _lib.load().int8kv_exchange_bytes(self.world, *self.shape)
+        if nbytes <= 0:
+            raise ValueError(f"no exchange layout for {self.world} ranks and shape {self.shape}")
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, group)
+        self.buffer.zero_()  # control words, flags and slabs start at zero on every rank ...
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # ... before anyone's first push can arrive
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        assert len(ptrs) == self.world and ptrs[self.rank] == self.buffer.data_ptr()
+        self.exchange = _lib.Exchange(self.world, self.rank, (_lib._VP * 16)(*ptrs), nbytes)
+        self._group = group
+
+    def close(self) -> None:
+        """Collective: every rank stops using the buffers before any of them lets go of its own."""
+        import torch.distributed as dist
+
+        if self.buffer is not None:
+            torch.cuda.synchronize(self.buffer.device)
+            dist.barrier(self._group)
+            self.exchange = self.handle = self.buffer = None
+
+
 def sequence_parallel_int8_attention(query, local_key_cache, local_value_cache, local_block_tables, local_seq_lens,
-                                     k_scale, v_scale, *, group=None, out_dtype=None, max_seq_len=None):
+                                     k_scale, v_scale, *, group=None, out_dtype=None, max_seq_len=None, exchange=None):
     """INT8 paged decode attention with the sequence split across the ranks of `group`.
 
     Every rank passes the full query [B, Hq, D], its own caches/block tables (local physical block ids) and
     the number of tokens of each sequence that it holds.  Returns the merged [B, Hq, D] on every rank.
+    exchange: a PeerExchange built for this batch and head layout; the partial rows then travel by peer stores and
+    flags instead of an NCCL all-gather (same result).
     """
     from . import ops
 
+    if exchange is not None:
+        B, Hq, D = query.shape
+        assert exchange.shape == (B, Hq, D)
+        ops.int8_paged_attention_partial_push(query, local_key_cache, local_value_cache, local_block_tables,
+                                              local_seq_lens, k_scale, v_scale, exchange.exchange,
+                                              max_seq_len=max_seq_len)
+        return ops.merge_exchanged(exchange.exchange, B, Hq, D, dtype=out_dtype or query.dtype, device=query.device)
     rows = ops.int8_paged_attention_partial(query, local_key_cache, local_value_cache, local_block_tables,
                                             local_seq_lens, k_scale, v_scale, max_seq_len=max_seq_len)
     gathered = gather_partials(rows, group)

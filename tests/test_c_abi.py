@@ -156,6 +156,22 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert layers_call(None, 2) == _lib.E_NULLPTR
     arr = (_lib.LayerArgs * 2)()  # all-null per-layer pointers: the first layer fails its own null check
     assert layers_call(arr, 2) == _lib.E_NULLPTR and failed.value == 0
+    # peer exchange: layout size, and descriptors that cannot be right are refused before anything is launched
+    rows = 32 * 64 * 132 * 4
+    assert lib.int8kv_exchange_bytes(8, 32, 64, 128) == 256 + rows * 17
+    assert lib.int8kv_exchange_bytes(17, 32, 64, 128) == -1 and lib.int8kv_exchange_bytes(0, 32, 64, 128) == -1
+    ex = _lib.Exchange(2, 0, (C.c_void_p * 16)(), 256 + 3 * 28 * 132 * 4 * 5)
+    merge = lambda e: lib.int8kv_merge_exchanged(C.byref(e), 3, 28, 128, None, 0, st3, None, 0, None)
+    assert merge(ex) == _lib.E_NULLPTR  # no buffers
+    ex.peer_buffers[0], ex.peer_buffers[1] = 4096, 8192 + 16
+    assert merge(ex) == _lib.E_WORKSPACE  # a buffer that is not 256-byte aligned
+    ex.peer_buffers[1] = 8192
+    assert merge(ex) == _lib.E_NULLPTR  # buffers fine, no output
+    ex.buffer_bytes -= 1
+    assert merge(ex) == _lib.E_WORKSPACE
+    ex.rank = 2
+    assert merge(ex) == _lib.E_BAD_SHAPE
+    assert lib.int8kv_merge_exchanged(None, 3, 28, 128, None, 0, st3, None, 0, None) == _lib.E_NULLPTR
     # the library's own workspace: its accessors refuse null destinations before touching the device
     assert lib.int8kv_static_ws_status(None, 0, None) == _lib.E_NULLPTR
     assert lib.int8kv_static_ws_address(None) == _lib.E_NULLPTR

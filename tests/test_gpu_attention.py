@@ -863,6 +863,8 @@ def test_vllm_call_sites_with_fake_engine_objects(kv, workloads):
             out2 = torch.zeros(4, 28, 128, dtype=torch.bfloat16, device=dev)
             stream = torch.cuda.Stream()
             with torch.cuda.stream(stream):
+                impl.forward(Layer(), padded_q, None, None, native, Meta(), out2)  # sizes this stream's workspace
+                stream.synchronize()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, stream=stream):
                     impl.forward(Layer(), padded_q, None, None, native, Meta(), out2)

@@ -1,6 +1,7 @@
 """Sequence-parallel INT8 attention on two GPUs: every rank holds a contiguous block range of every sequence
-in its own cache, computes partial rows, NCCL all-gathers them into local memory and merges locally.  The
-result must equal single-GPU attention over the whole sequence.  Skipped when fewer than two GPUs are visible.
+in its own cache, computes partial rows, brings the rows of all ranks into local memory (an NCCL all-gather, or
+peer stores with arrival flags) and merges locally.  The result must equal single-GPU attention over the whole
+sequence.  Skipped when fewer than two GPUs are visible.
 Also checks the collective-free KV-head x batch sharding on each rank against the oracle."""
 
 import os
@@ -57,6 +58,29 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         got = out.float().cpu()
         seq_err, seq_cos = max_abs(got, want.to(torch.bfloat16).float()), cosine(got, want)
+        # the same split with the rows exchanged by peer stores and arrival flags instead of the all-gather: several
+        # steps in a row (the buffers alternate between two slabs), then the same steps replayed as a CUDA graph
+        peer = sh.PeerExchange(len(lens), 28, 128, dev)
+        args = (case.query.to(dev), local_kc.to(dev), local_vc.to(dev), local_tables.to(dev),
+                torch.tensor(local_lens, dtype=torch.int32, device=dev), case.k_scale.to(dev), case.v_scale.to(dev))
+        for _ in range(3):
+            out_p = sh.sequence_parallel_int8_attention(*args, exchange=peer, max_seq_len=max(max(local_lens), 1))
+        torch.cuda.synchronize()
+        peer_equal = bool(torch.equal(out_p, out))
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            sh.sequence_parallel_int8_attention(*args, exchange=peer, max_seq_len=max(max(local_lens), 1))
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                out_g = sh.sequence_parallel_int8_attention(*args, exchange=peer, max_seq_len=max(max(local_lens), 1))
+            for _ in range(3):
+                out_g.zero_()
+                g.replay()
+            stream.synchronize()
+        peer_equal = peer_equal and bool(torch.equal(out_g, out))
+        del g
+        peer.close()
 
         # --- head x batch shard of this rank, no collective
         shard = sh.head_batch_partition(world, 28, 4, len(lens))[rank]
@@ -67,7 +91,7 @@ def _worker(rank, world, port, ret):
         b0, b1 = shard.batch
         ref = want[b0:b1, q0:q1]
         ret[rank] = (seq_err, seq_cos, max_abs(part, ref.to(torch.bfloat16).float()), cosine(part, ref),
-                     int(kv.device_status(dev)))
+                     int(kv.device_status(dev)), peer_equal)
     finally:
         dist.destroy_process_group()
 
@@ -86,7 +110,8 @@ def test_two_gpu_sequence_split_and_head_shards_match_the_oracle():
             p.join(240)
             assert p.exitcode == 0
         assert len(ret) == world
-        for seq_err, seq_cos, shard_err, shard_cos, status in ret.values():
+        for seq_err, seq_cos, shard_err, shard_cos, status, peer_equal in ret.values():
             assert seq_err <= 2e-2 and seq_cos >= 0.9999
             assert shard_err <= 2e-2 and shard_cos >= 0.9999
             assert status == 0
+            assert peer_equal  # the two exchanges deliver the same rows to the same merge: bit-identical outputs
