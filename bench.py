@@ -89,7 +89,9 @@ def build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed, with_bf16=Fals
     """Per layer: INT8 caches filled through the product write kernel from seeded bf16 K/V draws (and, with
     `with_bf16`, bf16 caches holding the same un-quantised rows at the same slots).  `seed` drives the K/V draws
     and the block placement; `common_seed` (default: seed) drives what ranks of one job must agree on: the static
-    scales, the outlier channels and the queries."""
+    scales, the outlier channels and the queries.  All layers share one block table and one seq_lens tensor, as
+    the layers of a model do in a serving engine (a sequence's block ids are the same in every layer's cache); the
+    caches themselves are distinct allocations with distinct contents."""
     common_seed = seed if common_seed is None else common_seed
     shape = wl.LayerShape(hq, hkv, 128, 16)
     B = len(seq_lens)
@@ -104,18 +106,18 @@ def build_layers(kv, wl, device, hq, hkv, seq_lens, layers, seed, with_bf16=Fals
     gen = torch.Generator(device=device)
     qgen = torch.Generator(device=device)
     gain = wl.channel_gain(shape, common_seed, device)
+    block_tables = wl.permuted_block_tables(seq_lens, 16, num_blocks, seed).to(device)
+    seq_lens_dev = torch.tensor(seq_lens, dtype=torch.int32, device=device)
+    slots = block_tables[seq_of_tok, pos // 16].long() * 16 + pos % 16
     for li in range(layers):
         L = Layer()
         L.k_scale, L.v_scale = [t.to(device) for t in wl.calibrate_scales(shape, common_seed, li)]
-        tables = wl.permuted_block_tables(seq_lens, 16, num_blocks, seed + 13 * li)
-        L.block_tables = tables.to(device)
-        L.seq_lens = torch.tensor(seq_lens, dtype=torch.int32, device=device)
+        L.block_tables, L.seq_lens = block_tables, seq_lens_dev
         L.kc = torch.zeros(num_blocks, 16, hkv, 128, dtype=torch.int8, device=device)
         L.vc = torch.zeros_like(L.kc)
         if with_bf16:
             L.kb = torch.zeros(num_blocks, 16, hkv, 128, dtype=torch.bfloat16, device=device)
             L.vb = torch.zeros_like(L.kb)
-        slots = L.block_tables[seq_of_tok, pos // 16].long() * 16 + pos % 16
         gen.manual_seed(seed * 1000003 + li)
         for t0 in range(0, slots.numel(), chunk):
             s = slots[t0:t0 + chunk]
@@ -457,6 +459,50 @@ def leg_cache_write(ctx):
     }
 
 
+def layered_steps(ctx, layers_data, max_seq, num_splits=None, bf16=False):
+    """The step function of a device-timed leg: all layers of `layers_data` (INT8 caches, or their bf16 twins).
+    --launch chained (default): one DecodeStepLayers call with the inputs-ready promise, i.e. one launch per layer,
+    each carrying the previous layer's split-KV merge; per-call: one operator call per layer, each with the promise;
+    ordered: one operator call per layer, fully ordered behind the previous one."""
+    kv, mode = ctx.kv, ctx.args.launch
+    L0 = layers_data[0]
+    outs = torch.empty((len(layers_data),) + tuple(L0.query.shape), dtype=L0.query.dtype, device=L0.query.device)
+    for i, L in enumerate(layers_data):
+        L.out = outs[i]
+    if mode == "chained":
+        with torch.cuda.stream(ctx.stream):
+            if bf16:
+                plan = kv.DecodeStepLayers([L.query for L in layers_data], None, None, [L.kb for L in layers_data],
+                                           [L.vb for L in layers_data], None, L0.block_tables, L0.seq_lens, None, None,
+                                           max_seq_len=max_seq, num_splits=num_splits, out=outs, inputs_ready=True)
+            else:
+                plan = kv.DecodeStepLayers([L.query for L in layers_data], None, None, [L.kc for L in layers_data],
+                                           [L.vc for L in layers_data], None, L0.block_tables, L0.seq_lens,
+                                           [L.k_scale for L in layers_data], [L.v_scale for L in layers_data],
+                                           max_seq_len=max_seq, num_splits=num_splits, out=outs, inputs_ready=True)
+        return plan
+    ready = mode == "per-call"
+
+    def step():
+        for L in layers_data:
+            if bf16:
+                kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens, num_splits=num_splits,
+                                        max_seq_len=max_seq, out=L.out, inputs_ready=ready)
+            else:
+                kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
+                                        num_splits=num_splits, max_seq_len=max_seq, out=L.out, inputs_ready=ready)
+
+    return step
+
+
+LAUNCH_MODES = {
+    "chained": "all layers of a step behind one int8kv_decode_step_layers call with the inputs-ready promise: one launch "
+               "per layer, each carrying the previous layer's split-KV merge (INT8 and BF16 alike)",
+    "per-call": "one operator call per layer, each with the inputs-ready promise (INT8KV_FLAG_INPUTS_READY)",
+    "ordered": "one operator call per layer, every call fully ordered behind the previous one",
+}
+
+
 def leg_shape(ctx, spec: str):
     """int8_paged_attention on one layer of an arbitrary shape, "--shape Hq,Hkv,D,block[,batch,seq]": the layers outside
     the headline workloads (all of them head_dim 128), which the library serves with its non-tiled kernels.  The
@@ -497,7 +543,7 @@ def leg_sweep(ctx, variants=True):
     over enough distinct layer caches to exceed the L2."""
     kv, wl, device = ctx.kv, ctx.wl, ctx.device
     hq, hkv = wl.QWEN25_7B.num_q_heads, wl.QWEN25_7B.num_kv_heads
-    ready = not ctx.args.ordered  # every input of a step is resident before the step starts
+    ready = ctx.args.launch != "ordered"  # every input of a step is resident before the step starts
     cells = []
     for B in (1, 2, 4, 8):
         for seq in (512, 1024, 2048, 4096):
@@ -505,24 +551,19 @@ def leg_sweep(ctx, variants=True):
             layers = 28 if (B, seq) == (8, 4096) else max(4, min(64, int(600e6 / cell_bytes)))
             L = build_layers(kv, wl, device, hq, hkv, [seq] * B, layers, seed=5, with_bf16=True)
 
-            def int8_step(**kw):
+            def int8_variant(**kw):  # the reference's other table columns, one operator call per layer
                 for x in L:
                     kv.int8_paged_attention(x.query, x.kc, x.vc, x.block_tables, x.seq_lens, x.k_scale, x.v_scale,
                                             max_seq_len=seq, out=x.out, inputs_ready=ready, **kw)
 
-            def bf16_step():
-                for x in L:
-                    kv.bf16_paged_attention(x.query, x.kb, x.vb, x.block_tables, x.seq_lens, max_seq_len=seq, out=x.out,
-                                            inputs_ready=ready)
-
-            i8 = ctx.time_device(int8_step) / layers * 1e3
-            bf = ctx.time_device(bf16_step) / layers * 1e3
+            i8 = ctx.time_device(layered_steps(ctx, L, seq)) / layers * 1e3
+            bf = ctx.time_device(layered_steps(ctx, L, seq, bf16=True)) / layers * 1e3
             nb = algorithmic_bytes([seq] * B, hq, hkv)
             cell = {"batch": B, "seq_len": seq, "layer_caches": layers, "int8_us": i8, "bf16_us": bf,
                     "int8_speedup": bf / i8, "int8_gbs": nb / i8 / 1e3}
             if variants:
-                cell["int8_quantize_q_us"] = ctx.time_device(lambda: int8_step(quantize_q=True)) / layers * 1e3
-                cell["int8_split8_us"] = ctx.time_device(lambda: int8_step(num_splits=8)) / layers * 1e3
+                cell["int8_quantize_q_us"] = ctx.time_device(lambda: int8_variant(quantize_q=True)) / layers * 1e3
+                cell["int8_split8_us"] = ctx.time_device(lambda: int8_variant(num_splits=8)) / layers * 1e3
             cells.append(cell)
             del L
             _release()
@@ -534,14 +575,15 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
     INT8 attention, the BF16 baseline, the host-to-host leg and the oracle check.  Returns the JSON line's body
     (on every rank; only rank 0's is printed)."""
     kv, wl, args, device, world, rank = ctx.kv, ctx.wl, ctx.args, ctx.device, ctx.world, ctx.rank
-    if world > 1:
-        shard = ctx.sh.head_batch_partition(world, hq, hkv, len(seq_lens))[rank]
+    parts = world if world > 1 else (args.one_shard_of or 1)
+    if parts > 1:
+        shard = ctx.sh.head_batch_partition(parts, hq, hkv, len(seq_lens))[rank]
         group = hq // hkv
         hkv = shard.kv_heads[1] - shard.kv_heads[0]
         hq = hkv * group
         seq_lens = seq_lens[shard.batch[0]:shard.batch[1]]
-        config["parallelism"] = (f"KV-head x batch sharded over {world} ranks, no collective: {hkv} KV head(s) x "
-                                 f"{len(seq_lens)} sequences per rank")
+        config["parallelism"] = (f"KV-head x batch sharded over {parts} ranks, no collective: {hkv} KV head(s) x "
+                                 f"{len(seq_lens)} sequences per rank" + ("" if world > 1 else " (one rank's shard alone, on one GPU)"))
         config["batch_per_gpu"], config["kv_heads_per_gpu"] = len(seq_lens), hkv
     dynamic = args.scales == "dynamic"
     want_bf16 = args.bf16_baseline and not dynamic
@@ -561,25 +603,22 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
             L.vsc = torch.rand(L.kc.shape[:3], device=device, generator=gen_s) * 0.02 + 0.005
     nbytes_step = nbytes_call * layers
     # Every input of a step (queries, caches, tables, lengths, scales) is resident before the step starts and no
-    # layer reads what another writes, so the calls carry the inputs-ready promise: each may start streaming its
-    # pages while the previous call's split-KV merge finishes.  --ordered turns the promise off.
-    ready = not args.ordered
-    config["call_ordering"] = ("inputs-ready promise (INT8KV_FLAG_INPUTS_READY) on every call, INT8 and BF16 alike"
-                               if ready else "every call fully ordered behind the previous one")
-
-    def device_step():
-        for L in layers_data:
-            if dynamic:
+    # layer reads what another writes, which is what the inputs-ready promise asks for; see LAUNCH_MODES.
+    ready = args.launch != "ordered"
+    config["launch"] = f"{args.launch}: {LAUNCH_MODES[args.launch]}"
+    if dynamic:
+        def device_step():
+            for L in layers_data:
                 kv.int8_paged_attention_dynamic(L.query, L.kc, L.vc, L.ksc, L.vsc, L.block_tables, L.seq_lens,
                                                 num_splits=args.num_splits, max_seq_len=max_seq, out=L.out,
                                                 inputs_ready=ready)
-            else:
-                kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
-                                        num_splits=args.num_splits, max_seq_len=max_seq, out=L.out, inputs_ready=ready)
+    else:
+        device_step = layered_steps(ctx, layers_data, max_seq, args.num_splits)
 
     lib = kv._lib.load()
     splits = args.num_splits or lib.int8kv_choose_splits(B, hkv, max_seq, 16, ctx.sm)
     launches_per_call = 1 + (1 if splits > 1 else 0)
+    chained = args.launch == "chained" and not dynamic and layers > 1
     split_plan = None
     with torch.cuda.stream(ctx.stream):
         device_step()
@@ -619,11 +658,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
     # ---- same-run BF16 baseline on identical block tables and the same K/V rows (one step = the same calls) ----
     bf16_ms = float("nan")
     if want_bf16:
-        def bf16_step():
-            for L in layers_data:
-                kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens, max_seq_len=max_seq, out=L.out,
-                                        inputs_ready=ready)
-
+        bf16_step = layered_steps(ctx, layers_data, max_seq, args.num_splits, bf16=True)
         bf16_ms = ctx.time_device(bf16_step)
         for L in layers_data:
             del L.kb, L.vb
@@ -766,7 +801,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         "tokens_layers_per_s": total_token_layers / (dev_ms * 1e-3),
         "frac_of_8TBps": value / world / HBM_NOMINAL_GBS,
         "num_splits": splits, "split_plan": split_plan,
-        "gpu_launches": launches_per_call * layers * args.steps,
+        "gpu_launches": ((layers + (1 if launches_per_call > 1 else 0)) if chained else launches_per_call * layers) * args.steps,
         "clocks": clocks, "device_status": int(status), "shard_check": check,
         "e2e": {"value": total_step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": int(h2d_all), "d2h_bytes_per_step": int(d2h_all),
@@ -891,14 +926,17 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg (profiling runs)")
     ap.add_argument("--no-bf16", dest="bf16_baseline", action="store_false", help="skip the same-run BF16 baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--ordered", action="store_true",
-                    help="do not pass the inputs-ready promise: every call waits for the previous one to finish")
+    ap.add_argument("--launch", default="chained", choices=sorted(LAUNCH_MODES),
+                    help="how the layers of a device-timed step are launched: " + "; ".join(f"{k} = {v}" for k, v in LAUNCH_MODES.items()))
     ap.add_argument("--scales", default="static", choices=["static", "dynamic"],
                     help="dynamic: time the attention over per-(token, head) scale caches (device leg only)")
     ap.add_argument("--sweep", action="store_true",
                     help="c2 only, one GPU: time all 16 cells of the sweep and list them under `cells`")
     ap.add_argument("--shape", default=None, metavar="Hq,Hkv,D,BLOCK[,BATCH,SEQ]",
                     help="time int8_paged_attention on one layer of any shape (one GPU) and print that record alone")
+    ap.add_argument("--one-shard-of", type=int, default=None, metavar="N",
+                    help="one GPU: run rank 0's shard of an N-way KV-head x batch partition alone (what one rank of an "
+                         "N-GPU job computes); the printed value covers that shard only")
     ap.add_argument("--batch", type=int, default=None, help="use only the first BATCH sequences of the workload")
     ap.add_argument("--layers", type=int, default=None, help="override the number of distinct layer caches")
     args = ap.parse_args()

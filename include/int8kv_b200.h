@@ -224,8 +224,13 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype,
  * then holds its index, else -1.
  * flags: with INT8KV_FLAG_INPUTS_READY the promise is about the layers of this call: no layer reads what an earlier
  * layer of the call writes (all queries and new rows were produced before the call, every layer has its own cache
- * and output).  Layers after the first then overlap the previous layer's merge; the first layer orders itself behind
- * whatever precedes the call in the ordinary way.
+ * and output).  The first layer orders itself behind whatever precedes the call in the ordinary way; the layers
+ * after it are CHAINED when the workspace holds at least twice what one layer needs (and starts on a 256-byte
+ * boundary): layer l works in half l % 2 of the workspace, and its split-KV merge is not a launch of its own but
+ * rides, as extra thread blocks, on the launch of layer l + 1, whose page stream starts while layer l is still
+ * draining.  A step is then one launch per layer plus one closing merge; layer l's output is complete when layer
+ * l + 1's launch is (all outputs when the call's work on the stream is).  Results are identical to unchained calls.
+ * With a smaller workspace the layers still overlap their predecessor's merge, as single calls with the flag do.
  */
 typedef struct int8kv_layer_args {
   const void* query;      /* [batch, Hq, D] */
@@ -242,6 +247,23 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
                               int kv_dtype, const int64_t key_strides[3], const int64_t value_strides[3],
                               const void* slot_mapping, int slot_is_i64,
                               int q_dtype, const int64_t q_strides[3],
+                              int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                              const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
+                              int64_t num_blocks, int block_size,
+                              const void* block_tables, int bt_is_i64, const int64_t bt_strides[2], int64_t bt_width,
+                              const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                              int out_dtype, const int64_t out_strides[3],
+                              int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream);
+
+/*
+ * The BF16/FP16 baseline for `num_layers` layers in one call: int8kv_paged_attn_bf16 once per entry of `layers`
+ * (query, out, key_cache, value_cache; key, value and the scales must be NULL), sharing shapes, tables and the
+ * workspace, with the same chaining under INT8KV_FLAG_INPUTS_READY as int8kv_decode_step_layers, so that the
+ * baseline can be timed under the conditions of the INT8 path.  The reference's baseline is one call per layer
+ * (src/triton_ops/bf16_paged_attention.py:118-165).
+ */
+int int8kv_paged_attn_bf16_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer,
+                              int cache_dtype, int q_dtype, const int64_t q_strides[3],
                               int batch, int num_q_heads, int num_kv_heads, int head_dim,
                               const int64_t key_cache_strides[4], const int64_t value_cache_strides[4],
                               int64_t num_blocks, int block_size,

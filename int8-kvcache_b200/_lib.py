@@ -111,6 +111,13 @@ _SIGNATURES = {
          _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, C.c_int, _I64P,
          C.c_int, _VP, C.c_int64, C.c_int, _VP],
     ),
+    "int8kv_paged_attn_bf16_layers": (
+        C.c_int,
+        [C.POINTER(LayerArgs), C.c_int, C.POINTER(C.c_int), C.c_int, C.c_int, _I64P,
+         C.c_int, C.c_int, C.c_int, C.c_int, _I64P, _I64P, C.c_int64, C.c_int,
+         _VP, C.c_int, _I64P, C.c_int64, _VP, C.c_int, C.c_int64, C.c_int, _I64P,
+         C.c_int, _VP, C.c_int64, C.c_int, _VP],
+    ),
     "int8kv_static_ws_status": (C.c_int, [_VP, C.c_int, _VP]),
     "int8kv_static_ws_address": (C.c_int, [C.POINTER(_VP)]),
     "int8kv_exchange_bytes": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int]),

@@ -86,7 +86,13 @@ static int64_t pow2_floor(int64_t x) {
   return p;
 }
 
-int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
+// `chained`: the call is one layer of a chained sequence (run_layers), where consecutive layers overlap and what
+// counts is the period of a layer, not the latency of one call.  A layer's merge is the one piece of a chained layer
+// that cannot overlap the merge of the layer before it, and it costs one round trip to the L2 per 16 parts, so the
+// latency-driven count is capped at 16 parts (measured on the 8 x 4096-token cell, per layer: 32 parts 11.1 us, of
+// which the second round trip of the merge is about 2 us) and the rule that cuts the smallest calls into more,
+// shorter parts is left out.
+int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count, bool chained = false) {
   (void)block_size;
   if (B <= 0 || Hkv <= 0 || max_seq <= 0) return 1;
   const int64_t tiles = (max_seq + 15) / 16;
@@ -98,11 +104,12 @@ int choose_splits(int B, int Hkv, int64_t max_seq, int block_size, int sm_count)
   //  * large calls are bound by HBM, where ragged batches balance best with about four waves of warps, but a part
   //    of fewer than 32 tiles would spend too much of its traffic on its partial rows.
   const int64_t slots = static_cast<int64_t>(sm_count) * 12;
-  const int64_t by_latency = std::min<int64_t>(tiles / 2, std::max<int64_t>(16, tiles / 8));
+  const int64_t by_latency = chained ? std::min<int64_t>(tiles / 2, 16)
+                                     : std::min<int64_t>(tiles / 2, std::max<int64_t>(16, tiles / 8));
   int64_t s_fill = std::min(pow2_floor(std::max<int64_t>(1, slots / items)), pow2_floor(std::max<int64_t>(1, by_latency)));
   // the smallest calls (512 warps or fewer in total) still gain from parts of only 4 tiles
   const int64_t s_quarter = std::min<int64_t>(pow2_floor(std::max<int64_t>(1, tiles / 4)), kMaxSplits);
-  if (s_quarter > s_fill && items * s_quarter <= 512) s_fill = s_quarter;
+  if (!chained && s_quarter > s_fill && items * s_quarter <= 512) s_fill = s_quarter;
   int64_t s_bw = 1;
   while (s_bw * items < slots * 4) s_bw *= 2;
   s_bw = std::min(s_bw, pow2_floor(std::max<int64_t>(1, tiles / 32)));
@@ -220,76 +227,118 @@ struct AttnCall {
   // dynamic per-(token, head) scales (null ks_cache = static scales)
   const float* ks_cache = nullptr; const float* vs_cache = nullptr;
   const int64_t* ks_st = nullptr; const int64_t* vs_st = nullptr;
+  // device status word to use instead of the one at the end of `ws` (a call that works in a part of a larger workspace)
+  unsigned int* status = nullptr;
+  bool chained = false;  // one layer of a chained sequence: the automatic split count favours throughput
 };
 
-int run_attention(const AttnCall& a) {
+// What a call will do, decided from its arguments alone (no launch, no device access beyond the SM count).
+struct AttnPlan {
+  int G, sm, S, rf, esz;
+  int64_t max_seq, tiles, need;
+  bool tiled, planned, dyn;
+  int quantize_q;
+  PlanShape ps;
+  PlanLayout pl;
+};
+
+int plan_attention(const AttnCall& a, AttnPlan& t) {
   if (a.B < 0 || a.Hq <= 0 || a.Hkv <= 0 || a.D <= 0 || a.block_size <= 0 || a.num_blocks < 0 || a.bt_width < 0)
     return INT8KV_E_BAD_SHAPE;
   if (a.Hq % a.Hkv != 0) return INT8KV_E_BAD_SHAPE;
   if (a.num_splits < INT8KV_SPLITS_PLANNED || a.num_splits > kMaxSplits) return INT8KV_E_BAD_SHAPE;
   if (a.flags & ~(INT8KV_FLAG_QUANTIZE_Q | INT8KV_FLAG_INPUTS_READY)) return INT8KV_E_BAD_SHAPE;
-  const int quantize_q = (a.flags & INT8KV_FLAG_QUANTIZE_Q) ? 1 : 0;
-  if (quantize_q && (a.cache_kind != kCacheInt8 || a.ks_cache != nullptr || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
+  t.quantize_q = (a.flags & INT8KV_FLAG_QUANTIZE_Q) ? 1 : 0;
+  if (t.quantize_q && (a.cache_kind != kCacheInt8 || a.ks_cache != nullptr || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
   if (!valid_float_dtype(a.q_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.partial_out == nullptr && !valid_float_dtype(a.out_dtype)) return INT8KV_E_BAD_DTYPE;
   if (a.B == 0) return INT8KV_OK;
   if (!a.query || !a.kc || !a.vc || !a.bt || !a.sl || !a.q_st || !a.kc_st || !a.vc_st || !a.bt_st)
     return INT8KV_E_NULLPTR;
   if (a.partial_out == nullptr && (!a.out || !a.o_st)) return INT8KV_E_NULLPTR;
-  const bool dyn = a.ks_cache != nullptr || a.vs_cache != nullptr;
-  if (dyn && (!a.ks_cache || !a.vs_cache || !a.ks_st || !a.vs_st)) return INT8KV_E_NULLPTR;
-  if (dyn && (a.cache_kind != kCacheInt8 || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
-  if (a.cache_kind == kCacheInt8 && !dyn && (!a.k_scale || !a.v_scale)) return INT8KV_E_NULLPTR;
+  t.dyn = a.ks_cache != nullptr || a.vs_cache != nullptr;
+  if (t.dyn && (!a.ks_cache || !a.vs_cache || !a.ks_st || !a.vs_st)) return INT8KV_E_NULLPTR;
+  if (t.dyn && (a.cache_kind != kCacheInt8 || a.new_k != nullptr)) return INT8KV_E_UNSUPPORTED;
+  if (a.cache_kind == kCacheInt8 && !t.dyn && (!a.k_scale || !a.v_scale)) return INT8KV_E_NULLPTR;
   if (a.kc_st[3] != 1 || a.vc_st[3] != 1) return INT8KV_E_UNSUPPORTED;  // the reference asserts unit last stride too
 
-  const int G = a.Hq / a.Hkv;
-  const int sm = device_sm_count();
-  int64_t max_seq = a.max_seq_hint > 0 ? a.max_seq_hint : a.bt_width * a.block_size;
-  if (max_seq > a.bt_width * a.block_size) max_seq = a.bt_width * a.block_size;
-  int S = a.num_splits > 0 ? a.num_splits : choose_splits(a.B, a.Hkv, max_seq, a.block_size, sm);
+  t.G = a.Hq / a.Hkv;
+  t.sm = device_sm_count();
+  t.max_seq = a.max_seq_hint > 0 ? a.max_seq_hint : a.bt_width * a.block_size;
+  if (t.max_seq > a.bt_width * a.block_size) t.max_seq = a.bt_width * a.block_size;
+  t.S = a.num_splits > 0 ? a.num_splits : choose_splits(a.B, a.Hkv, t.max_seq, a.block_size, t.sm, a.chained);
   // more splits than 16-token tiles only produces empty parts
-  const int64_t tiles = (max_seq + 15) / 16;
-  if (S > tiles) S = tiles > 0 ? static_cast<int>(tiles) : 1;
+  t.tiles = (t.max_seq + 15) / 16;
+  if (t.S > t.tiles) t.S = t.tiles > 0 ? static_cast<int>(t.tiles) : 1;
 
-  const int rf = partial_row_floats(a.D);
-  const int esz = a.cache_kind == kCacheInt8 ? 1 : 2;
-  const bool tiled = a.D == 128 && (a.block_size % 16) == 0 && G <= 8 && a.num_blocks > 0 &&
-                     tma_friendly(a.kc, esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, esz, a.vc_st, a.num_blocks) &&
-                     (rf % 4 == 0);
-  if (!tiled && a.num_splits == 0) {
+  t.rf = partial_row_floats(a.D);
+  t.esz = a.cache_kind == kCacheInt8 ? 1 : 2;
+  t.tiled = a.D == 128 && (a.block_size % 16) == 0 && t.G <= 8 && a.num_blocks > 0 &&
+            tma_friendly(a.kc, t.esz, a.kc_st, a.num_blocks) && tma_friendly(a.vc, t.esz, a.vc_st, a.num_blocks) &&
+            (t.rf % 4 == 0);
+  if (!t.tiled && a.num_splits == 0) {
     // the automatic count above is fitted to the tiled kernels; use the untiled one if the workspace allows it
-    int su = untiled_splits(a.B, a.Hq, a.Hkv, a.D, a.cache_kind == kCacheInt8, max_seq, sm);
-    if (su > tiles) su = tiles > 0 ? static_cast<int>(tiles) : 1;
-    if (su <= 1 || (a.ws != nullptr && a.ws_bytes >= ws_bytes(a.B, a.Hq, a.D, su))) S = su;
+    int su = untiled_splits(a.B, a.Hq, a.Hkv, a.D, a.cache_kind == kCacheInt8, t.max_seq, t.sm);
+    if (su > t.tiles) su = t.tiles > 0 ? static_cast<int>(t.tiles) : 1;
+    if (su <= 1 || (a.ws != nullptr && a.ws_bytes >= ws_bytes(a.B, a.Hq, a.D, su))) t.S = su;
   }
   // Device-planned splits: asked for explicitly, or chosen for a large automatic call when the workspace has
   // room for the plan (callers that sized it with int8kv_workspace_bytes_auto always have).
-  bool planned = false;
-  PlanShape ps{};
-  PlanLayout pl{};
-  if (a.num_splits <= 0 && tiled && tiles > 0 &&
+  t.planned = false;
+  if (a.num_splits <= 0 && t.tiled && t.tiles > 0 &&
       a.bt_width * a.block_size < (int64_t(1) << 21) * 16 &&  // tile counts stay exact in fp32 on the device
-      (a.num_splits == INT8KV_SPLITS_PLANNED ? plan_possible(a.B, a.Hkv, sm)
-                                              : plan_pays(a.B, a.Hkv, max_seq, a.block_size, sm))) {
-    ps = plan_shape(a.B, a.Hkv, tiles, sm);
-    pl = plan_layout(a.B, a.Hq, a.Hkv, a.D, ps.max_items);
+      (a.num_splits == INT8KV_SPLITS_PLANNED ? plan_possible(a.B, a.Hkv, t.sm)
+                                              : plan_pays(a.B, a.Hkv, t.max_seq, a.block_size, t.sm))) {
+    t.ps = plan_shape(a.B, a.Hkv, t.tiles, t.sm);
+    t.pl = plan_layout(a.B, a.Hq, a.Hkv, a.D, t.ps.max_items);
     // the plan's header sits in the 16 bytes before the status word, wherever the workspace ends
-    planned = a.ws != nullptr && a.ws_bytes >= pl.total && (reinterpret_cast<uintptr_t>(a.ws) & 15u) == 0 &&
-              pl.header_off + 16 <= int8kv_workspace_status_offset(a.ws_bytes);
-    if (planned) pl.header_off = int8kv_workspace_status_offset(a.ws_bytes) - 16;
-    if (!planned && a.num_splits == INT8KV_SPLITS_PLANNED) return INT8KV_E_WORKSPACE;
+    t.planned = a.ws != nullptr && a.ws_bytes >= t.pl.total && (reinterpret_cast<uintptr_t>(a.ws) & 15u) == 0 &&
+                t.pl.header_off + 16 <= int8kv_workspace_status_offset(a.ws_bytes);
+    if (t.planned) t.pl.header_off = int8kv_workspace_status_offset(a.ws_bytes) - 16;
+    if (!t.planned && a.num_splits == INT8KV_SPLITS_PLANNED) return INT8KV_E_WORKSPACE;
   } else if (a.num_splits == INT8KV_SPLITS_PLANNED) {
     return INT8KV_E_UNSUPPORTED;
   }
-  if (planned) S = kMaxSplits;  // upper bound of the parts of one sequence; the real count is in the plan
-  const int64_t need = planned ? pl.total : ws_bytes(a.B, a.Hq, a.D, S);
-  unsigned int* status = nullptr;
-  if (a.ws != nullptr && a.ws_bytes >= 16)
-    status = reinterpret_cast<unsigned int*>(static_cast<char*>(a.ws) + int8kv_workspace_status_offset(a.ws_bytes));
-  if (S > 1) {
-    if (a.ws == nullptr || a.ws_bytes < need) return INT8KV_E_WORKSPACE;
+  if (t.planned) t.S = kMaxSplits;  // upper bound of the parts of one sequence; the real count is in the plan
+  t.need = t.planned ? t.pl.total : ws_bytes(a.B, a.Hq, a.D, t.S);
+  if (t.S > 1) {
+    if (a.ws == nullptr || a.ws_bytes < t.need) return INT8KV_E_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(a.ws) & 15u) return INT8KV_E_WORKSPACE;
   }
+  if (a.new_k != nullptr && !(t.tiled && a.cache_kind == kCacheInt8)) return INT8KV_E_UNSUPPORTED;
+  if (!t.tiled && a.cache_kind != kCacheInt8 && t.quantize_q) return INT8KV_E_UNSUPPORTED;
+  return INT8KV_OK;
+}
+
+// A sequence of layer calls whose split-KV merges ride on the NEXT layer's attention launch (chained layers): the
+// merge of layer l runs in extra CTAs of layer l+1's launch, beside that layer's page stream, instead of in a launch
+// of its own between the two.  Possible when the caller promised that the layers are independent (the outputs of
+// layer l are not inputs of layer l+1) and every layer has its own half of the workspace.
+struct Chain {
+  bool active = false;    // merges may be deferred to the next launch
+  bool pending = false;   // `merge` has not been launched or carried yet
+  MergeParams merge;
+};
+
+int flush_chain(Chain* chain, cudaStream_t stream) {
+  if (chain == nullptr || !chain->pending) return INT8KV_OK;
+  chain->pending = false;
+  return launch_merge(chain->merge, stream);
+}
+
+int run_attention(const AttnCall& a, Chain* chain = nullptr) {
+  AttnPlan t;
+  std::memset(&t, 0, sizeof(t));
+  const int checked = plan_attention(a, t);
+  if (checked != INT8KV_OK || a.B == 0) return checked;
+  const int G = t.G, sm = t.sm, S = t.S, rf = t.rf, esz = t.esz;
+  const int64_t tiles = t.tiles;
+  const bool tiled = t.tiled, planned = t.planned, dyn = t.dyn;
+  const PlanShape& ps = t.ps;
+  const PlanLayout& pl = t.pl;
+  unsigned int* status = a.status;
+  if (status == nullptr && a.ws != nullptr && a.ws_bytes >= 16)
+    status = reinterpret_cast<unsigned int*>(static_cast<char*>(a.ws) + int8kv_workspace_status_offset(a.ws_bytes));
 
   AttnParams p;
   std::memset(&p, 0, sizeof(p));
@@ -309,14 +358,13 @@ int run_attention(const AttnCall& a) {
   p.num_splits = S;
   p.per_longest = static_cast<int>(std::max<int64_t>(1, (tiles + S - 1) / S));
   p.row_floats = rf;
-  p.quantize_q = quantize_q;
+  p.quantize_q = t.quantize_q;
   p.defer_wait = (a.flags & INT8KV_FLAG_INPUTS_READY) ? 1 : 0;
   p.sm_scale_log2 = static_cast<float>(1.4426950408889634 / std::sqrt(static_cast<double>(a.D)));
   p.status = status;
   if (S > 1) p.part = reinterpret_cast<float*>(a.ws);
   else p.part = a.partial_out;  // null for the ordinary call: write `out` directly
 
-  if (a.new_k != nullptr && !(tiled && a.cache_kind == kCacheInt8)) return INT8KV_E_UNSUPPORTED;  // nothing launched yet
   if (dyn) {
     p.ks_cache = a.ks_cache; p.vs_cache = a.vs_cache;
     for (int i = 0; i < 3; ++i) { p.ks_st[i] = a.ks_st[i]; p.vs_st[i] = a.vs_st[i]; }
@@ -337,13 +385,22 @@ int run_attention(const AttnCall& a) {
     p.plan_min_part = ps.min_part;
     p.direct_part = a.partial_out;
   }
+  // A merge left over from the previous layer rides on this launch when this launch can carry it (tiled kernels,
+  // static scales, plain query); otherwise it gets its own launch first.
+  const bool carry = chain != nullptr && chain->pending && tiled && !dyn && !t.quantize_q;
+  if (chain != nullptr && chain->pending && !carry) {
+    rc = flush_chain(chain, a.stream);
+    if (rc != INT8KV_OK) return rc;
+  }
   if (tiled) {
     alignas(64) CUtensorMap tmK, tmV;
     if (!make_cache_map(&tmK, a.kc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.kc_st) ||
         !make_cache_map(&tmV, a.vc, esz, a.D, a.Hkv, a.num_blocks, a.block_size, a.vc_st))
       return INT8KV_E_LAUNCH;
-    rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, sm, a.stream)
-                                    : launch_attn_tiled_f16(p, tmK, tmV, sm, a.stream);
+    const MergeParams* prev = carry ? &chain->merge : nullptr;
+    rc = a.cache_kind == kCacheInt8 ? launch_attn_tiled_int8(p, tmK, tmV, sm, a.stream, prev)
+                                    : launch_attn_tiled_f16(p, tmK, tmV, sm, a.stream, prev);
+    if (carry && rc == INT8KV_OK) chain->pending = false;
   } else {
     rc = launch_attn_generic(p, a.stream);
   }
@@ -357,6 +414,11 @@ int run_attention(const AttnCall& a) {
   m.part_out = a.partial_out;
   m.inputs_ready = p.defer_wait;
   if (planned) m.seq_table = reinterpret_cast<const int2*>(static_cast<char*>(a.ws) + pl.table_off);
+  if (chain != nullptr && chain->active && tiled && a.partial_out == nullptr) {
+    chain->merge = m;  // the next layer's launch carries it (or flush_chain launches it)
+    chain->pending = true;
+    return INT8KV_OK;
+  }
   return launch_merge(m, a.stream);
 }
 
@@ -677,6 +739,102 @@ int int8kv_decode_step(const void* key, const void* value, int kv_dtype, const i
                                 workspace, workspace_bytes, flags & ~INT8KV_FLAG_INPUTS_READY, stream);
 }
 
+}  // extern "C"
+
+namespace {
+
+// The layers of one model step, INT8 caches (with or without the step's cache write) or float caches (attention
+// only), behind one call.  With the inputs-ready promise and a workspace of at least twice one layer's need, the
+// layers are CHAINED: layer l works in half l % 2 of the workspace and its split-KV merge is carried by the launch of
+// layer l + 1, so a step is one launch per layer plus one closing merge, and a layer's page stream starts under the
+// previous layer's tail.
+int run_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer, int cache_kind, int kv_dtype,
+               const int64_t* key_strides, const int64_t* value_strides, const void* slot_mapping, int slot_is_i64,
+               int q_dtype, const int64_t* q_strides, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+               const int64_t* key_cache_strides, const int64_t* value_cache_strides, int64_t num_blocks,
+               int block_size, const void* block_tables, int bt_is_i64, const int64_t* bt_strides, int64_t bt_width,
+               const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint, int out_dtype,
+               const int64_t* out_strides, int num_splits, void* workspace, int64_t workspace_bytes, int flags,
+               void* stream) {
+  if (failed_layer) *failed_layer = -1;
+  if (num_layers < 0) return INT8KV_E_BAD_SHAPE;
+  if (num_layers == 0) return INT8KV_OK;
+  if (!layers) return INT8KV_E_NULLPTR;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto make_call = [&](const int8kv_layer_args& L, void* ws, int64_t ws_bytes, int lf) {
+    AttnCall a{L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+               L.key_cache, L.value_cache, cache_kind, key_cache_strides, value_cache_strides, num_blocks, block_size,
+               block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
+               L.k_scale, L.v_scale, L.out, out_dtype, out_strides, nullptr,
+               num_splits, ws, ws_bytes, lf, st};
+    if (L.key != nullptr) {
+      a.new_k = L.key; a.new_v = L.value; a.new_dtype = kv_dtype; a.nk_st = key_strides; a.nv_st = value_strides;
+      a.new_slots = slot_mapping; a.new_slot_is_i64 = slot_is_i64;
+    }
+    return a;
+  };
+  Chain chain;
+  char* ws = static_cast<char*>(workspace);
+  int64_t half = 0;
+  unsigned int* status = nullptr;
+  if ((flags & INT8KV_FLAG_INPUTS_READY) && num_layers > 1 && ws != nullptr && workspace_bytes >= 1024 &&
+      (reinterpret_cast<uintptr_t>(ws) & 255u) == 0) {
+    half = (workspace_bytes / 2) & ~int64_t(255);
+    status = reinterpret_cast<unsigned int*>(ws + int8kv_workspace_status_offset(workspace_bytes));
+    AttnCall probe = make_call(layers[0], ws, half, flags);
+    AttnPlan t;
+    std::memset(&t, 0, sizeof(t));
+    chain.active = batch > 0 && plan_attention(probe, t) == INT8KV_OK && t.tiled;  // else: one workspace, own merges
+  }
+  for (int l = 0; l < num_layers; ++l) {
+    const int8kv_layer_args& L = layers[l];
+    if (L.key != nullptr && (!L.value || !slot_mapping || !key_strides || !value_strides) && batch > 0) {
+      flush_chain(&chain, st);
+      if (failed_layer) *failed_layer = l;
+      return INT8KV_E_NULLPTR;
+    }
+    if (L.key != nullptr && !valid_float_dtype(kv_dtype)) {
+      flush_chain(&chain, st);
+      if (failed_layer) *failed_layer = l;
+      return INT8KV_E_BAD_DTYPE;
+    }
+    // the promise is about the layers of this call; what precedes the call on the stream is unknown here, so the
+    // first layer orders itself behind it in the ordinary way
+    const int lf = l == 0 ? (flags & ~INT8KV_FLAG_INPUTS_READY) : flags;
+    AttnCall a = chain.active ? make_call(L, ws + (l & 1) * half, half, lf) : make_call(L, workspace, workspace_bytes, lf);
+    if (chain.active) {
+      a.status = status;
+#ifndef INT8KV_EXPERIMENT_LATENCY_SPLITS
+      a.chained = true;
+#endif
+    }
+    int rc = run_attention(a, &chain);
+    if (rc == INT8KV_E_UNSUPPORTED && L.key != nullptr) {
+      // a shape outside the tiled kernel: the write and the attention as two calls (nothing was launched above)
+      rc = flush_chain(&chain, st);
+      if (rc == INT8KV_OK)
+        rc = int8kv_cache_write(L.key, L.value, kv_dtype, batch, num_kv_heads, head_dim, key_strides, value_strides,
+                                L.key_cache, L.value_cache, key_cache_strides, value_cache_strides, num_blocks,
+                                block_size, slot_mapping, slot_is_i64, L.k_scale, L.v_scale, stream);
+      if (rc == INT8KV_OK) {
+        AttnCall b = make_call(L, workspace, workspace_bytes, lf & ~INT8KV_FLAG_INPUTS_READY);
+        b.new_k = nullptr;
+        rc = run_attention(b, nullptr);
+      }
+    }
+    if (rc != INT8KV_OK) {
+      flush_chain(&chain, st);
+      if (failed_layer) *failed_layer = l;
+      return rc;
+    }
+  }
+  return flush_chain(&chain, st);
+}
+
+}  // namespace
+
+extern "C" {
+
 int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer, int kv_dtype,
                               const int64_t key_strides[3], const int64_t value_strides[3],
                               const void* slot_mapping, int slot_is_i64, int q_dtype, const int64_t q_strides[3],
@@ -686,36 +844,33 @@ int int8kv_decode_step_layers(const int8kv_layer_args* layers, int num_layers, i
                               const int64_t bt_strides[2], int64_t bt_width, const void* seq_lens, int sl_is_i64,
                               int64_t max_seq_len_hint, int out_dtype, const int64_t out_strides[3],
                               int num_splits, void* workspace, int64_t workspace_bytes, int flags, void* stream) {
+  return run_layers(layers, num_layers, failed_layer, kCacheInt8, kv_dtype, key_strides, value_strides, slot_mapping,
+                    slot_is_i64, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, key_cache_strides,
+                    value_cache_strides, num_blocks, block_size, block_tables, bt_is_i64, bt_strides, bt_width,
+                    seq_lens, sl_is_i64, max_seq_len_hint, out_dtype, out_strides, num_splits, workspace,
+                    workspace_bytes, flags, stream);
+}
+
+int int8kv_paged_attn_bf16_layers(const int8kv_layer_args* layers, int num_layers, int* failed_layer, int cache_dtype,
+                                  int q_dtype, const int64_t q_strides[3], int batch, int num_q_heads,
+                                  int num_kv_heads, int head_dim, const int64_t key_cache_strides[4],
+                                  const int64_t value_cache_strides[4], int64_t num_blocks, int block_size,
+                                  const void* block_tables, int bt_is_i64, const int64_t bt_strides[2],
+                                  int64_t bt_width, const void* seq_lens, int sl_is_i64, int64_t max_seq_len_hint,
+                                  int out_dtype, const int64_t out_strides[3], int num_splits, void* workspace,
+                                  int64_t workspace_bytes, int flags, void* stream) {
   if (failed_layer) *failed_layer = -1;
-  if (num_layers < 0) return INT8KV_E_BAD_SHAPE;
-  if (num_layers == 0) return INT8KV_OK;
-  if (!layers) return INT8KV_E_NULLPTR;
-  for (int l = 0; l < num_layers; ++l) {
-    const int8kv_layer_args& L = layers[l];
-    // the promise is about the layers of this call; what precedes the call on the stream is unknown here, so the
-    // first layer orders itself behind it in the ordinary way
-    const int lf = l == 0 ? (flags & ~INT8KV_FLAG_INPUTS_READY) : flags;
-    int rc;
-    if (L.key != nullptr) {
-      rc = int8kv_decode_step(L.key, L.value, kv_dtype, key_strides, value_strides, slot_mapping, slot_is_i64,
-                              L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim, L.key_cache,
-                              L.value_cache, key_cache_strides, value_cache_strides, num_blocks, block_size,
-                              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
-                              L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits, workspace,
-                              workspace_bytes, lf, stream);
-    } else {
-      rc = int8kv_paged_attn_int8(L.query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
-                                  L.key_cache, L.value_cache, key_cache_strides, value_cache_strides, num_blocks,
-                                  block_size, block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64,
-                                  max_seq_len_hint, L.k_scale, L.v_scale, L.out, out_dtype, out_strides, num_splits,
-                                  workspace, workspace_bytes, lf, stream);
-    }
-    if (rc != INT8KV_OK) {
+  if (cache_dtype != INT8KV_BF16 && cache_dtype != INT8KV_FP16) return INT8KV_E_BAD_DTYPE;
+  for (int l = 0; layers != nullptr && l < num_layers; ++l)
+    if (layers[l].key != nullptr || layers[l].value != nullptr) {  // float caches have no quantising write
       if (failed_layer) *failed_layer = l;
-      return rc;
+      return INT8KV_E_UNSUPPORTED;
     }
-  }
-  return INT8KV_OK;
+  return run_layers(layers, num_layers, failed_layer, cache_dtype == INT8KV_BF16 ? kCacheBf16 : kCacheFp16, 0, nullptr,
+                    nullptr, nullptr, 0, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
+                    key_cache_strides, value_cache_strides, num_blocks, block_size, block_tables, bt_is_i64,
+                    bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint, out_dtype, out_strides, num_splits,
+                    workspace, workspace_bytes, flags, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -144,12 +144,22 @@ struct MergeParams {
   unsigned int* status;
 };
 
+// A merge carried by the NEXT layer's attention launch (chained layers): the CTAs from `attn_ctas` on do not attend,
+// they merge the previous layer's partial rows, one warp per output row, `merge_warps` warps in all.
+struct ChainedMerge {
+  MergeParams m;    // m.rows == 0: nothing to merge
+  int attn_ctas;
+  int merge_warps;
+};
+
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
 int launch_cache_write_dynamic(const DynWriteParams& p, cudaStream_t stream);
+// `prev`: null, or the merge of the previous layer's partial rows to be carried by this launch (tiled kernels with
+// static scales only; the caller has made sure of that).
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const MergeParams* prev = nullptr);
 int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                          cudaStream_t stream);
+                          cudaStream_t stream, const MergeParams* prev = nullptr);
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
 int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream);

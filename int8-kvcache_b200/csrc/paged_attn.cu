@@ -387,6 +387,110 @@ __device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord
 }
 
 // ---------------------------------------------------------------------------------------------
+// Merge of one output row's partial rows by ONE warp (head_dim 128: a 16-byte piece of the row per lane).  Used by
+// the chained launches, where the CTAs behind the attention items merge the PREVIOUS layer's rows while this
+// layer's pages stream: off the critical path, so one warp per row, eight parts in flight, is enough.  Same
+// arithmetic as merge_partials_kernel: weights exp(lse_r - max lse), parts with lse = -inf never read, all-empty
+// rows give zeros.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t row, int lane) {
+  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
+  int64_t stride_r = p.rows * p.row_floats;
+  const float* base = p.parts + row * p.row_floats;
+  int R = p.R;
+  if (p.seq_table != nullptr) {
+    const int2 e = __ldcg(p.seq_table + b);
+    if (e.y <= 1) return;  // a single part went straight to the output
+    R = e.y < kMaxSplits ? e.y : kMaxSplits;
+    stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
+    base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
+  }
+#ifndef INT8KV_MERGE_TRIP
+#define INT8KV_MERGE_TRIP 16
+#endif
+  constexpr int kTrip = INT8KV_MERGE_TRIP;  // parts whose rows are in flight together
+  float w[kMaxSplits / kWarp], top = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / kWarp; ++j) {
+    const int r = lane + kWarp * j;
+    w[j] = r < R ? __ldcg(base + r * stride_r + p.D) : -INFINITY;
+  }
+  // The rows of the first trip are requested before the weights exist, so that both reads share one latency.  Rows
+  // of empty parts were never written: whatever they hold is discarded by the weight test below.
+  float4 o[kTrip];
+#pragma unroll
+  for (int u = 0; u < kTrip; ++u) {
+    o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#ifndef INT8KV_MERGE_NO_PREFETCH
+    if (u < R) o[u] = __ldcg(reinterpret_cast<const float4*>(base + u * stride_r + 4 * lane));
+#endif
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / kWarp; ++j) top = fmaxf(top, w[j]);
+  for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
+  float den = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / kWarp; ++j) {
+    w[j] = w[j] == -INFINITY ? 0.f : __expf(w[j] - top);
+    den += w[j];
+  }
+  for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(kFull, den, off);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  // Four running sums, part r into sum r % 4, added up in the order ((s0 + s1) + s2) + s3: the order in which the
+  // four warps of merge_partials_kernel accumulate and combine, so that both merges return the same bits.
+  float4 acc[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r0 = 0; r0 < R; r0 += kTrip) {
+    const int slot = r0 >> 5;  // the same for all parts of this trip
+    const float mine = slot == 0 ? w[0] : (slot == 1 ? w[1] : (slot == 2 ? w[2] : w[3]));
+    float wr[kTrip];
+#pragma unroll
+    for (int u = 0; u < kTrip; ++u) {
+      wr[u] = r0 + u < R ? __shfl_sync(kFull, mine, (r0 + u) & 31) : 0.f;
+#ifndef INT8KV_MERGE_NO_PREFETCH
+      if (r0 > 0 && wr[u] > 0.f) o[u] = __ldcg(reinterpret_cast<const float4*>(base + (r0 + u) * stride_r + 4 * lane));
+#else
+      if (wr[u] > 0.f) o[u] = __ldcg(reinterpret_cast<const float4*>(base + (r0 + u) * stride_r + 4 * lane));
+#endif
+    }
+#pragma unroll
+    for (int u = 0; u < kTrip; ++u) {
+      if (wr[u] > 0.f) {
+        float4& a = acc[u & 3];
+        a.x += wr[u] * o[u].x; a.y += wr[u] * o[u].y; a.z += wr[u] * o[u].z; a.w += wr[u] * o[u].w;
+      }
+    }
+  }
+  float4 a;
+  a.x = (acc[0].x + acc[1].x + acc[2].x + acc[3].x) * inv;
+  a.y = (acc[0].y + acc[1].y + acc[2].y + acc[3].y) * inv;
+  a.z = (acc[0].z + acc[1].z + acc[2].z + acc[3].z) * inv;
+  a.w = (acc[0].w + acc[1].w + acc[2].w + acc[3].w) * inv;
+  const int d = 4 * lane;
+  const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
+  if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && ((reinterpret_cast<uintptr_t>(p.out) + 2 * (ob + d)) & 7u) == 0) {
+    uint2 v;
+    v.x = pack_bf162(a.x, a.y);
+    v.y = pack_bf162(a.z, a.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + ob + d) = v;
+  } else {
+    store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
+    store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
+    store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
+    store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
+  }
+}
+
+// The merge share of a chained launch: warp `mw` of `cm.merge_warps` takes the rows mw, mw + merge_warps, ...
+// The rows come from the launch that precedes this one on the stream, so the dependency is resolved first.
+__device__ __forceinline__ void chained_merge(const ChainedMerge& cm, int mw, int lane) {
+  grid_dependency_wait();
+  grid_launch_dependents();
+  for (int64_t row = mw; row < cm.m.rows; row += cm.merge_warps) merge_row_by_warp(cm.m, row, lane);
+}
+
+// ---------------------------------------------------------------------------------------------
 // INT8 cache, D = 128, group <= 8
 // ---------------------------------------------------------------------------------------------
 // One V tile (16 tokens x 128 dims of one head, swizzled in shared memory) times P^T (two B registers):
@@ -472,10 +576,11 @@ __device__ __noinline__ void fused_row_write(const void* kc, const void* vc, int
 // PLANNED: the items come from plan_in_warp instead of being numbered arithmetically.  A template parameter rather
 // than a run-time test, so that the kernel that serves small calls does not carry the planning code.
 // QQ: the reference's optional INT8 query (quantize_q), one limb; its own instantiation as well.
-template <int NST, int MODE, bool PLANNED, bool QQ>
+// CHAINED: the CTAs behind the attention items merge the previous layer's partial rows (chained_merge).
+template <int NST, int MODE, bool PLANNED, bool QQ, bool CHAINED>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                       const AttnParams p) {
+                       const AttnParams p, const ChainedMerge cm) {
   static_assert(NST % 2 == 0, "tiles are consumed in pairs");
   constexpr bool FUSED_WRITE = MODE == kFusedWrite;
   constexpr bool DYN = MODE == kDynScales;
@@ -484,6 +589,12 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   const int wpc = blockDim.x >> 5;  // warps per CTA: 1 for small grids (spread over all SMs), 4 otherwise
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  if constexpr (CHAINED) {
+    if (static_cast<int>(blockIdx.x) >= cm.attn_ctas) {
+      chained_merge(cm, (static_cast<int>(blockIdx.x) - cm.attn_ctas) * wpc + warp, lane);
+      return;
+    }
+  }
 
   ItemCoord it;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
@@ -851,15 +962,21 @@ __device__ __forceinline__ void mma16(float (&d)[4], const uint32_t (&a)[4], uin
   else mma_f16(d, a[0], a[1], a[2], a[3], b0, b1);
 }
 
-template <int NST, bool IS_BF16, bool PLANNED>
+template <int NST, bool IS_BF16, bool PLANNED, bool CHAINED>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp)
 paged_attn_f16_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                      const AttnParams p) {
+                      const AttnParams p, const ChainedMerge cm) {
   constexpr int kStage = 8192;  // K: two 16x128-byte halves (dims 0-63, 64-127), then V likewise
   extern __shared__ uint8_t smem_raw[];
   const int wpc = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  if constexpr (CHAINED) {
+    if (static_cast<int>(blockIdx.x) >= cm.attn_ctas) {
+      chained_merge(cm, (static_cast<int>(blockIdx.x) - cm.attn_ctas) * wpc + warp, lane);
+      return;
+    }
+  }
 
   ItemCoord it;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * wpc + warp;
@@ -1845,30 +1962,65 @@ static int pick_wpc(int64_t items, int sm_count) {
   return items <= static_cast<int64_t>(sm_count) * 12 ? 1 : kTiledWarpsPerCta;
 }
 
+// Grid of a tiled launch.  With a merge to carry (chained layers), CTAs are appended behind the attention items:
+// as many as the previous layer has rows per CTA's warps, but no more than the slots the attention CTAs leave
+// free on the device (so that the whole grid is scheduled at once and the next launch is not held back), and at
+// least one per SM; each merge warp then walks several rows.
+struct TiledGrid {
+  unsigned ctas;
+  ChainedMerge cm;
+};
+static TiledGrid tiled_grid(int64_t items, int wpc, int ctas_per_sm, int sm_count, const MergeParams* prev) {
+  TiledGrid g;
+  std::memset(&g, 0, sizeof(g));
+  const int64_t attn = (items + wpc - 1) / wpc;
+  g.cm.attn_ctas = static_cast<int>(attn);
+  g.ctas = static_cast<unsigned>(attn);
+  if (prev != nullptr && prev->rows > 0) {
+    const int64_t want = (prev->rows + wpc - 1) / wpc;
+    const int64_t spare = static_cast<int64_t>(sm_count) * ctas_per_sm - attn;
+    const int64_t merge_ctas = std::max<int64_t>(1, std::min<int64_t>(want, std::max<int64_t>(sm_count, spare)));
+    g.cm.m = *prev;
+    g.cm.merge_warps = static_cast<int>(merge_ctas * wpc);
+    g.ctas += static_cast<unsigned>(merge_ctas);
+  }
+  return g;
+}
+
 // One instantiation of the INT8 kernel: raises its dynamic shared-memory limit once, sizes the grid, launches.
-template <int NST, int MODE, bool PLANNED, bool QQ = false>
+template <int NST, int MODE, bool PLANNED, bool QQ = false, bool CHAINED = false>
 static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const MergeParams* prev = nullptr) {
   constexpr int per_warp = NST * (4096 + 8 + (MODE == kDynScales ? 128 : 0));  // stages, barriers, scale slots
-  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED, QQ>;
-  if (set_smem<100 + NST * 16 + MODE * 4 + (PLANNED ? 2 : 0) + (QQ ? 1 : 0)>(kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
+  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED, QQ, CHAINED>;
+  if (set_smem<100 + NST * 32 + MODE * 8 + (PLANNED ? 4 : 0) + (QQ ? 2 : 0) + (CHAINED ? 1 : 0)>(
+          kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
     return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   if (items >= (int64_t(1) << 31)) return INT8KV_E_UNSUPPORTED;  // the kernels number their items in 32 bits
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * per_warp + 1024;
-  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
+  const int ctas_per_sm = std::min<int>(wpc == 1 ? 32 : 3, static_cast<int>((227 * 1024) / smem));
+  const TiledGrid g = tiled_grid(items, wpc, ctas_per_sm, sm_count, CHAINED ? prev : nullptr);
+  return launch_pdl(kernel, g.ctas, wpc * kWarp, smem, stream, tmK, tmV, p, g.cm);
 }
 
 int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const MergeParams* prev) {
   constexpr int N = kInt8Stages;
   const bool planned = p.plan_table != nullptr;
+  if (prev != nullptr && prev->rows > 0) {  // static scales, no INT8 query: the caller has checked
+    if (planned)
+      return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, true, false, true>(p, tmK, tmV, sm_count, stream, prev)
+                                : launch_int8_variant<N, kPlain, true, false, true>(p, tmK, tmV, sm_count, stream, prev);
+    return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, false, false, true>(p, tmK, tmV, sm_count, stream, prev)
+                              : launch_int8_variant<N, kPlain, false, false, true>(p, tmK, tmV, sm_count, stream, prev);
+  }
   if (p.ks_cache != nullptr)
     return planned ? launch_int8_variant<N, kDynScales, true>(p, tmK, tmV, sm_count, stream)
                    : launch_int8_variant<N, kDynScales, false>(p, tmK, tmV, sm_count, stream);
-  if (p.quantize_q && p.new_k == nullptr)  // the INT8 query exists with the default ring depth only
+  if (p.quantize_q && p.new_k == nullptr)  // the INT8 query exists without the fused write only
     return planned ? launch_int8_variant<N, kPlain, true, true>(p, tmK, tmV, sm_count, stream)
                    : launch_int8_variant<N, kPlain, false, true>(p, tmK, tmV, sm_count, stream);
   if (planned)
@@ -1878,23 +2030,32 @@ int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CU
                             : launch_int8_variant<N, kPlain, false>(p, tmK, tmV, sm_count, stream);
 }
 
-template <bool IS_BF16, bool PLANNED>
+template <bool IS_BF16, bool PLANNED, bool CHAINED = false>
 static int launch_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, const MergeParams* prev = nullptr) {
   constexpr int smem_max = kTiledWarpsPerCta * kF16Stages * 8192 + kTiledWarpsPerCta * kF16Stages * 8 + 1024;
-  auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16, PLANNED>;
-  if (set_smem<(IS_BF16 ? 1 : 2) + (PLANNED ? 2 : 0)>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
+  auto kernel = paged_attn_f16_kernel<kF16Stages, IS_BF16, PLANNED, CHAINED>;
+  if (set_smem<(IS_BF16 ? 1 : 2) + (PLANNED ? 2 : 0) + (CHAINED ? 4 : 0)>(kernel, smem_max) != 0) return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
   if (items <= 0) return INT8KV_OK;
   if (items >= (int64_t(1) << 31)) return INT8KV_E_UNSUPPORTED;  // the kernels number their items in 32 bits
   const int wpc = pick_wpc(items, sm_count);
   const size_t smem = static_cast<size_t>(wpc) * kF16Stages * 8192 + wpc * kF16Stages * 8 + 1024;
-  return launch_pdl(kernel, static_cast<unsigned>((items + wpc - 1) / wpc), wpc * kWarp, smem, stream, tmK, tmV, p);
+  const int ctas_per_sm = std::min<int>(wpc == 1 ? 32 : 4, static_cast<int>((227 * 1024) / smem));
+  const TiledGrid g = tiled_grid(items, wpc, ctas_per_sm, sm_count, CHAINED ? prev : nullptr);
+  return launch_pdl(kernel, g.ctas, wpc * kWarp, smem, stream, tmK, tmV, p, g.cm);
 }
 
 int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const MergeParams* prev) {
   const bool planned = p.plan_table != nullptr;
+  if (prev != nullptr && prev->rows > 0) {
+    if (p.cache_kind == kCacheBf16)
+      return planned ? launch_f16<true, true, true>(p, tmK, tmV, sm_count, stream, prev)
+                     : launch_f16<true, false, true>(p, tmK, tmV, sm_count, stream, prev);
+    return planned ? launch_f16<false, true, true>(p, tmK, tmV, sm_count, stream, prev)
+                   : launch_f16<false, false, true>(p, tmK, tmV, sm_count, stream, prev);
+  }
   if (p.cache_kind == kCacheBf16)
     return planned ? launch_f16<true, true>(p, tmK, tmV, sm_count, stream)
                    : launch_f16<true, false>(p, tmK, tmV, sm_count, stream);

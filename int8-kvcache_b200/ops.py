@@ -254,16 +254,18 @@ def _sm_count(device: torch.device) -> int:
     return n
 
 
-def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits):
+def _plan_workspace(lib, device, B, Hq, Hkv, D, block_size, max_seq, num_splits, copies: int = 1):
     """(split argument for the library, workspace).  num_splits None = automatic (the library picks a count from the
     shape or, for large calls, plans the parts on the device from seq_lens), "planned" = always plan on the
-    device, an int = exactly that many."""
+    device, an int = exactly that many.  copies = 2: room for two layers' partial rows (chained layers)."""
     if num_splits is None or num_splits == "planned":
         splits = _lib.SPLITS_AUTO if num_splits is None else _lib.SPLITS_PLANNED
         nbytes = lib.int8kv_workspace_bytes_auto(B, Hq, Hkv, D, max_seq, block_size, _sm_count(device))
     else:
         splits = max(1, min(int(num_splits), lib.int8kv_max_splits()))
         nbytes = lib.int8kv_workspace_bytes(B, Hq, D, splits)
+    if copies > 1:
+        nbytes = copies * ((nbytes + 511) // 256 * 256)
     ws = _workspace(device, nbytes)
     return splits, ws
 
@@ -518,14 +520,17 @@ class DecodeStepLayers:
     under CUDA-graph replay), so everything the binding needs — L pointer records, strides, table geometry, the
     workspace — is fixed when this object is built; calling it costs one ctypes crossing and no per-layer Python.
     Arguments as int8_decode_step_layers.  The tensors are kept alive by the object; their contents may change
-    between calls, their addresses may not.  inputs_ready: no layer reads what an earlier layer of the call writes
-    (INT8KV_FLAG_INPUTS_READY), so every layer after the first overlaps the previous layer's merge."""
+    between calls, their addresses may not.  Caches may be INT8 (keys / values: the step's new rows, or None for
+    attention only) or bf16 / fp16 (attention only, no scales: the baseline).
+    inputs_ready: no layer reads what an earlier layer of the call writes (INT8KV_FLAG_INPUTS_READY).  The object then
+    holds a workspace of twice the ordinary size and the library chains the layers: one launch per layer, each
+    carrying the previous layer's split-KV merge and starting its page stream under the previous layer's tail."""
 
     def __init__(self, queries, keys, values, key_caches, value_caches, slot_mapping, block_tables, seq_lens,
                  k_scales, v_scales, *, max_seq_len: int, num_splits: Optional[int] = None,
                  out: Optional[torch.Tensor] = None, inputs_ready: bool = False):
         L = len(key_caches)
-        assert len(value_caches) == L and len(queries) == L and len(k_scales) == L and len(v_scales) == L
+        assert len(value_caches) == L and len(queries) == L
         assert (keys is None) == (values is None)
         fused = keys is not None
         if fused:
@@ -546,6 +551,10 @@ class DecodeStepLayers:
         assert out.shape[1:] == (B, Hq, D)
         if B == 0:
             return
+        int8_cache = kc0.dtype == torch.int8
+        assert int8_cache or (kc0.dtype in (torch.bfloat16, torch.float16) and not fused)
+        if int8_cache:
+            assert len(k_scales) == L and len(v_scales) == L
         lib = _require_lib()
         if seq_lens.stride(0) != 1:
             seq_lens = seq_lens.contiguous()
@@ -562,17 +571,18 @@ class DecodeStepLayers:
         for l in range(L):
             q, kc, vc = queries[l], key_caches[l], value_caches[l]
             assert q.is_cuda and q.shape == q0.shape and q.dtype == q0.dtype and q.stride() == q0.stride()
-            assert kc.dtype == torch.int8 and vc.dtype == torch.int8 and kc.is_cuda and vc.is_cuda
+            assert kc.dtype == kc0.dtype and vc.dtype == kc0.dtype and kc.is_cuda and vc.is_cuda
             assert kc.shape == kc0.shape and vc.shape == kc0.shape
             assert kc.stride() == kc0.stride() and vc.stride() == vc0.stride()
-            ks, vs = _as_f32_scale(k_scales[l]), _as_f32_scale(v_scales[l])
-            assert ks.is_cuda and vs.is_cuda and ks.numel() == Hkv and vs.numel() == Hkv
-            keep += [ks, vs]
             assert out[l].stride() == out[0].stride()
             a = layers[l]
             a.query, a.out = q.data_ptr(), out[l].data_ptr()
             a.key_cache, a.value_cache = kc.data_ptr(), vc.data_ptr()
-            a.k_scale, a.v_scale = ks.data_ptr(), vs.data_ptr()
+            if int8_cache:
+                ks, vs = _as_f32_scale(k_scales[l]), _as_f32_scale(v_scales[l])
+                assert ks.is_cuda and vs.is_cuda and ks.numel() == Hkv and vs.numel() == Hkv
+                keep += [ks, vs]
+                a.k_scale, a.v_scale = ks.data_ptr(), vs.data_ptr()
             if fused:
                 k, v = keys[l], values[l]
                 assert k.is_cuda and v.is_cuda and k.shape == k0.shape and v.shape == k0.shape
@@ -580,18 +590,14 @@ class DecodeStepLayers:
                 assert k.stride() == k0.stride() and v.stride() == v0.stride()
                 a.key, a.value = k.data_ptr(), v.data_ptr()
         self._device = q0.device
-        splits, ws = _plan_workspace(lib, q0.device, B, Hq, Hkv, D, block_size, int(max_seq_len), num_splits)
+        splits, ws = _plan_workspace(lib, q0.device, B, Hq, Hkv, D, block_size, int(max_seq_len), num_splits,
+                                     copies=2 if inputs_ready and L > 1 else 1)
         self._ws_stream = torch.cuda.current_stream(q0.device).cuda_stream
         keep.append(ws)
         self._keep = keep
         self._failed = C.c_int(-1)
         zero3 = _lib.i64((0, 0, 0))
-        self._fn = lib.int8kv_decode_step_layers
-        self._args = (
-            layers, L, C.byref(self._failed),
-            _FLOAT_CODES[keys[0].dtype] if fused else 0,
-            _lib.i64(keys[0].stride()) if fused else zero3, _lib.i64(values[0].stride()) if fused else zero3,
-            slot_mapping.data_ptr() if fused else None, int(fused and slot_mapping.dtype == torch.int64),
+        common = (
             _FLOAT_CODES[q0.dtype], _lib.i64(q0.stride()),
             B, Hq, Hkv, D,
             _lib.i64(kc0.stride()), _lib.i64(vc0.stride()),
@@ -602,6 +608,19 @@ class DecodeStepLayers:
             _FLOAT_CODES[out.dtype], _lib.i64(out[0].stride()),
             splits, ws.data_ptr(), ws.numel(), _flags(False, inputs_ready),
         )
+        if int8_cache:
+            self._name = "int8kv_decode_step_layers"
+            self._fn = lib.int8kv_decode_step_layers
+            self._args = (
+                layers, L, C.byref(self._failed),
+                _FLOAT_CODES[keys[0].dtype] if fused else 0,
+                _lib.i64(keys[0].stride()) if fused else zero3, _lib.i64(values[0].stride()) if fused else zero3,
+                slot_mapping.data_ptr() if fused else None, int(fused and slot_mapping.dtype == torch.int64),
+            ) + common
+        else:
+            self._name = "int8kv_paged_attn_bf16_layers"
+            self._fn = lib.int8kv_paged_attn_bf16_layers
+            self._args = (layers, L, C.byref(self._failed), _FLOAT_CODES[kc0.dtype]) + common
 
     def __call__(self) -> torch.Tensor:
         """Enqueue the L layers on the current stream of the tensors' device and return `out` [L, B, Hq, D].
@@ -612,7 +631,7 @@ class DecodeStepLayers:
         assert stream == self._ws_stream, "DecodeStepLayers must run on the stream it was built on"
         rc = self._fn(*self._args, stream)
         if rc != _lib.OK:
-            raise _lib.Int8KVError(f"int8kv_decode_step_layers (layer {self._failed.value})", rc)
+            raise _lib.Int8KVError(f"{self._name} (layer {self._failed.value})", rc)
         return self.out
 
 

@@ -526,6 +526,114 @@ def test_inputs_ready_promise_changes_timing_not_results(kv, workloads):
     assert kv.device_status() == 0
 
 
+@pytest.mark.parametrize("lens,splits", [
+    ([700, 45, 260, 1, 2048, 130], 4),          # every sequence split four ways
+    ([700, 45, 260, 1, 2048, 130], None),       # automatic count
+    ([700, 45, 260, 1, 2048, 130], "planned"),  # parts planned on the device, some sequences unsplit
+    ([40, 17], 1),                              # no split at all: nothing to chain, outputs written directly
+    ([3000] * 12, 32),                          # enough items for four-warp thread blocks
+])
+def test_chained_layers_match_single_calls(kv, workloads, lens, splits):
+    """The L-layer entry point with the inputs-ready promise chains its layers: every layer works in its own half of
+    the workspace and its split-KV merge is carried, as extra thread blocks, by the next layer's launch (the last one
+    by a closing merge).  Outputs must be bit for bit those of one ordinary call per layer: INT8 attention, the
+    fused decode step (cache bytes included) and the BF16 baseline, for odd and even layer counts, launched
+    eagerly several times in a row and replayed as a CUDA graph."""
+    dev = "cuda"
+    B, mx = len(lens), max(lens)
+    base, kc0, vc0 = _case_on_gpu(kv, workloads, lens, seed=70)
+    bt, sl = base.block_tables.to(dev), base.seq_lens.to(dev)
+    last = torch.tensor([sum(lens[: b + 1]) - 1 for b in range(B)])
+    slots = base.slot_mapping[last].to(dev)
+    g = torch.Generator().manual_seed(71)
+    for L in (5, 2):
+        layers = []
+        for li in range(L):
+            # same block table for all layers, own cache contents, scales, queries and new rows per layer
+            k = (torch.randn(base.key.shape, generator=g) * (1 + 0.1 * li)).to(torch.bfloat16)
+            v = (torch.randn(base.value.shape, generator=g) * 0.5).to(torch.bfloat16)
+            ks = (k.float().abs().amax(dim=(0, 2)) / 127).clamp_min(1e-6)
+            vs = (v.float().abs().amax(dim=(0, 2)) / 127).clamp_min(1e-6)
+            kc, vc = torch.zeros_like(kc0), torch.zeros_like(vc0)
+            oracle.cache_write(k, v, kc, vc, base.slot_mapping, ks, vs)
+            kb = torch.zeros(base.num_blocks, 16, 4, 128, dtype=torch.bfloat16)
+            vb = torch.zeros_like(kb)
+            s_ = base.slot_mapping
+            kb[s_ // 16, s_ % 16], vb[s_ // 16, s_ % 16] = k, v
+            q = torch.randn(B, 28, 128, generator=g).to(torch.bfloat16)
+            layers.append(dict(q=q.to(dev), kc=kc.to(dev), vc=vc.to(dev), kb=kb.to(dev), vb=vb.to(dev), ks=ks.to(dev),
+                               vs=vs.to(dev), nk=torch.randn(B, 4, 128, generator=g).to(torch.bfloat16).to(dev),
+                               nv=(torch.randn(B, 4, 128, generator=g) * 0.5).to(torch.bfloat16).to(dev),
+                               q_cpu=q, kc_cpu=kc, vc_cpu=vc, ks_cpu=ks, vs_cpu=vs))
+        # --- what single calls return
+        want_i8 = torch.stack([kv.int8_paged_attention(x["q"], x["kc"], x["vc"], bt, sl, x["ks"], x["vs"],
+                                                       num_splits=splits, max_seq_len=mx) for x in layers])
+        want_bf = torch.stack([kv.bf16_paged_attention(x["q"], x["kb"], x["vb"], bt, sl, num_splits=splits,
+                                                       max_seq_len=mx) for x in layers])
+        torch.cuda.synchronize()
+        _check(want_i8[0], oracle.int8_paged_attention_oracle(layers[0]["q_cpu"], layers[0]["kc_cpu"], layers[0]["vc_cpu"],
+                                                              base.block_tables, lens, layers[0]["ks_cpu"], layers[0]["vs_cpu"]))
+        # --- attention only, chained
+        out = torch.full_like(want_i8, float("nan"))
+        plan = kv.DecodeStepLayers([x["q"] for x in layers], None, None, [x["kc"] for x in layers],
+                                   [x["vc"] for x in layers], None, bt, sl, [x["ks"] for x in layers],
+                                   [x["vs"] for x in layers], max_seq_len=mx, num_splits=splits, out=out,
+                                   inputs_ready=True)
+        for _ in range(3):
+            plan()
+        torch.cuda.synchronize()
+        assert torch.equal(out, want_i8)
+        # --- the BF16 baseline through the same chaining
+        out_b = torch.full_like(want_bf, float("nan"))
+        plan_b = kv.DecodeStepLayers([x["q"] for x in layers], None, None, [x["kb"] for x in layers],
+                                     [x["vb"] for x in layers], None, bt, sl, None, None, max_seq_len=mx,
+                                     num_splits=splits, out=out_b, inputs_ready=True)
+        for _ in range(3):
+            plan_b()
+        torch.cuda.synchronize()
+        assert torch.equal(out_b, want_bf)
+        # --- both replayed as one CUDA graph, INT8 and BF16 chains back to back
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            p1 = kv.DecodeStepLayers([x["q"] for x in layers], None, None, [x["kc"] for x in layers],
+                                     [x["vc"] for x in layers], None, bt, sl, [x["ks"] for x in layers],
+                                     [x["vs"] for x in layers], max_seq_len=mx, num_splits=splits, out=out,
+                                     inputs_ready=True)
+            p2 = kv.DecodeStepLayers([x["q"] for x in layers], None, None, [x["kb"] for x in layers],
+                                     [x["vb"] for x in layers], None, bt, sl, None, None, max_seq_len=mx,
+                                     num_splits=splits, out=out_b, inputs_ready=True)
+            p1(), p2()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                p1(), p2()
+            out.fill_(float("nan"))
+            out_b.fill_(float("nan"))
+            for _ in range(3):
+                graph.replay()
+            stream.synchronize()
+        assert torch.equal(out, want_i8) and torch.equal(out_b, want_bf)
+        del graph
+        # --- the fused decode step, chained, against one int8_decode_step per layer: outputs and cache bytes
+        ca = [(x["kc"].clone(), x["vc"].clone()) for x in layers]
+        cb = [(x["kc"].clone(), x["vc"].clone()) for x in layers]
+        want_s = torch.stack([kv.int8_decode_step(x["q"], x["nk"], x["nv"], ca[i][0], ca[i][1], slots, bt, sl, x["ks"],
+                                                  x["vs"], max_seq_len=mx, num_splits=splits)
+                              for i, x in enumerate(layers)])
+        out_s = torch.full_like(want_s, float("nan"))
+        plan_s = kv.DecodeStepLayers([x["q"] for x in layers], [x["nk"] for x in layers], [x["nv"] for x in layers],
+                                     [c[0] for c in cb], [c[1] for c in cb], slots, bt, sl, [x["ks"] for x in layers],
+                                     [x["vs"] for x in layers], max_seq_len=mx, num_splits=splits, out=out_s,
+                                     inputs_ready=True)
+        for _ in range(2):
+            plan_s()
+        torch.cuda.synchronize()
+        assert torch.equal(out_s, want_s)
+        for (ka, va), (kb_, vb_) in zip(ca, cb):
+            assert torch.equal(ka, kb_) and torch.equal(va, vb_)
+    assert kv.device_status() == 0
+
+
 def test_device_planned_splits(kv, workloads):
     """num_splits="planned": the kernel reads seq_lens and cuts the sequences into parts of one common length that
     fill whole waves of warps; every operator that takes the tiled path accepts it."""
