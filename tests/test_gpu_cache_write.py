@@ -69,6 +69,40 @@ def test_prefill_write_full_size_with_padding_slots(kv, workloads):
     assert int((kc.reshape(-1, 512) == CANARY).all(dim=1).sum()) >= skipped
 
 
+@pytest.mark.parametrize("dtype,heads,dim,tokens,bs", [
+    (torch.bfloat16, 4, 128, 2048 + 37, 16),
+    (torch.float16, 8, 128, 4099, 32),
+    (torch.float32, 4, 128, 2500, 16),         # fp32 rows: four 16-byte pieces per unit
+    (torch.bfloat16, 2, 64, 3000, 16),
+    (torch.bfloat16, 16, 256, 2048, 16),
+    (torch.float32, 3, 48, 2100, 16),          # units per token not a power of two: division instead of shifts
+])
+def test_large_writes_special_values_and_random_slot_order(kv, dtype, heads, dim, tokens, bs):
+    """Thousands of tokens, several row widths and input types: int32 slots in random order over a pool larger than
+    the write, padding slots, exact rounding ties, huge, infinite and NaN inputs (the quantiser's packed fast path has
+    no range test of its own: saturation and the exact branch must come out right all the same), canaries around."""
+    g = torch.Generator().manual_seed(tokens)
+    key = torch.randn(tokens, heads, dim, generator=g).to(dtype)
+    value = (torch.randn(tokens, heads, dim, generator=g) * 0.5).to(dtype)
+    k_scale = torch.rand(heads, generator=g) * 0.02 + 0.01
+    v_scale = torch.full((heads,), 0.0078125)  # 2^-7: every multiple of 2^-8 among the values is an exact tie
+    special = torch.tensor([1e9, -1e9, float("inf"), float("-inf"), float("nan"), 0.0, -0.0, 3.0])
+    if dtype == torch.float32:
+        special[:2] = torch.tensor([3e38, -3e38])  # quotients far beyond the range in which the rounding trick is exact
+    key[5, 0, :8] = special.to(dtype)
+    value[7, 1, :8] = (torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, 126.5, -126.5, 127.5]) * 0.0078125).to(dtype)
+    num_blocks = (tokens + bs - 1) // bs + 9
+    perm = torch.randperm(num_blocks * bs, generator=g)[:tokens]
+    slots = perm.to(torch.int32)
+    slots[torch.rand(tokens, generator=g) < 0.02] = -1
+    shape = (num_blocks, bs, heads, dim)
+    kc, vc = _gpu_write(kv, key, value, shape, slots, k_scale, v_scale, fill=CANARY)
+    kc_o = torch.full(shape, CANARY, dtype=torch.int8)
+    vc_o = torch.full(shape, CANARY, dtype=torch.int8)
+    oracle.cache_write(key, value, kc_o, vc_o, slots.long(), k_scale, v_scale)
+    assert torch.equal(kc, kc_o) and torch.equal(vc, vc_o)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("slot_dtype", [torch.int32, torch.int64])
 def test_input_and_slot_dtypes(kv, dtype, slot_dtype):
