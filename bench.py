@@ -47,10 +47,11 @@ if str(REPO) not in sys.path:
     sys.path.insert(0, str(REPO))
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one paged_attn_int8_kernel launch per algorithmic byte of the
-# launch, from ncu captures of this script (the summaries under profiles/): the c2 figure is a one-pass capture of
-# the workload itself, the c4 / c5 figures come from captures of a smaller batch of the same shape and are scaled
-# by the bytes a full launch processes (traffic grows in proportion: every page is read once).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"c2": 33690154 / 33677376, "c4": 1.013, "c5": 1.002}
+# launch, from one-pass ncu captures of this script's own workloads (profiles/bench_default__launch_list.md for c4
+# and c2); the c5 figure comes from a capture of a smaller batch of the same shape
+# (profiles/paged_attn_int8_kernel__c4_first64.md names the method) and is scaled by the bytes a full launch
+# processes: traffic grows in proportion, every page is read once.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"c2": 35601446 / 33677376, "c4": 1243454701 / 1206481112, "c5": 1.002}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 METRIC = "int8_paged_decode_attn_achieved_hbm_gbps"
@@ -825,7 +826,8 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": ctx.peak, "unit": "GB/s", "frac": achieved / ctx.peak,
                      "traffic": int(traffic * nbytes_call) if traffic and not (args.batch or dynamic) else None,
                      "traffic_source": "ncu dram bytes of a smaller launch of the same shape, scaled by algorithmic bytes"
-                     if name in ("c4", "c5") else "ncu dram bytes of this launch",
+                     if name == "c5" or parts > 1 else "ncu dram bytes of this launch (serialised: the carried merge "
+                     "re-reads the previous layer's partial rows from DRAM there, from L2 in the timed run)",
                      "peak_source": ctx.peak_src,
                      "kernel": "paged_attn_int8_kernel (+ merge_partials_kernel when split), per call inside the graph",
                      "algorithmic_bytes_per_call": nbytes_call},

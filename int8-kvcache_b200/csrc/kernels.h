@@ -144,12 +144,16 @@ struct MergeParams {
   unsigned int* status;
 };
 
-// A merge carried by the NEXT layer's attention launch (chained layers): the CTAs from `attn_ctas` on do not attend,
-// they merge the previous layer's partial rows, one warp per output row, `merge_warps` warps in all.
+// A merge carried by the NEXT layer's attention launch (chained layers), one warp per output row, `merge_warps`
+// warps in all.  Two ways to seat those warps:
+//  duty = 0  extra CTAs behind the attention items (from CTA `attn_ctas` on) that do nothing else;
+//  duty = 1  the attention warps themselves, each as its last act (after it resolved the dependency for its own
+//            writes), with no extra CTAs.
 struct ChainedMerge {
   MergeParams m;    // m.rows == 0: nothing to merge
   int attn_ctas;
   int merge_warps;
+  int duty;
 };
 
 int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream);
