@@ -460,12 +460,12 @@ def leg_cache_write(ctx):
     }
 
 
-def layered_steps(ctx, layers_data, max_seq, num_splits=None, bf16=False):
+def layered_steps(ctx, layers_data, max_seq, num_splits=None, bf16=False, mode=None):
     """The step function of a device-timed leg: all layers of `layers_data` (INT8 caches, or their bf16 twins).
     --launch chained (default): one DecodeStepLayers call with the inputs-ready promise, i.e. one launch per layer,
     each carrying the previous layer's split-KV merge; per-call: one operator call per layer, each with the promise;
     ordered: one operator call per layer, fully ordered behind the previous one."""
-    kv, mode = ctx.kv, ctx.args.launch
+    kv, mode = ctx.kv, mode or ctx.args.launch
     L0 = layers_data[0]
     outs = torch.empty((len(layers_data),) + tuple(L0.query.shape), dtype=L0.query.dtype, device=L0.query.device)
     for i, L in enumerate(layers_data):
@@ -484,14 +484,14 @@ def layered_steps(ctx, layers_data, max_seq, num_splits=None, bf16=False):
         return plan
     ready = mode == "per-call"
 
-    def step():
-        for L in layers_data:
+    def step():  # writes this call's own `outs`, whatever L.out names by the time it runs
+        for L, out in zip(layers_data, outs):
             if bf16:
                 kv.bf16_paged_attention(L.query, L.kb, L.vb, L.block_tables, L.seq_lens, num_splits=num_splits,
-                                        max_seq_len=max_seq, out=L.out, inputs_ready=ready)
+                                        max_seq_len=max_seq, out=out, inputs_ready=ready)
             else:
                 kv.int8_paged_attention(L.query, L.kc, L.vc, L.block_tables, L.seq_lens, L.k_scale, L.v_scale,
-                                        num_splits=num_splits, max_seq_len=max_seq, out=L.out, inputs_ready=ready)
+                                        num_splits=num_splits, max_seq_len=max_seq, out=out, inputs_ready=ready)
 
     return step
 
@@ -615,6 +615,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
                                                 inputs_ready=ready)
     else:
         device_step = layered_steps(ctx, layers_data, max_seq, args.num_splits)
+    main_out0 = layers_data[0].out  # layer 0's output buffer of the timed mode (other legs bring their own)
 
     lib = kv._lib.load()
     splits = args.num_splits or lib.int8kv_choose_splits(B, hkv, max_seq, 16, ctx.sm)
@@ -634,11 +635,22 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
     dev_ms = ctx.time_device(device_step, sampler=sampler)
     clocks = sampler.stop() if sampler is not None else None
 
+    # ---- the same step in the other launch modes, for the record (see LAUNCH_MODES) ---------------------------
+    other_modes = {}
+    if not dynamic and not sub and not args.no_graph:
+        for m in LAUNCH_MODES:
+            if m != args.launch:
+                other_modes[m] = ctx.time_device(layered_steps(ctx, layers_data, max_seq, args.num_splits, mode=m))
+        with torch.cuda.stream(ctx.stream):
+            main_out0.fill_(float("nan"))
+            device_step()  # the timed mode once more: its result is what the check below reads
+            ctx.stream.synchronize()
+
     # ---- oracle check of the timed calls' result (layer 0, a few sequences of this rank's shard) -------------
     check = None
     if not dynamic:
         picks = sorted(set([0, B // 2, B - 1]))[: (3 if max_seq <= 16384 else 1)]
-        err, cos = oracle_check(layers_data[0], layers_data[0].out, hkv, picks)
+        err, cos = oracle_check(layers_data[0], main_out0, hkv, picks)
         err, = ctx.reduce([err], "max")
         cos, = ctx.reduce([cos], "min")
         check = {"layer": 0, "sequences_per_rank": picks, "max_abs": err, "cosine": cos,
@@ -782,6 +794,9 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
 
     dev_ms, e2e_ms, e2e_eager_ms, bf16_ms, e2e_layers_ms, warm_ms = ctx.reduce(
         [dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms, e2e_layers_s * 1e3, warm_ms], "max")
+    mode_names = sorted(other_modes)
+    mode_ms = dict(zip(mode_names, ctx.reduce([other_modes[m] for m in mode_names], "max"))) if mode_names else {}
+    mode_ms[args.launch] = dev_ms
     total_step_bytes, total_token_layers, h2d_all, d2h_all = ctx.reduce(
         [nbytes_step, B * layers, h2d, d2h], "sum")
     status = kv.device_status(device)
@@ -802,6 +817,7 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         "tokens_layers_per_s": total_token_layers / (dev_ms * 1e-3),
         "frac_of_8TBps": value / world / HBM_NOMINAL_GBS,
         "num_splits": splits, "split_plan": split_plan,
+        "launch_modes_us_per_call": {m: v * 1e3 / layers for m, v in sorted(mode_ms.items())},
         "gpu_launches": ((layers + (1 if launches_per_call > 1 else 0)) if chained else launches_per_call * layers) * args.steps,
         "clocks": clocks, "device_status": int(status), "shard_check": check,
         "e2e": {"value": total_step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",

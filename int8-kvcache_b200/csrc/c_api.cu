@@ -174,9 +174,18 @@ bool plan_pays(int B, int Hkv, int64_t max_seq, int block_size, int sm_count) {
   return items * choose_splits(B, Hkv, max_seq, block_size, sm_count) < slots * 4;
 }
 
-PlanShape plan_shape(int B, int Hkv, int64_t tiles, int sm_count) {
+// Warps per SM that a plan counts as one wave.  A single call fills the machine exactly (12 resident warps per SM).
+// A layer of a chained sequence aims for two thirds of that: with every slot taken by one layer, the next layer's
+// warps can only enter as these leave, and each layer pays its prologue and epilogue with idle memory pipes; at 8 per
+// SM two layers interleave.  Measured per layer, chained, 12 -> 8 warps per SM: one KV head x 128 ragged sequences
+// (the 8-GPU shard of the 256-sequence batch) 29.7 -> 25.4 us (0.83 -> 0.97 of the HBM peak), 64 ragged sequences x 4
+// heads 50.1 -> 48.3 us, 16 sequences 17.5 -> 15.1 us; 6 per SM gains nothing more on the small ones and loses on
+// the large ones (53 us), 10 sits between.
+constexpr int kPlanWaveSingle = 12, kPlanWaveChained = 8;
+
+PlanShape plan_shape(int B, int Hkv, int64_t tiles, int sm_count, int wave_warps = kPlanWaveSingle) {
   constexpr int min_part = 48;  // shortest part (16-token tiles) a plan aiming for more than one wave may choose
-  const int64_t slots = static_cast<int64_t>(sm_count) * 12;
+  const int64_t slots = static_cast<int64_t>(sm_count) * wave_warps;
   const int64_t items = static_cast<int64_t>(B) * Hkv;
   PlanShape s{1, 0, min_part};
   // the same rule the plan kernel applies, on the nominal lengths: the actual k can only be smaller
@@ -289,7 +298,7 @@ int plan_attention(const AttnCall& a, AttnPlan& t) {
       a.bt_width * a.block_size < (int64_t(1) << 21) * 16 &&  // tile counts stay exact in fp32 on the device
       (a.num_splits == INT8KV_SPLITS_PLANNED ? plan_possible(a.B, a.Hkv, t.sm)
                                               : plan_pays(a.B, a.Hkv, t.max_seq, a.block_size, t.sm))) {
-    t.ps = plan_shape(a.B, a.Hkv, t.tiles, t.sm);
+    t.ps = plan_shape(a.B, a.Hkv, t.tiles, t.sm, a.chained ? kPlanWaveChained : kPlanWaveSingle);
     t.pl = plan_layout(a.B, a.Hq, a.Hkv, a.D, t.ps.max_items);
     // the plan's header sits in the 16 bytes before the status word, wherever the workspace ends
     t.planned = a.ws != nullptr && a.ws_bytes >= t.pl.total && (reinterpret_cast<uintptr_t>(a.ws) & 15u) == 0 &&
@@ -380,7 +389,7 @@ int run_attention(const AttnCall& a, Chain* chain = nullptr) {
     p.plan_table = reinterpret_cast<int2*>(base + pl.table_off);
     p.plan_header = reinterpret_cast<int*>(base + pl.header_off);
     p.plan_grid_items = ps.max_items;
-    p.plan_slots = sm * 12;
+    p.plan_slots = sm * (a.chained ? kPlanWaveChained : kPlanWaveSingle);
     p.plan_k_max = ps.k_max;
     p.plan_min_part = ps.min_part;
     p.direct_part = a.partial_out;
@@ -462,8 +471,10 @@ int64_t int8kv_workspace_bytes_auto(int batch, int num_q_heads, int num_kv_heads
       n = std::max(n, ws_bytes(batch, num_q_heads, head_dim,
                                untiled_splits(batch, num_q_heads, num_kv_heads, head_dim, int8_cache, max_seq_len, sm)));
   if (batch > 0 && tiles > 0 && plan_possible(batch, num_kv_heads, sm)) {
-    const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm);
-    n = std::max(n, plan_layout(batch, num_q_heads, num_kv_heads, head_dim, ps.max_items).total);
+    for (const int wave : {kPlanWaveSingle, kPlanWaveChained}) {  // a chained layer may plan more, shorter waves
+      const PlanShape ps = plan_shape(batch, num_kv_heads, tiles, sm, wave);
+      n = std::max(n, plan_layout(batch, num_q_heads, num_kv_heads, head_dim, ps.max_items).total);
+    }
   }
   return n;
 }
@@ -804,9 +815,7 @@ int run_layers(const int8kv_layer_args* layers, int num_layers, int* failed_laye
     AttnCall a = chain.active ? make_call(L, ws + (l & 1) * half, half, lf) : make_call(L, workspace, workspace_bytes, lf);
     if (chain.active) {
       a.status = status;
-#ifndef INT8KV_EXPERIMENT_LATENCY_SPLITS
       a.chained = true;
-#endif
     }
     int rc = run_attention(a, &chain);
     if (rc == INT8KV_E_UNSUPPORTED && L.key != nullptr) {

@@ -405,10 +405,7 @@ __device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t 
     stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
     base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
   }
-#ifndef INT8KV_MERGE_TRIP
-#define INT8KV_MERGE_TRIP 16
-#endif
-  constexpr int kTrip = INT8KV_MERGE_TRIP;  // parts whose rows are in flight together
+  constexpr int kTrip = 16;  // parts whose rows are in flight together
   float w[kMaxSplits / kWarp], top = -INFINITY;
 #pragma unroll
   for (int j = 0; j < kMaxSplits / kWarp; ++j) {
@@ -421,9 +418,7 @@ __device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t 
 #pragma unroll
   for (int u = 0; u < kTrip; ++u) {
     o[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#ifndef INT8KV_MERGE_NO_PREFETCH
     if (u < R) o[u] = __ldcg(reinterpret_cast<const float4*>(base + u * stride_r + 4 * lane));
-#endif
   }
 #pragma unroll
   for (int j = 0; j < kMaxSplits / kWarp; ++j) top = fmaxf(top, w[j]);
@@ -448,11 +443,7 @@ __device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t 
 #pragma unroll
     for (int u = 0; u < kTrip; ++u) {
       wr[u] = r0 + u < R ? __shfl_sync(kFull, mine, (r0 + u) & 31) : 0.f;
-#ifndef INT8KV_MERGE_NO_PREFETCH
       if (r0 > 0 && wr[u] > 0.f) o[u] = __ldcg(reinterpret_cast<const float4*>(base + (r0 + u) * stride_r + 4 * lane));
-#else
-      if (wr[u] > 0.f) o[u] = __ldcg(reinterpret_cast<const float4*>(base + (r0 + u) * stride_r + 4 * lane));
-#endif
     }
 #pragma unroll
     for (int u = 0; u < kTrip; ++u) {
