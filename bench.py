@@ -449,7 +449,22 @@ def leg_cache_write(ctx):
 
     us = ctx.time_device(step) * 1e3 / len(sets)
     gbs = nbytes / us / 1e3
+    # yardstick: what a plain device copy reaches at this launch size (same total bytes read + written per launch, same
+    # 8-set rotation, same graph replay) - the roofline's peak is a long copy, whose ramp and tail weigh nothing
+    half = int(nbytes // 2) // 16 * 16
+    srcs = [torch.rand(half // 4, dtype=torch.float32, device=device) for _ in sets]
+    dsts = [torch.empty_like(x) for x in srcs]
+
+    def copies():
+        for a, b in zip(srcs, dsts):
+            torch.neg(a, out=b)
+
+    copy_us = ctx.time_device(copies) * 1e3 / len(sets)
+    del srcs, dsts
     return {
+        "same_bytes_copy": {"us_per_call": copy_us, "frac": 2 * half / copy_us / 1e3 / ctx.peak,
+                            "what": "torch.neg on fp32, bytes/2 read and bytes/2 written per launch, timed the same way (an "
+                                    "elementwise kernel of PyTorch, not of this library)"},
         "metric": "int8_dynamic_scale_kv_cache_write_achieved_hbm_gbps" if dynamic else "int8_kv_cache_write_achieved_hbm_gbps",
         "value": gbs, "unit": "GB/s", "us_per_call": us, "frac": gbs / ctx.peak, "frac_of_8TBps": gbs / HBM_NOMINAL_GBS,
         "gpu_launches": len(sets) * args.steps, "ms_per_step": us * len(sets) / 1e3,
@@ -896,6 +911,29 @@ def leg_sequence_parallel(ctx, hq, hkv, seq_lens):
         chk = sequence_parallel_check(ctx, layer, local_lens, merged[key], picks)
         result[label] = {"us_per_step": ms * 1e3, "eager_us_per_step": eager_ms * 1e3,
                          "value": nbytes / (ms * 1e-3) / 1e9, "seq_parallel_check": chk}
+    if peer is not None:
+        # where a peer-store step spends its time: the rank's own attention (parts + their merge into rows), the same
+        # followed by the push (nobody waits for the flags), and the whole step
+        B, D = len(seq_lens), 128
+        rows = torch.empty((B, hq, 132), device=device, dtype=torch.float32)  # out (128) | lse | pad
+
+        def partial_only():
+            kv.int8_paged_attention_partial(layer.query, layer.kc, layer.vc, layer.block_tables, layer.seq_lens,
+                                            layer.k_scale, layer.v_scale, max_seq_len=max_local, out=rows)
+
+        def partial_push():
+            kv.int8_paged_attention_partial_push(layer.query, layer.kc, layer.vc, layer.block_tables,
+                                                     layer.seq_lens, layer.k_scale, layer.v_scale, peer.exchange,
+                                                     max_seq_len=max_local)
+
+        a_ms, = ctx.reduce([ctx.time_device(partial_only)], "max")
+        b_ms, = ctx.reduce([ctx.time_device(partial_push)], "max")
+        result["peer_stores"]["breakdown_us"] = {
+            "partial_rows": a_ms * 1e3, "partial_rows_and_push": b_ms * 1e3,
+            "whole_step": result["peer_stores"]["us_per_step"],
+            "what": "max over ranks of: the rank's attention and the merge of its parts into rows; the same followed by "
+                    "the push into every rank's buffer (no rank waits for flags); the whole step with the flag wait and "
+                    "the merge of all ranks' rows"}
     status, = ctx.reduce([kv.device_status(device)], "max")
     result["device_status"] = int(status)
     result["collective"] = {"bytes_per_rank": len(seq_lens) * hq * 132 * 4,
@@ -1016,7 +1054,7 @@ def main():
                     "warmup": args.warmup, "ms_per_step": rec["ms_per_step"], "higher_is_better": True,
                     "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
                     "us_per_call": rec["us_per_call"], "gpu_launches": rec["gpu_launches"],
-                    "config": {"workload": rec["workload"]},
+                    "same_bytes_copy": rec["same_bytes_copy"], "config": {"workload": rec["workload"]},
                     "roofline": {"bound": "hbm", "achieved": rec["value"], "peak": ctx.peak, "unit": "GB/s",
                                  "frac": rec["frac"], "traffic": None, "kernel": rec["kernel"],
                                  "algorithmic_bytes_per_call": rec["algorithmic_bytes_per_call"]}}

@@ -340,14 +340,15 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
  * Sequence-parallel exchange over peer memory (NVLink / NVSwitch), for the split of one long sequence across GPUs
  * with one process per GPU.  The reference has no multi-GPU path; the math is its split-KV merge (:330-388) across
  * devices, as with int8kv_paged_attn_int8_partial + int8kv_merge_partials, but the partial rows travel by plain
- * 16-byte stores into the other ranks' memory instead of through a collective library:
+ * 16-byte stores into the other ranks' memory instead of through a collective library, every fp32 value paired with
+ * the step's number so that the receiver recognises a value of the current step by itself (no flag behind the data,
+ * no fence on the sender):
  *   - every rank owns one exchange buffer of int8kv_exchange_bytes() bytes, 256-byte aligned, ZEROED before first
  *     use, and mapped into every other rank's address space (CUDA IPC or a symmetric-memory allocator; the library
  *     allocates and maps nothing).  `peer_buffers[r]` is rank r's buffer as seen from THIS process; entry `rank`
  *     is the local one.  All ranks must agree on world, batch, num_q_heads, head_dim;
  *   - int8kv_paged_attn_int8_partial_push computes this rank's partial rows (arguments of
- *     int8kv_paged_attn_int8_partial) and stores them, with an arrival flag behind them, into every rank's buffer;
- *     it never waits for another GPU;
+ *     int8kv_paged_attn_int8_partial) and stores them into every rank's buffer; it never waits for another GPU;
  *   - int8kv_merge_exchanged, enqueued behind it on the same stream, waits until every rank's rows of the current
  *     step have arrived and merges them from LOCAL memory.  The wait is bounded (about a second); if it runs out,
  *     INT8KV_DEV_WAIT_TIMEOUT is set in the status word of `workspace` (optional) and the output is left unwritten.

@@ -51,7 +51,7 @@ __device__ __forceinline__ void quant2_stream(float x0, float x1, float scale, f
   const float2 t = __fadd2_rn(q, make_float2(kRoundMagic, kRoundMagic));
   const float2 n = __fadd2_rn(t, make_float2(-kRoundMagic, -kRoundMagic));
   const float2 d = __ffma2_rn(n, make_float2(-1.f, -1.f), q);  // q - n, exact
-  n0 = max(__float_as_int(t.x), 0) - kRoundMagicBits;
+  n0 = max(__float_as_int(t.x), 0) - kRoundMagicBits;  // (a fused add-then-max would wrap for -1.5 * 2^23 < t < 0)
   n1 = max(__float_as_int(t.y), 0) - kRoundMagicBits;
   if (!(fabsf(d.x) < 0.5f - 6.2e-5f)) n0 = quant1_exact(x0, scale);
   if (!(fabsf(d.y) < 0.5f - 6.2e-5f)) n1 = quant1_exact(x1, scale);
@@ -87,8 +87,11 @@ struct Raw16 {
 // unit count fits) and by shift where the sizes are powers of two.  128 threads and a register cap that fits 12
 // CTAs = 48 warps per SM: finer waves and more resident warps than 256 threads x 5 CTAs (12.8 -> 11.8 us on the
 // 16384-token write).
+// DENSE: K and V rows and both caches are dense in their logical order and Hkv * D / 16 and D / 16 are powers of two
+// (the launcher checks), so a unit's source is unit * 16 elements from the base and its destination slot * Hkv * D +
+// (unit mod units-per-token) * 16: a handful of shifts instead of ten 64-bit stride products per thread.
 constexpr int kVecThreads = 128;
-template <typename T>
+template <typename T, bool DENSE>
 __global__ void __launch_bounds__(kVecThreads, 12) cache_write_vec_kernel(const WriteParams p, const uint32_t total,
                                                               const int bs_shift, const int pt_shift, const int ch_shift) {
   const uint32_t chunks = static_cast<uint32_t>(p.D) >> 4;
@@ -97,6 +100,22 @@ __global__ void __launch_bounds__(kVecThreads, 12) cache_write_vec_kernel(const 
   if (idx >= total) return;
   grid_dependency_wait();    // the new rows and the slots may come from the kernel launched just before
   grid_launch_dependents();  // the next kernel in the stream waits for this grid before it reads the cache
+  if constexpr (DENSE) {
+    const uint32_t t = idx >> pt_shift;
+    const uint32_t rem = idx & ((1u << pt_shift) - 1u);
+    const uint32_t h = rem >> ch_shift;
+    const int64_t slot = load_index(p.slots, p.slot_is_i64, t);
+    Raw16<T> kr, vr;
+    kr.load(reinterpret_cast<const T*>(p.key) + static_cast<int64_t>(idx) * 16);
+    vr.load(reinterpret_cast<const T*>(p.value) + static_cast<int64_t>(idx) * 16);
+    const float ks = fmaxf(__ldg(p.k_scale + h), 1e-6f);
+    const float vs = fmaxf(__ldg(p.v_scale + h), 1e-6f);
+    if (slot < 0 || slot >= p.num_slots) return;
+    const int64_t dst = (slot << (pt_shift + 4)) + (rem << 4);
+    *reinterpret_cast<uint4*>(p.kc + dst) = kr.quantise(ks, __frcp_rn(ks));
+    *reinterpret_cast<uint4*>(p.vc + dst) = vr.quantise(vs, __frcp_rn(vs));
+    return;
+  }
   const uint32_t t = pt_shift >= 0 ? idx >> pt_shift : idx / per_token;
   const uint32_t rem = idx - t * per_token;
   const uint32_t h = ch_shift >= 0 ? rem >> ch_shift : rem / chunks;
@@ -304,9 +323,20 @@ int launch_cache_write(const WriteParams& p, int sm_count, cudaStream_t stream) 
     const int pt_shift = shift_of(static_cast<int64_t>(p.Hkv) * (p.D / 16));
     const unsigned blocks = static_cast<unsigned>((units + threads - 1) / threads);
     const uint32_t total = static_cast<uint32_t>(units);
-    if (p.in_dtype == INT8KV_BF16) return launch_pdl(cache_write_vec_kernel<__nv_bfloat16>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
-    if (p.in_dtype == INT8KV_FP16) return launch_pdl(cache_write_vec_kernel<__half>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
-    return launch_pdl(cache_write_vec_kernel<float>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+    const int64_t row = static_cast<int64_t>(p.Hkv) * p.D;
+    bool dense = pt_shift >= 0 && ch_shift >= 0 && p.kc_st[2] == p.D && p.kc_st[1] == row &&
+                 p.kc_st[0] == row * p.block_size;
+    for (int i = 0; i < 4 && dense; ++i) dense = p.kc_st[i] == p.vc_st[i];
+    for (int i = 0; i < 3 && dense; ++i) dense = p.k_st[i] == p.v_st[i];
+    dense = dense && p.k_st[1] == p.D && p.k_st[0] == row;
+    if (dense) {
+      if (p.in_dtype == INT8KV_BF16) return launch_pdl(cache_write_vec_kernel<__nv_bfloat16, true>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+      if (p.in_dtype == INT8KV_FP16) return launch_pdl(cache_write_vec_kernel<__half, true>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+      return launch_pdl(cache_write_vec_kernel<float, true>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+    }
+    if (p.in_dtype == INT8KV_BF16) return launch_pdl(cache_write_vec_kernel<__nv_bfloat16, false>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+    if (p.in_dtype == INT8KV_FP16) return launch_pdl(cache_write_vec_kernel<__half, false>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
+    return launch_pdl(cache_write_vec_kernel<float, false>, blocks, threads, 0, stream, p, total, bs_shift, pt_shift, ch_shift);
   } else {
     const int64_t work = p.T * p.Hkv * static_cast<int64_t>(p.D);
     int64_t blocks = (work + threads - 1) / threads;

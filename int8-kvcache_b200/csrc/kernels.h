@@ -135,9 +135,8 @@ struct MergeParams {
   const int2* seq_table;  // device-planned splits: parts of row (b, hq) are rows (row0 + c) * Hq + hq, c < used
   int early_trigger;  // call griddepcontrol.launch_dependents right after the dependency wait
   int inputs_ready;   // the call that produced the parts carried the inputs-ready promise: always trigger early
-  // Parts that other GPUs pushed into the local exchange buffer (exchange_ctrl != null): the kernel first waits,
-  // with a bound, until every rank's arrival flag has reached the owner's epoch, and reads the slab of that epoch;
-  // `parts` then points at slab 0 and slab_floats is the distance to slab 1.
+  // Rows that all ranks pushed into the local exchange buffer as (value, epoch) pairs (merge_exchanged_kernel only):
+  // exchange_ctrl is the buffer's control block, `parts` points at slab 0 and slab_floats counts the pairs of a slab.
   const int* exchange_ctrl;
   int exchange_world;
   int64_t slab_floats;
@@ -167,6 +166,11 @@ int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUt
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
 int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream);
+int launch_merge_exchanged(const MergeParams& p, cudaStream_t stream);
+// The merge of a rank's split-KV parts and the push of the merged rows in one kernel (head_dim % 4 == 0): p.part_out
+// names the staging area of the local exchange buffer, where rows of sequences with a single part already lie; the
+// merged rows go straight into every rank's slab.
+int launch_merge_push(const MergeParams& p, const ExchangeParams& e, cudaStream_t stream);
 int launch_bounded_wait_selftest(unsigned int* status, unsigned int attempts, cudaStream_t stream);
 
 // resident warps per SM the tiled int8 kernel is sized for (used by the split heuristic)

@@ -1753,7 +1753,40 @@ __global__ void __launch_bounds__(128, GM == 4 ? 4 : (GM == 8 ? 3 : 2)) paged_at
 // ---------------------------------------------------------------------------------------------
 constexpr int kMergeWarps = 4;
 
-__global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(const MergeParams p) {
+// 16- and 8-byte accesses that are neither cached in L1 nor reordered with one another: the (value, epoch) pairs of
+// the sequence-parallel exchange (see exchange_push_kernel)
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void st_volatile_v2(void* p, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+template <bool PUSH>
+struct PushTarget {};
+template <>
+struct PushTarget<true> {
+  ExchangeParams e;
+};
+
+// PUSH (sequence-parallel exchange, head dims that are multiples of 4): the merged row (out | lse) is not kept locally
+// but stored as (value, epoch) pairs into slab[epoch & 1][rank] of every rank's exchange buffer, which is what
+// exchange_push_kernel would have done with it in a launch of its own; p.part_out is the local staging area, where
+// the attention kernel has left the rows of sequences with a single part, and those are forwarded as they are.
+template <bool PUSH>
+__global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(const MergeParams p,
+                                                                             const PushTarget<PUSH> push) {
   __shared__ float w_s[kMaxSplits];
   __shared__ float red_s[kMergeWarps][4 * kWarp];
   __shared__ float top_s[kMergeWarps];
@@ -1766,38 +1799,33 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 
   grid_dependency_wait();    // the partial rows come from the attention kernel launched just before
   if (p.early_trigger) grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before reading
-  if (p.exchange_ctrl != nullptr) {
-    // Rows pushed by other GPUs: wait until every rank's push of the current epoch has landed.  The epoch was
-    // advanced by this rank's own push kernel, which precedes this kernel on the stream.  Waits are bounded; a rank
-    // that never arrives is reported in the status word and the row is left unwritten.
-    __shared__ int arrived_s;
-    if (threadIdx.x == 0) arrived_s = 1;
-    __syncthreads();
-    const int epoch = ld_acquire_sys(p.exchange_ctrl + 1);
-    if (static_cast<int>(threadIdx.x) < p.exchange_world) {
-      const int* flag = p.exchange_ctrl + 16 + threadIdx.x;  // byte 64 onwards
-      bool ok = false;
-      for (uint32_t spin = 0; spin < kFlagSpinLimit; ++spin) {
-        if (ld_acquire_sys(flag) - epoch >= 0) {
-          ok = true;
-          break;
-        }
-        __nanosleep(spin < 64 ? 100 : 1000);
-      }
-      if (!ok) arrived_s = 0;
-    }
-    __syncthreads();
-    if (!arrived_s) {
-      if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
-      return;
-    }
-    base += static_cast<int64_t>(epoch & 1) * p.slab_floats;
+  uint32_t push_epoch = 0;
+  int64_t push_off = 0;  // byte offset of this row in slab[epoch & 1][rank] of any rank's buffer
+  if constexpr (PUSH) {
+    const ExchangeParams& e = push.e;
+    push_epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
+    const int64_t rank_floats = e.rows * e.row_floats;
+    push_off = kExchCtrlBytes + rank_floats * 4 + (((push_epoch & 1u) * e.world + e.rank) * rank_floats + row * p.row_floats) * 8;
   }
   if (p.seq_table != nullptr) {
     // device-planned splits: this sequence's parts are consecutive part indices; a single part was written to
     // `out` by the attention kernel itself
     const int2 e = __ldg(p.seq_table + b);
-    if (e.y <= 1) return;
+    if (e.y <= 1) {
+      if constexpr (PUSH) {  // ... or, here, to the staging area: forward the row
+        if (static_cast<int>(threadIdx.x) * 4 < p.row_floats) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_out + row * p.row_floats) + threadIdx.x);
+          const uint4 lo = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
+          const uint4 hi = make_uint4(__float_as_uint(v.z), push_epoch, __float_as_uint(v.w), push_epoch);
+          for (int r = 0; r < push.e.world; ++r) {
+            char* dst = push.e.peer[r] + push_off + 32 * threadIdx.x;
+            st_volatile_v4(dst, lo);
+            st_volatile_v4(dst + 16, hi);
+          }
+        }
+      }
+      return;
+    }
     R = e.y < kMaxSplits ? e.y : kMaxSplits;
     stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
     base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
@@ -1857,7 +1885,15 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
       a.y = (a.y + x1.y + x2.y + x3.y) * inv;
       a.z = (a.z + x1.z + x2.z + x3.z) * inv;
       a.w = (a.w + x1.w + x2.w + x3.w) * inv;
-      if (p.part_out != nullptr) {
+      if constexpr (PUSH) {
+        const uint4 lo = make_uint4(__float_as_uint(a.x), push_epoch, __float_as_uint(a.y), push_epoch);
+        const uint4 hi = make_uint4(__float_as_uint(a.z), push_epoch, __float_as_uint(a.w), push_epoch);
+        for (int r = 0; r < push.e.world; ++r) {
+          char* dst = push.e.peer[r] + push_off + 8 * d;
+          st_volatile_v4(dst, lo);
+          st_volatile_v4(dst + 16, hi);
+        }
+      } else if (p.part_out != nullptr) {
         *reinterpret_cast<float4*>(p.part_out + row * p.row_floats + d) = a;
       } else if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
                  ((reinterpret_cast<uintptr_t>(p.out) + 2 * (b * p.o_st[0] + hq * p.o_st[1] + d)) & 7u) == 0) {
@@ -1875,41 +1911,172 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
     }
     __syncthreads();
   }
-  if (p.part_out != nullptr && threadIdx.x == 0)
+  if constexpr (PUSH) {
+    if (threadIdx.x == 0) {
+      const float l = den > 0.f ? top + __logf(den) : -INFINITY;
+      for (int r = 0; r < push.e.world; ++r)
+        st_volatile_v2(push.e.peer[r] + push_off + 8 * p.D, make_uint2(__float_as_uint(l), push_epoch));
+    }
+  } else if (p.part_out != nullptr && threadIdx.x == 0) {
     p.part_out[row * p.row_floats + p.D] = den > 0.f ? top + __logf(den) : -INFINITY;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Push of this rank's partial rows into every rank's exchange buffer (sequence-parallel attention over NVLink).
-// The rows sit in the local buffer's staging area; every CTA copies a share of them into slab[epoch & 1][rank] of
-// every peer with plain 16-byte stores to peer-mapped memory (no TMA, no multicast), makes its stores visible
-// system-wide, and takes a ticket; the CTA that draws the last ticket advances the local epoch and raises this
-// rank's arrival flag in every peer's buffer.  Nothing here waits for another GPU.
+// Sequence-parallel exchange over NVLink: partial rows travel as (value, epoch) pairs.
+//
+// A rank's buffer is [256 B control: ticket, epoch | staging rows, fp32 | 2 slabs x world x rows x row_floats pairs].
+// Every float of a row crosses as an 8-byte pair {value, epoch of the step}; a pair is written by one store (or
+// by one half of a 16-byte store) and therefore arrives whole, so the receiver needs no flag behind the data and
+// the sender no system-scope fence before such a flag: it reads a pair, and the pair is this step's as soon as
+// its second word says so.  (A first version sent bare rows, a fence per CTA, a ticket, and one flag per rank: the
+// push alone then cost 19 us per step on two GPUs, most of it fences.)  The slab alternates with the parity of
+// the epoch, so a fast rank's next step cannot overwrite what a slow rank is still merging: a rank pushes step
+// e + 1 only after its own merge of step e, which needed every rank's push of step e, which followed that rank's
+// merge of step e - 1.  The epoch lives in the local buffer and is advanced by the merge (its last CTA), so a
+// captured graph replays.
 // ---------------------------------------------------------------------------------------------
+// Push of this rank's staged rows into slab[epoch & 1][rank] of EVERY rank's buffer: plain 16-byte stores of two
+// pairs each to peer-mapped memory (no TMA, no multicast, no fence).  Nothing here waits for another GPU.
 __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams e) {
   grid_dependency_wait();  // the staged rows come from the kernel launched just before
   grid_launch_dependents();
-  int* ctrl = reinterpret_cast<int*>(e.peer[e.rank]);
-  const int epoch = ld_acquire_sys(ctrl + 1) + 1;
-  const int64_t slab_floats = static_cast<int64_t>(e.world) * e.rows * e.row_floats;
-  const int64_t n4 = e.rows * e.row_floats / 4;  // row_floats is a multiple of 4
+  const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
+  const int64_t rank_floats = e.rows * e.row_floats;
+  const int64_t n4 = rank_floats / 4;  // row_floats is a multiple of 4
   const float4* src = reinterpret_cast<const float4*>(e.peer[e.rank] + kExchCtrlBytes);
-  const int64_t dst_off = kExchCtrlBytes + (e.rows * e.row_floats + (epoch & 1) * slab_floats +
-                                            static_cast<int64_t>(e.rank) * e.rows * e.row_floats) * 4;
+  const int64_t dst_off = kExchCtrlBytes + rank_floats * 4 + ((epoch & 1u) * e.world + e.rank) * rank_floats * 8;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const float4 v = __ldcg(src + i);
-    for (int r = 0; r < e.world; ++r) reinterpret_cast<float4*>(e.peer[r] + dst_off)[i] = v;
+    const uint4 lo = make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
+    const uint4 hi = make_uint4(__float_as_uint(v.z), epoch, __float_as_uint(v.w), epoch);
+    for (int r = 0; r < e.world; ++r) {
+      char* dst = e.peer[r] + dst_off + 32 * i;
+      st_volatile_v4(dst, lo);
+      st_volatile_v4(dst + 16, hi);
+    }
   }
-  __threadfence_system();
+}
+
+// Merge of the rows that all ranks pushed for the current step, from LOCAL memory: one warp per output row.  Lane r
+// asks for rank r's log-sum-exp and, in the same breath, every lane for its piece of the first eight ranks' rows; the
+// warp then polls until all of that carries the step's epoch (re-reading only what does not yet), so one round trip
+// covers weights and data.  The arithmetic is that of merge_partials_kernel over `world` parts, operation for
+// operation (weights, the shuffle tree of their sum, part r into running sum r % 4, sums combined as
+// ((s0 + s1) + s2) + s3), so both exchanges return the same bits.  Waits are bounded (attempts 50 ns to 1 us apart,
+// about a second in all); a rank that never arrives is reported in the status word and the row is left unwritten.
+constexpr int kExchMergeWarps = 4;
+constexpr int kExchChunk = 8;  // ranks whose rows a lane holds at once (two 16-byte vectors each)
+__global__ void __launch_bounds__(kExchMergeWarps * kWarp) merge_exchanged_kernel(const MergeParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kExchMergeWarps + warp;
+  int* ctrl = const_cast<int*>(p.exchange_ctrl);
+  // The epoch is only advanced by this kernel's last CTA, after every CTA has read it here.
+  const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(ctrl + 1)) + 1u;
+  grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before it reads
+  if (row < p.rows) {
+    const int R = p.exchange_world;
+    const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
+    const int64_t rank_stride = p.rows * p.row_floats * 8;
+    const char* base = reinterpret_cast<const char*>(p.parts) + (epoch & 1u) * p.slab_floats * 8 + row * p.row_floats * 8;
+    uint32_t budget = kFlagSpinLimit;
+    bool ok = true;
+    uint2 lse_pair = make_uint2(0u, epoch);  // lanes beyond the ranks count as arrived, with weight 0
+    bool lse_known = false;
+    float w_mine = 0.f, inv = 0.f;
+    for (int d0 = 0; ok && d0 < p.D; d0 += 4 * kWarp) {
+      const int d = d0 + 4 * lane;
+      const bool live = d < p.D;
+      float4 acc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r0 = 0; ok && r0 < R; r0 += kExchChunk) {
+        uint4 lo[kExchChunk], hi[kExchChunk];
+        const char* src = base + r0 * rank_stride + 8 * d;
+#pragma unroll
+        for (int u = 0; u < kExchChunk; ++u) {
+          lo[u] = hi[u] = make_uint4(0u, epoch, 0u, epoch);  // what is not asked for counts as arrived
+          if (live && r0 + u < R) {
+            lo[u] = ld_volatile_v4(src + u * rank_stride);
+            hi[u] = ld_volatile_v4(src + u * rank_stride + 16);
+          }
+        }
+        if (!lse_known && lane < R) lse_pair = ld_volatile_v2(base + lane * rank_stride + 8 * p.D);
+        for (;;) {
+          bool here = lse_pair.y == epoch;
+#pragma unroll
+          for (int u = 0; u < kExchChunk; ++u)
+            here = here && lo[u].y == epoch && lo[u].w == epoch && hi[u].y == epoch && hi[u].w == epoch;
+          if (__all_sync(kFull, here)) break;
+          if (budget == 0) {
+            ok = false;
+            break;
+          }
+          --budget;
+          __nanosleep(budget + 64 > kFlagSpinLimit ? 50 : 1000);
+          if (lse_pair.y != epoch) lse_pair = ld_volatile_v2(base + lane * rank_stride + 8 * p.D);
+#pragma unroll
+          for (int u = 0; u < kExchChunk; ++u) {
+            if (lo[u].y != epoch || lo[u].w != epoch) lo[u] = ld_volatile_v4(src + u * rank_stride);
+            if (hi[u].y != epoch || hi[u].w != epoch) hi[u] = ld_volatile_v4(src + u * rank_stride + 16);
+          }
+        }
+        if (!ok) break;
+        if (!lse_known) {
+          lse_known = true;
+          const float lse = lane < R ? __uint_as_float(lse_pair.x) : -INFINITY;
+          float top = lse;
+          for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, o));
+          w_mine = lse == -INFINITY ? 0.f : __expf(lse - top);
+          float den = w_mine;
+          for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(kFull, den, o);
+          inv = den > 0.f ? 1.f / den : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < kExchChunk; ++u) {
+          const float w = __shfl_sync(kFull, w_mine, (r0 + u) & 31);
+          if (r0 + u < R && w > 0.f) {
+            float4& a = acc[u & 3];  // kExchChunk is a multiple of 4: (r0 + u) % 4 == u % 4
+            a.x += w * __uint_as_float(lo[u].x); a.y += w * __uint_as_float(lo[u].z);
+            a.z += w * __uint_as_float(hi[u].x); a.w += w * __uint_as_float(hi[u].z);
+          }
+        }
+      }
+      if (!ok || !live) continue;
+      float4 a;
+      a.x = (acc[0].x + acc[1].x + acc[2].x + acc[3].x) * inv;
+      a.y = (acc[0].y + acc[1].y + acc[2].y + acc[3].y) * inv;
+      a.z = (acc[0].z + acc[1].z + acc[2].z + acc[3].z) * inv;
+      a.w = (acc[0].w + acc[1].w + acc[2].w + acc[3].w) * inv;
+      const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
+      if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
+          ((reinterpret_cast<uintptr_t>(p.out) + 2 * (ob + d)) & 7u) == 0) {
+        uint2 v;
+        v.x = pack_bf162(a.x, a.y);
+        v.y = pack_bf162(a.z, a.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + ob + d) = v;
+      } else {
+        store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
+        if (d + 1 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
+        if (d + 2 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
+        if (d + 3 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
+      }
+    }
+    if (!ok && lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
+  }
+  // The ticket; the last CTA advances the epoch for the next step's push and merge.  This grid does not wait for the
+  // push before it on the stream: whoever waits for this grid may find that push still waiting for the other GPUs to
+  // acknowledge its stores (measured: 8 us per step on two GPUs), but never reading or storing locally, because every
+  // row of the local push has arrived here, and the next push writes the other slab.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     const int ticket = atomicAdd(ctrl, 1);
     if (ticket == static_cast<int>(gridDim.x) - 1) {
       ctrl[0] = 0;
-      st_release_sys(ctrl + 1, epoch);
-      __threadfence_system();
-      for (int r = 0; r < e.world; ++r) st_release_sys(reinterpret_cast<int*>(e.peer[r] + 64) + e.rank, epoch);
+      __threadfence();
+      st_release_sys(ctrl + 1, static_cast<int>(epoch));
     }
   }
 }
@@ -2137,7 +2304,23 @@ int launch_merge(const MergeParams& p_in, cudaStream_t stream) {
   // small decode calls); a long one would only have that kernel's CTAs crowd the SMs it still needs.
   p.early_trigger = p.inputs_ready || p.rows * p.R <= 4096;
   if (p.rows <= 0) return INT8KV_OK;
-  return launch_pdl(merge_partials_kernel, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p);
+  return launch_pdl(merge_partials_kernel<false>, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p,
+                    PushTarget<false>{});
+}
+
+int launch_merge_push(const MergeParams& p_in, const ExchangeParams& e, cudaStream_t stream) {
+  MergeParams p = p_in;
+  p.early_trigger = 1;  // what follows is the merge of the exchanged rows, which polls for them
+  if (p.rows <= 0) return INT8KV_OK;
+  PushTarget<true> t;
+  t.e = e;
+  return launch_pdl(merge_partials_kernel<true>, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p, t);
+}
+
+int launch_merge_exchanged(const MergeParams& p, cudaStream_t stream) {
+  if (p.rows <= 0) return INT8KV_OK;
+  const unsigned grid = static_cast<unsigned>((p.rows + kExchMergeWarps - 1) / kExchMergeWarps);
+  return launch_pdl(merge_exchanged_kernel, grid, kExchMergeWarps * kWarp, 0, stream, p);
 }
 
 }  // namespace int8kv

@@ -10,8 +10,8 @@ contiguous range of every sequence's logical blocks in its own cache, computes u
 attention rows (normalised out | log-sum-exp), the rows of all ranks are brought into LOCAL memory,
 and a local merge kernel combines them.  The merge reads local memory only.  Two exchanges exist:
 an NCCL all-gather, and PeerExchange, where every rank stores its rows straight into the other
-ranks' buffers over NVLink (plain stores to peer-mapped memory, an arrival flag behind them) and
-the merge kernel itself waits, with a bound, for the flags.
+ranks' buffers over NVLink (plain stores to peer-mapped memory, every value paired with the step's
+number) and the merge kernel itself waits, with a bound, until the values it reads carry that number.
 
 The reference prototype is single-GPU (its README states TP=1); the split-KV partial/merge math that
 this generalises is its src/triton_ops/int8_paged_attention.py:293-388.
@@ -132,7 +132,7 @@ class PeerExchange:
             raise ValueError(f"no exchange layout for {self.world} ranks and shape {self.shape}")
         self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
         self.handle = symm_mem.rendezvous(self.buffer, group)
-        self.buffer.zero_()  # control words, flags and slabs start at zero on every rank ...
+        self.buffer.zero_()  # control words and slabs start at zero on every rank ...
         torch.cuda.synchronize(device)
         dist.barrier(group)  # ... before anyone's first push can arrive
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
@@ -156,8 +156,8 @@ def sequence_parallel_int8_attention(query, local_key_cache, local_value_cache, 
 
     Every rank passes the full query [B, Hq, D], its own caches/block tables (local physical block ids) and
     the number of tokens of each sequence that it holds.  Returns the merged [B, Hq, D] on every rank.
-    exchange: a PeerExchange built for this batch and head layout; the partial rows then travel by peer stores and
-    flags instead of an NCCL all-gather (same result).
+    exchange: a PeerExchange built for this batch and head layout; the partial rows then travel by peer stores
+    instead of an NCCL all-gather (same result).
     """
     from . import ops
 

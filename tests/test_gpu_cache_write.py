@@ -91,10 +91,13 @@ def test_large_writes_special_values_and_random_slot_order(kv, dtype, heads, dim
         special[:2] = torch.tensor([3e38, -3e38])  # quotients far beyond the range in which the rounding trick is exact
     key[5, 0, :8] = special.to(dtype)
     value[7, 1, :8] = (torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, 126.5, -126.5, 127.5]) * 0.0078125).to(dtype)
+    if dtype != torch.float16:  # quotients around -1.5 * 2^23 and -3 * 2^23, where the rounding constant's sum changes sign
+        value[9, 0, :8] = (torch.tensor([-1.2e7, -1.3e7, -2e7, -2.5e7, -2.6e7, -3.4e7, 1.3e7, 2.6e7]) * 0.0078125).to(dtype)
     num_blocks = (tokens + bs - 1) // bs + 9
     perm = torch.randperm(num_blocks * bs, generator=g)[:tokens]
     slots = perm.to(torch.int32)
     slots[torch.rand(tokens, generator=g) < 0.02] = -1
+    slots[9] = perm[9].to(torch.int32)  # the row of huge quotients is written, not padding
     shape = (num_blocks, bs, heads, dim)
     kc, vc = _gpu_write(kv, key, value, shape, slots, k_scale, v_scale, fill=CANARY)
     kc_o = torch.full(shape, CANARY, dtype=torch.int8)
