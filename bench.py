@@ -51,7 +51,8 @@ if str(REPO) not in sys.path:
 # and c2); the c5 figure comes from a capture of a smaller batch of the same shape
 # (profiles/paged_attn_int8_kernel__c4_first64.md names the method) and is scaled by the bytes a full launch
 # processes: traffic grows in proportion, every page is read once.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"c2": 35601446 / 33677376, "c4": 1243454701 / 1206481112, "c5": 1.002}
+C3_NCU_DRAM_BYTES_IN_KERNEL = 32_677_000 + 18_700  # profiles/cache_write_vec_kernel__c3_prefill.md: read + written, one launch
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"c2": 35601446 / 33677376, "c4": 1243505426 / 1206481112, "c5": 1.002}
 HBM_NOMINAL_GBS = 8000.0
 FALLBACK_PEAK_GBS = 6650.0
 METRIC = "int8_paged_decode_attn_achieved_hbm_gbps"
@@ -472,6 +473,8 @@ def leg_cache_write(ctx):
                     "8 rotated sets (larger than L2)",
         "kernel": "cache_write_dynamic_vec_kernel<bf16>" if dynamic else "cache_write_vec_kernel<bf16>",
         "algorithmic_bytes_per_call": nbytes,
+        # ncu, one launch: rows in from DRAM; the INT8 output is still in L2 at kernel end (written back later)
+        "traffic": None if dynamic else C3_NCU_DRAM_BYTES_IN_KERNEL,
     }
 
 
@@ -748,8 +751,20 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
         meta_h, meta_d = h_in[layers * per_layer:], d_in[layers * per_layer:]
 
+        overlap_copies = per_layer >= (1 << 20)  # a megabyte of input per layer and more
+
         def e2e_enqueue():
             main = torch.cuda.current_stream(device)
+            if not overlap_copies:
+                # small steps: per-layer copies and events would cost more host time than the copies take
+                d_in.copy_(h_in, non_blocking=True)
+                for i, L in enumerate(layers_data):
+                    q, k, v = dv[i]
+                    kv.int8_decode_step(q, k, v, L.kc, L.vc, d_slots, d_bt, d_sl, L.k_scale, L.v_scale,
+                                        num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[i],
+                                        inputs_ready=ready and i > 0)
+                h_out.copy_(d_out, non_blocking=True)
+                return
             s_in.wait_stream(main)
             s_out.wait_stream(main)
             ready_in = []
@@ -844,7 +859,8 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
                 "what": "per step and rank: pinned-host inputs (every layer's new q/k/v rows; block tables, seq_lens, "
                         "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python "
                         "operators, every layer's output -> pinned host, all streams synchronised; the copies run on "
-                        "their own streams, layer by layer, beside the compute of the neighbouring layers; `value` "
+                        "their own streams, layer by layer, beside the compute of the neighbouring layers (steps with less than a "
+                        "megabyte of input per layer copy once before and once after the layers instead); `value` "
                         "replays the step as one CUDA graph, `eager_value` launches it from Python every step, "
                         "`one_call_value` copies everything in, runs one int8kv_decode_step_layers call and copies "
                         "everything out (no graph, no overlap); bytes are summed over ranks"},
@@ -1056,7 +1072,10 @@ def main():
                     "us_per_call": rec["us_per_call"], "gpu_launches": rec["gpu_launches"],
                     "same_bytes_copy": rec["same_bytes_copy"], "config": {"workload": rec["workload"]},
                     "roofline": {"bound": "hbm", "achieved": rec["value"], "peak": ctx.peak, "unit": "GB/s",
-                                 "frac": rec["frac"], "traffic": None, "kernel": rec["kernel"],
+                                 "frac": rec["frac"], "traffic": C3_NCU_DRAM_BYTES_IN_KERNEL, "kernel": rec["kernel"],
+                                 "traffic_note": "ncu, dram__bytes_read.sum + dram__bytes_write.sum of one launch: the rows "
+                                                 "of the tokens that are written come in, the INT8 output is still in L2 when "
+                                                 "the kernel ends and is written back under later kernels",
                                  "algorithmic_bytes_per_call": rec["algorithmic_bytes_per_call"]}}
             if rank == 0:
                 print(json.dumps(_without_nan(line)))

@@ -1,6 +1,6 @@
 """Sequence-parallel INT8 attention on two GPUs: every rank holds a contiguous block range of every sequence
 in its own cache, computes partial rows, brings the rows of all ranks into local memory (an NCCL all-gather, or
-peer stores with arrival flags) and merges locally.  The result must equal single-GPU attention over the whole
+peer stores of {value, step number} pairs) and merges locally.  The result must equal single-GPU attention over the whole
 sequence.  Skipped when fewer than two GPUs are visible.
 Also checks the collective-free KV-head x batch sharding on each rank against the oracle."""
 
@@ -58,7 +58,8 @@ def _worker(rank, world, port, ret):
         torch.cuda.synchronize()
         got = out.float().cpu()
         seq_err, seq_cos = max_abs(got, want.to(torch.bfloat16).float()), cosine(got, want)
-        # the same split with the rows exchanged by peer stores and arrival flags instead of the all-gather: several
+        # the same split with the rows exchanged by peer stores instead of the all-gather (the split-KV merge stores
+        # its rows into the peers' buffers itself): several
         # steps in a row (the buffers alternate between two slabs), then the same steps replayed as a CUDA graph
         peer = sh.PeerExchange(len(lens), 28, 128, dev)
         args = (case.query.to(dev), local_kc.to(dev), local_vc.to(dev), local_tables.to(dev),
@@ -80,6 +81,13 @@ def _worker(rank, world, port, ret):
             stream.synchronize()
         peer_equal = peer_equal and bool(torch.equal(out_g, out))
         del g
+        # an unsplit call leaves its rows in the staging area and a copy kernel pushes them: same exchange, other sender
+        kv.int8_paged_attention_partial_push(*args, peer.exchange, num_splits=1, max_seq_len=max(max(local_lens), 1))
+        out_1 = kv.merge_exchanged(peer.exchange, len(lens), 28, 128, device=dev)
+        torch.cuda.synchronize()
+        got_1 = out_1.float().cpu()
+        unsplit_ok = max_abs(got_1, want.to(torch.bfloat16).float()) <= 2e-2 and cosine(got_1, want) >= 0.9999
+        peer_equal = peer_equal and unsplit_ok
         peer.close()
 
         # --- head x batch shard of this rank, no collective
