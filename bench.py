@@ -701,7 +701,9 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
     # attention for every layer through the Python operators, and copies every layer's output back to a
     # pinned host buffer.  Measured three ways: launched eagerly from Python, through one
     # int8kv_decode_step_layers call per step, and with the calls captured once into a CUDA graph and replayed.
-    e2e_s = e2e_eager_s = e2e_layers_s = float("nan")
+    e2e_s = e2e_eager_s = e2e_layers_s = e2e_per_layer_s = float("nan")
+    e2e_agree = None
+    e2e_from = "CUDA graph replay"
     h2d = d2h = 0
     if not args.no_e2e and not dynamic and not sub:
         shape = wl.LayerShape(hq, hkv, 128, 16)
@@ -794,7 +796,53 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
             e2e_enqueue()
             stream.synchronize()
 
-        e2e_eager_s = ctx.time_host(eager_step)
+        # The same step with the layers chained in groups (--launch chained): one int8kv_decode_step_layers call per
+        # group of layers, the group's inputs copied in beside the previous group's compute and its outputs copied
+        # out beside the next group's.  Steps too small for that (see overlap_copies) are one group.
+        group_len = 4 if overlap_copies else layers
+        groups = [(a, min(a + group_len, layers)) for a in range(0, layers, group_len)]
+        chained_e2e = args.launch == "chained"
+        if chained_e2e:
+            with torch.cuda.stream(stream):
+                group_plans = [kv.DecodeStepLayers(
+                    [dv[i][0] for i in range(a, b)], [dv[i][1] for i in range(a, b)], [dv[i][2] for i in range(a, b)],
+                    [L.kc for L in layers_data[a:b]], [L.vc for L in layers_data[a:b]], d_slots, d_bt, d_sl,
+                    [L.k_scale for L in layers_data[a:b]], [L.v_scale for L in layers_data[a:b]],
+                    num_splits=args.num_splits, max_seq_len=max_seq, out=d_out[a:b], inputs_ready=True) for a, b in groups]
+
+        def e2e_enqueue_grouped():
+            main = torch.cuda.current_stream(device)
+            if len(groups) == 1:
+                d_in.copy_(h_in, non_blocking=True)
+                group_plans[0]()
+                h_out.copy_(d_out, non_blocking=True)
+                return
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+            ready_in = []
+            with torch.cuda.stream(s_in):
+                meta_d.copy_(meta_h, non_blocking=True)
+                for a, b in groups:
+                    d_in[a * per_layer:b * per_layer].copy_(h_in[a * per_layer:b * per_layer], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                    ready_in.append(ev)
+            for gi, (a, b) in enumerate(groups):
+                main.wait_event(ready_in[gi])
+                group_plans[gi]()
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(done)
+                    h_out[a:b].copy_(d_out[a:b], non_blocking=True)
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        def eager_grouped_step():
+            e2e_enqueue_grouped()
+            stream.synchronize()
+
+        e2e_eager_s = ctx.time_host(eager_grouped_step if chained_e2e else eager_step)
         with torch.cuda.stream(stream):
             # the same step through the L-layer entry point: one library call per step, arguments marshalled once
             plan = kv.DecodeStepLayers([dv[i][0] for i in range(layers)], [dv[i][1] for i in range(layers)],
@@ -810,20 +858,38 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
             stream.synchronize()
 
         e2e_layers_s = ctx.time_host(layers_step)
-        with torch.cuda.stream(stream):
-            g3 = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g3, stream=stream):
-                e2e_enqueue()
+        def graphed(enqueue):
+            with torch.cuda.stream(stream):
+                enqueue()  # once eagerly on this stream: workspaces reach their size before the capture
+                stream.synchronize()
+                g3 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g3, stream=stream):
+                    enqueue()
 
-        def graph_step():
-            g3.replay()
-            stream.synchronize()
+            def graph_step():
+                g3.replay()
+                stream.synchronize()
 
-        e2e_s = ctx.time_host(graph_step)
-        del g3, plan
+            return ctx.time_host(graph_step)
 
-    dev_ms, e2e_ms, e2e_eager_ms, bf16_ms, e2e_layers_ms, warm_ms = ctx.reduce(
-        [dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms, e2e_layers_s * 1e3, warm_ms], "max")
+        e2e_per_layer_s = graphed(e2e_enqueue)
+        per_layer_out = h_out.clone()
+        h_out.zero_()
+        e2e_s = graphed(e2e_enqueue_grouped) if chained_e2e else e2e_per_layer_s
+        # same inputs, same caches: the two variants differ at most in their split counts (bf16 rounding of the output)
+        e2e_agree = {"bit_identical": bool(torch.equal(h_out, per_layer_out)),
+                     "max_abs": float((h_out.float() - per_layer_out.float()).abs().max()),
+                     "largest_output": float(per_layer_out.float().abs().max())}
+        e2e_agree["ok"] = e2e_agree["max_abs"] <= 2e-2 * max(1.0, e2e_agree["largest_output"])
+        del plan
+        if chained_e2e:
+            del group_plans
+
+    dev_ms, e2e_ms, e2e_eager_ms, bf16_ms, e2e_layers_ms, warm_ms, e2e_per_layer_ms = ctx.reduce(
+        [dev_ms, e2e_s * 1e3, e2e_eager_s * 1e3, bf16_ms, e2e_layers_s * 1e3, warm_ms, e2e_per_layer_s * 1e3], "max")
+    e2e_graph_ms = e2e_ms
+    if args.launch == "chained" and e2e_eager_ms < e2e_ms:  # launched from Python it can be the faster of the two
+        e2e_ms, e2e_from = e2e_eager_ms, "launched from Python every step"
     mode_names = sorted(other_modes)
     mode_ms = dict(zip(mode_names, ctx.reduce([other_modes[m] for m in mode_names], "max"))) if mode_names else {}
     mode_ms[args.launch] = dev_ms
@@ -852,18 +918,25 @@ def leg_decode(ctx, name, hq, hkv, seq_lens, layers, config, sub=False):
         "clocks": clocks, "device_status": int(status), "shard_check": check,
         "e2e": {"value": total_step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": int(h2d_all), "d2h_bytes_per_step": int(d2h_all),
-                "ms_per_step": e2e_ms, "eager_ms_per_step": e2e_eager_ms,
+                "ms_per_step": e2e_ms, "graph_ms_per_step": e2e_graph_ms, "eager_ms_per_step": e2e_eager_ms,
                 "eager_value": total_step_bytes / (e2e_eager_ms * 1e-3) / 1e9,
                 "one_call_ms_per_step": e2e_layers_ms,
                 "one_call_value": total_step_bytes / (e2e_layers_ms * 1e-3) / 1e9,
+                "value_from": e2e_from,
+                "outputs_agree_with_per_layer_calls": e2e_agree,
+                "per_layer_calls_ms_per_step": e2e_per_layer_ms,
+                "per_layer_calls_value": total_step_bytes / (e2e_per_layer_ms * 1e-3) / 1e9,
                 "what": "per step and rank: pinned-host inputs (every layer's new q/k/v rows; block tables, seq_lens, "
-                        "slots) -> device, int8_decode_step (cache write + attention) per layer through the Python "
-                        "operators, every layer's output -> pinned host, all streams synchronised; the copies run on "
-                        "their own streams, layer by layer, beside the compute of the neighbouring layers (steps with less than a "
-                        "megabyte of input per layer copy once before and once after the layers instead); `value` "
-                        "replays the step as one CUDA graph, `eager_value` launches it from Python every step, "
-                        "`one_call_value` copies everything in, runs one int8kv_decode_step_layers call and copies "
-                        "everything out (no graph, no overlap); bytes are summed over ranks"},
+                        "slots) -> device, the decode step (cache write + attention) of every layer through the Python "
+                        "operators, every layer's output -> pinned host, all streams synchronised.  With --launch chained "
+                        "the layers run as int8kv_decode_step_layers calls over groups of 4 layers, a group's inputs "
+                        "travelling in beside the previous group's compute and its outputs out beside the next group's, "
+                        "on streams of their own (steps with less than a megabyte of input per layer are one group with "
+                        "one copy before and one after); the step is timed as one CUDA graph replay and launched from "
+                        "Python every step (`eager_value`), `value` is the faster of the two (`value_from`); `per_layer_calls_value` is a graph of one int8_decode_step "
+                        "call per layer with per-layer copies beside them (what `value` is under --launch per-call or "
+                        "ordered); `one_call_value` copies everything in, runs one int8kv_decode_step_layers call over "
+                        "all layers and copies everything out (no graph, no overlap); bytes are summed over ranks"},
         "l2_warm": {"us_per_call": warm_ms * 1e3 / layers,
                     "what": "the same calls repeated on one layer's cache (re-read from L2 when it fits): not the "
                             "headline, which reads a different cache per call"},
