@@ -274,6 +274,12 @@ __device__ __forceinline__ void mbar_fence_init() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Orders this thread's earlier ordinary writes to shared memory before later writes of the async proxy (TMA) to the
+// same bytes: a ring stage that lanes have written by hand must be fenced by those lanes before it is refilled.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // 4-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros and reads nothing.
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");

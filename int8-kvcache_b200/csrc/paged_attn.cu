@@ -699,6 +699,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
 #pragma unroll
     for (int i = 0; i < 32; ++i) qv[i] = 0.f;
   }
+  fence_proxy_async_smem();  // a staged query was written by the lanes; the first tile is written by the TMA unit
   __syncwarp();  // every lane is done with the staging area before the first tile may land in it
 
   const int n = it.t1 - it.t0;
@@ -806,6 +807,7 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
         fused_row_write(p.kc, p.vc, p.kc_st[0], p.kc_st[1], it.h * p.kc_st[2], p.vc_st[0], p.vc_st[1], it.h * p.vc_st[2],
                         p.num_blocks, p.block_size, it.seq_len - 1, new_slot, last_blk, nk[0], nk[1], nk[2], nk[3],
                         nv[0], nv[1], nv[2], nv[3], k_scale_head, v_scale_head, ring.stage(last_rel), p.status, lane);
+        fence_proxy_async_smem();  // the patched stage is refilled by the TMA unit at the end of this trip
         __syncwarp();
       }
     }
