@@ -1,11 +1,9 @@
 """The sequence-parallel exchange on ONE device: the kernels that store partial rows as {value, step number} pairs,
-and the merge that polls them, with both "ranks'" buffers in this GPU's memory.  What needs two GPUs (NVLink stores,
+and the merge that polls them, with every "rank's" buffer in this GPU's memory.  What needs two GPUs (NVLink stores,
 symmetric memory, two processes) is in test_gpu_sequence_parallel.py; this file covers the same kernels where only one
-GPU is visible: a world of one against the ordinary operator (bit-identical), two ranks emulated one after the other
-against the all-gather path's merge (bit-identical), CUDA-graph replay, and a rank that never pushes (the bounded wait
-runs out, the status word says so, the context stays usable)."""
-
-import ctypes as C
+GPU is visible: a world of one against the ordinary operator (bit-identical), two and nine ranks emulated one after
+the other against the all-gather path's merge (bit-identical), CUDA-graph replay, and a rank that never pushes (the
+bounded wait runs out, the status word says so, the context stays usable)."""
 
 import pytest
 import torch
@@ -57,14 +55,15 @@ def test_world_of_one_equals_the_ordinary_call(kv, workloads, num_splits):
     assert int(bufs[0][:8].view(torch.int32)[1]) == 3  # the step count lives in the buffer
 
 
-def test_two_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads):
-    """Two "ranks" on one device, run one after the other on one stream: rank 1 pushes into both buffers, then rank 0
-    pushes and merges (its wait finds everything there), then rank 1 merges.  Both must return what merge_partials
-    gives for the two ranks' rows stacked, bit for bit, eagerly and replayed as a CUDA graph."""
+@pytest.mark.parametrize("world", [2, 9])
+def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads, world):
+    """Several "ranks" on one device, run one after the other on one stream: all of them push into all buffers (the
+    last rank first), then each merges (its wait finds everything there).  All must return what merge_partials gives
+    for the ranks' rows stacked, bit for bit, eagerly and replayed as a CUDA graph.  Nine ranks make the merge take
+    the other ranks' rows in two batches."""
     lib_mod, sh = package("_lib"), package("sharding")
     lens = [2000, 333, 64, 1]
     case, kc, vc = _case(workloads, lens, seed=77)
-    world = 2
     rank_args = []
     for rank in range(world):
         lo, hi, local_lens = sh.sequence_split(lens, rank, world, 16)
@@ -91,9 +90,9 @@ def test_two_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, w
     outs = [torch.empty_like(want) for _ in range(world)]
 
     def step():
-        for r in (1, 0):
+        for r in reversed(range(world)):
             kv.int8_paged_attention_partial_push(*rank_args[r][0], exs[r], max_seq_len=rank_args[r][1])
-        for r in (0, 1):
+        for r in range(world):
             kv.merge_exchanged(exs[r], len(lens), 28, 128, out=outs[r])
 
     stream = torch.cuda.Stream()
@@ -101,7 +100,7 @@ def test_two_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, w
         for _ in range(2):
             step()
         stream.synchronize()
-        assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+        assert all(torch.equal(o, want) for o in outs)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
             step()
@@ -110,7 +109,7 @@ def test_two_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, w
                 o.zero_()
             g.replay()
         stream.synchronize()
-        assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+        assert all(torch.equal(o, want) for o in outs)
         assert kv.device_status() == 0
     del g
 
