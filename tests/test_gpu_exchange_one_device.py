@@ -34,11 +34,12 @@ def _case(wl, lens, seed):
     return case, kc, vc
 
 
-@pytest.mark.parametrize("num_splits", [None, 1, 4])
+@pytest.mark.parametrize("num_splits", [None, 1, 4, "planned"])
 def test_world_of_one_equals_the_ordinary_call(kv, workloads, num_splits):
     """One rank: its rows go through the slab and come back through the polling merge.  With one part per row that
     merge multiplies by 1 and divides by 1, so the output has the bits of int8_paged_attention with the same split
-    (automatic: the split-KV merge pushes; 1: the attention kernel stages and the copy kernel pushes; 4: forced)."""
+    (automatic, 4, planned on the device: the last part of every group merges and pushes inside the attention kernel,
+    sequences with a single part push what they staged; 1: the attention kernel stages and a copy kernel pushes)."""
     lib_mod = package("_lib")
     lens = [1500, 333, 64, 1, 0, 4096]
     case, kc, vc = _case(workloads, lens, seed=5)
@@ -55,8 +56,34 @@ def test_world_of_one_equals_the_ordinary_call(kv, workloads, num_splits):
     assert int(bufs[0][:8].view(torch.int32)[1]) == 3  # the step count lives in the buffer
 
 
-@pytest.mark.parametrize("world", [2, 9])
-def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads, world):
+@pytest.mark.parametrize("num_splits", ["planned", 8, None])
+def test_many_groups_with_few_parts_each_push_from_the_attention_kernel(kv, workloads, num_splits):
+    """64 ragged sequences x 4 kv heads: few parts per group, which is where the attention kernel's last part of a
+    group merges and pushes by itself (device-planned parts included, and sequences with a single part, an empty one
+    and a one-token one among them).  World of one: the bits of the ordinary call with the same split."""
+    lib_mod = package("_lib")
+    g = torch.Generator().manual_seed(11)
+    lens = [int(x) for x in torch.randint(1, 3000, (64,), generator=g)]
+    lens[3], lens[17], lens[40] = 0, 1, 2999
+    case, kc, vc = _case(workloads, lens, seed=21)
+    args = [t.to(DEV) for t in (case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)]
+    want = kv.int8_paged_attention(*args, num_splits=num_splits, max_seq_len=max(lens))
+    ref = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    assert max_abs(want.float().cpu(), ref.to(torch.bfloat16).float()) <= 2e-2
+    bufs = _buffers(lib_mod, 1, len(lens), 28, 128)
+    ex = _exchange(lib_mod, 1, 0, bufs)
+    for step in range(3):
+        kv.int8_paged_attention_partial_push(*args, ex, num_splits=num_splits, max_seq_len=max(lens))
+        got = kv.merge_exchanged(ex, len(lens), 28, 128, device=DEV)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"step {step}"
+    assert kv.device_status() == 0
+    counters = bufs[0][256:256 + 4 * len(lens) * 4].view(torch.int32)
+    assert int(counters.abs().max()) == 0  # every group's arrival counter is back at zero
+
+
+@pytest.mark.parametrize("world,num_splits", [(2, None), (9, None), (2, "planned"), (3, 1), (2, 6)])
+def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads, world, num_splits):
     """Several "ranks" on one device, run one after the other on one stream: all of them push into all buffers (the
     last rank first), then each merges (its wait finds everything there).  All must return what merge_partials gives
     for the ranks' rows stacked, bit for bit, eagerly and replayed as a CUDA graph.  Nine ranks make the merge take
@@ -80,7 +107,7 @@ def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workl
                 nxt += 1
         rank_args.append(([t.to(DEV) for t in (case.query, lkc, lvc, tables, torch.tensor(local_lens, dtype=torch.int32),
                                                case.k_scale, case.v_scale)], max(max(local_lens), 1)))
-    rows = torch.stack([kv.int8_paged_attention_partial(*a, max_seq_len=m) for a, m in rank_args])
+    rows = torch.stack([kv.int8_paged_attention_partial(*a, max_seq_len=m, num_splits=num_splits) for a, m in rank_args])
     want = kv.merge_partials(rows, 128)
     ref = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
     assert max_abs(want.float().cpu(), ref.to(torch.bfloat16).float()) <= 2e-2 and cosine(want.float().cpu(), ref) >= 0.9999
@@ -91,7 +118,8 @@ def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workl
 
     def step():
         for r in reversed(range(world)):
-            kv.int8_paged_attention_partial_push(*rank_args[r][0], exs[r], max_seq_len=rank_args[r][1])
+            kv.int8_paged_attention_partial_push(*rank_args[r][0], exs[r], max_seq_len=rank_args[r][1],
+                                                 num_splits=num_splits)
         for r in range(world):
             kv.merge_exchanged(exs[r], len(lens), 28, 128, out=outs[r])
 

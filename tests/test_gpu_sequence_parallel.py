@@ -88,6 +88,15 @@ def _worker(rank, world, port, ret):
         got_1 = out_1.float().cpu()
         unsplit_ok = max_abs(got_1, want.to(torch.bfloat16).float()) <= 2e-2 and cosine(got_1, want) >= 0.9999
         peer_equal = peer_equal and unsplit_ok
+        # few parts per (sequence, kv head) group: the attention kernel's last part of a group merges and pushes by
+        # itself, so the rows cross NVLink while other warps still stream; same bits as gathering the same rows
+        for _ in range(2):
+            kv.int8_paged_attention_partial_push(*args, peer.exchange, num_splits=6, max_seq_len=max(max(local_lens), 1))
+            out_6 = kv.merge_exchanged(peer.exchange, len(lens), 28, 128, device=dev)
+        rows_6 = kv.int8_paged_attention_partial(*args, num_splits=6, max_seq_len=max(max(local_lens), 1))
+        want_6 = kv.merge_partials(sh.gather_partials(rows_6), 128)
+        torch.cuda.synchronize()
+        peer_equal = peer_equal and bool(torch.equal(out_6, want_6))
         peer.close()
 
         # --- head x batch shard of this rank, no collective
