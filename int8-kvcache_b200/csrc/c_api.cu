@@ -217,8 +217,6 @@ PlanLayout plan_layout(int B, int Hq, int Hkv, int D, int max_items) {
   return l;
 }
 
-constexpr int kTailMaxParts = 8;  // most parts per (sequence, kv head) group for which the attention kernel merges and pushes itself
-
 struct AttnCall {
   const void* query; int q_dtype; const int64_t* q_st;
   int B, Hq, Hkv, D;
@@ -400,20 +398,6 @@ int run_attention(const AttnCall& a, Chain* chain = nullptr) {
     p.plan_min_part = ps.min_part;
     p.direct_part = a.partial_out;
   }
-  // Rows that go to the other ranks of a sequence split: the tiled INT8 kernel merges and pushes them itself
-  // when a group has few parts (measured, one GPU, 32 sequences x 8 kv heads: with 7 parts per group the tail costs
-  // 9 us and hides the 20 us the rows need on the links of eight GPUs; with 32 parts it costs 47 us, because the last
-  // wave's groups all finish together and each is merged by one warp, against 4 us for the merge kernel)
-  const int64_t groups = static_cast<int64_t>(a.B) * a.Hkv;
-  const int64_t parts_per_group = planned ? (ps.max_items + groups - 1) / groups : S;
-  const bool tail = a.push != nullptr && a.partial_out != nullptr && tiled && a.cache_kind == kCacheInt8 && !dyn &&
-                    !t.quantize_q && a.new_k == nullptr && (S > 1 || planned) && chain == nullptr &&
-                    parts_per_group <= kTailMaxParts;
-  if (tail) {
-    p.push_world = a.push->world;
-    p.push_rank = a.push->rank;
-    for (int r = 0; r < a.push->world; ++r) p.push_peer[r] = a.push->peer[r];
-  }
   // A merge left over from the previous layer rides on this launch when this launch can carry it (tiled kernels,
   // static scales, plain query); otherwise it gets its own launch first.
   const bool carry = chain != nullptr && chain->pending && tiled && !dyn && !t.quantize_q;
@@ -432,10 +416,6 @@ int run_attention(const AttnCall& a, Chain* chain = nullptr) {
     if (carry && rc == INT8KV_OK) chain->pending = false;
   } else {
     rc = launch_attn_generic(p, a.stream);
-  }
-  if (tail && rc == INT8KV_OK) {
-    if (a.pushed != nullptr) *a.pushed = true;
-    return rc;
   }
   if (rc != INT8KV_OK || S == 1) return rc;
 
@@ -637,10 +617,9 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
 
 int64_t int8kv_exchange_bytes(int world, int batch, int num_q_heads, int head_dim) {
   if (world <= 0 || world > kMaxPeers || batch < 0 || num_q_heads <= 0 || head_dim <= 0) return -1;
-  // control block | arrival counters | staging rows (fp32) | 2 slabs x world ranks x rows of (value, epoch) pairs
-  const int64_t rows = static_cast<int64_t>(batch) * num_q_heads;
-  const int64_t rows4 = rows * partial_row_floats(head_dim) * 4;
-  return exch_data_off(rows) + rows4 * (1 + 4 * static_cast<int64_t>(world));
+  // control block | staging rows (fp32) | 2 slabs x world ranks x rows of (value, epoch) pairs
+  const int64_t rows4 = static_cast<int64_t>(batch) * num_q_heads * partial_row_floats(head_dim) * 4;
+  return kExchCtrlBytes + rows4 * (1 + 4 * static_cast<int64_t>(world));
 }
 
 static int exchange_params(const int8kv_exchange* ex, int batch, int num_q_heads, int head_dim, ExchangeParams* e) {
@@ -674,7 +653,7 @@ int int8kv_paged_attn_int8_partial_push(const void* query, int q_dtype, const in
   int rc = exchange_params(exchange, batch, num_q_heads, head_dim, &e);
   if (rc != INT8KV_OK) return rc;
   if (batch == 0) return INT8KV_OK;
-  float* staging = reinterpret_cast<float*>(e.peer[e.rank] + exch_data_off(e.rows));
+  float* staging = reinterpret_cast<float*>(e.peer[e.rank] + kExchCtrlBytes);
   AttnCall a{query, q_dtype, q_strides, batch, num_q_heads, num_kv_heads, head_dim,
              key_cache, value_cache, kCacheInt8, key_cache_strides, value_cache_strides, num_blocks, block_size,
              block_tables, bt_is_i64, bt_strides, bt_width, seq_lens, sl_is_i64, max_seq_len_hint,
@@ -701,7 +680,7 @@ int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q
   MergeParams m;
   std::memset(&m, 0, sizeof(m));
   const int64_t rank_floats = e.rows * e.row_floats;  // floats of one rank's rows
-  m.parts = reinterpret_cast<const float*>(e.peer[e.rank] + exch_data_off(e.rows)) + rank_floats;  // slab 0 follows the staging
+  m.parts = reinterpret_cast<const float*>(e.peer[e.rank] + kExchCtrlBytes) + rank_floats;  // slab 0 follows the staging
   m.R = e.world; m.rows = e.rows; m.Hq = num_q_heads; m.D = head_dim; m.row_floats = e.row_floats;
   m.out = out; m.out_dtype = out_dtype;
   for (int i = 0; i < 3; ++i) m.o_st[i] = out_strides[i];

@@ -252,24 +252,6 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// 16- and 8-byte accesses that are neither cached in L1 nor reordered with one another: the (value, epoch) pairs of
-// the sequence-parallel exchange
-__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void st_volatile_v2(void* p, uint2 v) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-}
 // Attempts of a wait for another GPU's flag: 100 ns to 1 us apart, so the limit gives up after about a second.
 constexpr uint32_t kFlagSpinLimit = 1u << 20;
 

@@ -47,9 +47,6 @@ struct DynWriteParams {
 // cache element kinds
 enum CacheKind { kCacheInt8 = 0, kCacheBf16 = 1, kCacheFp16 = 2 };
 
-constexpr int kMaxPeers = 16;       // ranks of a sequence-parallel exchange
-constexpr int kExchCtrlBytes = 256;  // control block at the head of an exchange buffer
-
 struct AttnParams {
   const void* q;
   int q_dtype;
@@ -108,22 +105,16 @@ struct AttnParams {
   int plan_slots;       // resident warps of the kernel on the device
   int plan_k_max;       // most waves to aim for
   int plan_min_part;    // shortest part (tiles) the plan may choose when it aims for more than one wave
-  // Sequence-parallel tail (push_world > 0; tiled INT8 kernel, static scales, parts in the workspace): the last part
-  // of a (sequence, kv head) group to finish merges the group's rows and stores them as (value, epoch) pairs into
-  // every rank's exchange buffer, so the rows leave while the other warps still stream.  See ExchangeParams.
-  int push_world, push_rank;
-  char* push_peer[kMaxPeers];
 };
 
 // Cross-GPU exchange of partial rows through peer-mapped buffers (sequence-parallel attention).  Every rank owns one
 // buffer of the same layout, mapped into every other rank's address space:
-//   [0, 256)            control words of the owner: {ticket of the merge's CTAs, epoch = steps completed}
-//   [256, data)         arrival counters, one per (sequence, kv head) group (room for rows = B * Hq of them), zero
-//                       between calls: the parts of a group count themselves in, the last one merges and pushes
-//   [data, ...)         staging [rows, row_floats] fp32: rows that a kernel leaves for a separate push
-//   then                2 slabs x [world, rows, row_floats] pairs {fp32 value, epoch}, used alternately (epoch
-//                       parity): slab[s][q] = rows of rank q
-__host__ __device__ inline int64_t exch_data_off(int64_t rows) { return kExchCtrlBytes + (rows * 4 + 255) / 256 * 256; }
+//   [0, 64)     control words of the owner: {ticket of the push kernel's CTAs, epoch = pushes completed}
+//   [64, 256)   arrival flags: flag[q] = epoch of the last push of rank q whose rows have landed in this buffer
+//   [256, ...)  staging [rows, row_floats]: the owner's own partial rows before they are pushed
+//   then        2 slabs x [world, rows, row_floats] fp32, used alternately (epoch parity): slab[s][q] = rows of rank q
+constexpr int kMaxPeers = 16;
+constexpr int kExchCtrlBytes = 256;
 struct ExchangeParams {
   int world, rank;
   char* peer[kMaxPeers];  // base of every rank's buffer as mapped here; peer[rank] is the local buffer

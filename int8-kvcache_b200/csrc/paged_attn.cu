@@ -163,8 +163,6 @@ struct ItemCoord {
   int b, h, c;       // sequence, kv head, split
   int seq_len;       // tokens of the sequence (clamped to what the table can address)
   int t0, t1;        // tile range of this split
-  int parts;         // parts whose rows make up this sequence's result (arithmetic numbering: num_splits, empty ones too)
-  int first_part;    // device-planned splits: index of the sequence's first part; -1 with arithmetic numbering
 };
 
 // Which (sequence, kv head, split) a work item is: arithmetic only.
@@ -204,8 +202,6 @@ __device__ __forceinline__ void item_range(const AttnParams& p, ItemCoord& it) {
   const int per = static_cast<int>(static_cast<uint32_t>(ntiles + used - 1) / static_cast<uint32_t>(used));
   it.t0 = it.c * per;
   it.t1 = it.c < used ? min(it.t0 + per, ntiles) : it.t0;
-  it.parts = p.num_splits;
-  it.first_part = -1;
 }
 
 // Device-planned splits.  Every sequence is cut into parts of one common length P (in 16-token tiles), the smallest
@@ -354,8 +350,6 @@ __device__ __forceinline__ bool plan_in_warp(const AttnParams& p, int64_t item, 
   const int per = (tiles + used - 1) / used;
   it.t0 = min(it.c * per, tiles);
   it.t1 = min(it.t0 + per, tiles);
-  it.parts = used;
-  it.first_part = part - it.c;
   row0 = used == 1 ? -1 : static_cast<int64_t>(part) * p.Hq + it.h * p.G;
   if (it.c == 0 && it.h == 0) {
     note.table_b = it.b;
@@ -399,16 +393,24 @@ __device__ __forceinline__ void write_empty(const AttnParams& p, const ItemCoord
 // arithmetic as merge_partials_kernel: weights exp(lse_r - max lse), parts with lse = -inf never read, all-empty
 // rows give zeros.
 // ---------------------------------------------------------------------------------------------
-// The arithmetic: lane's piece `a` of the merged row (floats 4 * lane .. 4 * lane + 3 of head_dim 128) and the row's
-// log-sum-exp, from R parts whose rows start at base + r * stride_r.
-__device__ __forceinline__ void merge_row_core(const float* base, int64_t stride_r, int R, int D, int lane, float4& a,
-                                               float& lse_out) {
+__device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t row, int lane) {
+  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
+  int64_t stride_r = p.rows * p.row_floats;
+  const float* base = p.parts + row * p.row_floats;
+  int R = p.R;
+  if (p.seq_table != nullptr) {
+    const int2 e = __ldcg(p.seq_table + b);
+    if (e.y <= 1) return;  // a single part went straight to the output
+    R = e.y < kMaxSplits ? e.y : kMaxSplits;
+    stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
+    base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
+  }
   constexpr int kTrip = 16;  // parts whose rows are in flight together
   float w[kMaxSplits / kWarp], top = -INFINITY;
 #pragma unroll
   for (int j = 0; j < kMaxSplits / kWarp; ++j) {
     const int r = lane + kWarp * j;
-    w[j] = r < R ? __ldcg(base + r * stride_r + D) : -INFINITY;
+    w[j] = r < R ? __ldcg(base + r * stride_r + p.D) : -INFINITY;
   }
   // The rows of the first trip are requested before the weights exist, so that both reads share one latency.  Rows
   // of empty parts were never written: whatever they hold is discarded by the weight test below.
@@ -451,28 +453,11 @@ __device__ __forceinline__ void merge_row_core(const float* base, int64_t stride
       }
     }
   }
+  float4 a;
   a.x = (acc[0].x + acc[1].x + acc[2].x + acc[3].x) * inv;
   a.y = (acc[0].y + acc[1].y + acc[2].y + acc[3].y) * inv;
   a.z = (acc[0].z + acc[1].z + acc[2].z + acc[3].z) * inv;
   a.w = (acc[0].w + acc[1].w + acc[2].w + acc[3].w) * inv;
-  lse_out = den > 0.f ? top + __logf(den) : -INFINITY;  // as merge_partials_kernel writes it
-}
-
-__device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t row, int lane) {
-  const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
-  int64_t stride_r = p.rows * p.row_floats;
-  const float* base = p.parts + row * p.row_floats;
-  int R = p.R;
-  if (p.seq_table != nullptr) {
-    const int2 e = __ldcg(p.seq_table + b);
-    if (e.y <= 1) return;  // a single part went straight to the output
-    R = e.y < kMaxSplits ? e.y : kMaxSplits;
-    stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
-    base = p.parts + (static_cast<int64_t>(e.x) * p.Hq + hq) * p.row_floats;
-  }
-  float4 a;
-  float lse;
-  merge_row_core(base, stride_r, R, p.D, lane, a, lse);
   const int d = 4 * lane;
   const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
   if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && ((reinterpret_cast<uintptr_t>(p.out) + 2 * (ob + d)) & 7u) == 0) {
@@ -485,131 +470,6 @@ __device__ __forceinline__ void merge_row_by_warp(const MergeParams& p, int64_t 
     store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
     store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
     store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Sequence-parallel tail of the tiled INT8 kernel (AttnParams::push_world > 0): compute and collective in one kernel.
-// Every part of a (sequence, kv head) group counts itself in when its rows are in the workspace; the part that
-// arrives last merges the group's rows (merge_row_core: the bits of merge_partials_kernel) and stores each merged row
-// (out | lse) as {value, epoch} pairs into slab[epoch & 1][rank] of EVERY rank's exchange buffer — plain 16-byte
-// stores to peer-mapped memory, no TMA, no multicast, no fence towards the other GPUs (see exchange_push_kernel for
-// the protocol).  The rows therefore cross NVLink while the other warps of the kernel still stream their pages, and
-// the call needs neither a merge launch nor a push launch.  The counters live in the local exchange buffer, which
-// is zero before first use; the last part to arrive sets its counter back to zero for the next call.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void push_row_pairs(const AttnParams& p, uint32_t epoch, int64_t row, float4 a, float lse, int lane) {
-  const int64_t rows = static_cast<int64_t>(p.B) * p.Hq;
-  const int64_t rank_floats = rows * p.row_floats;
-  const int64_t off = exch_data_off(rows) + rank_floats * 4 +
-                      (((epoch & 1u) * p.push_world + p.push_rank) * rank_floats + row * p.row_floats) * 8;
-  const uint4 lo = make_uint4(__float_as_uint(a.x), epoch, __float_as_uint(a.y), epoch);
-  const uint4 hi = make_uint4(__float_as_uint(a.z), epoch, __float_as_uint(a.w), epoch);
-  for (int r = 0; r < p.push_world; ++r) {
-    char* dst = p.push_peer[r] + off;
-    st_volatile_v4(dst + 32 * lane, lo);
-    st_volatile_v4(dst + 32 * lane + 16, hi);
-    if (lane == 0) st_volatile_v2(dst + 8 * p.D, make_uint2(__float_as_uint(lse), epoch));
-  }
-}
-
-// Two rows of at most eight parts each, merged side by side (all sixteen part rows in flight together): the
-// arithmetic of merge_row_core, operation for operation.
-__device__ __forceinline__ void merge_two_rows_small(const float* base0, const float* base1, int64_t stride_r, int R, int D,
-                                                     int lane, float4 (&a)[2], float (&lse_out)[2]) {
-  const float* base[2] = {base0, base1};
-  float lw[2];
-  float4 o[2][8];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    lw[i] = lane < R ? __ldcg(base[i] + lane * stride_r + D) : -INFINITY;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      o[i][u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (u < R) o[i][u] = __ldcg(reinterpret_cast<const float4*>(base[i] + u * stride_r + 4 * lane));
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    float top = lw[i];
-    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(kFull, top, off));
-    const float w = lw[i] == -INFINITY ? 0.f : __expf(lw[i] - top);
-    float den = w;
-    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(kFull, den, off);
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    float4 acc[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const float wr = u < R ? __shfl_sync(kFull, w, u) : 0.f;
-      if (wr > 0.f) {
-        float4& x = acc[u & 3];
-        x.x += wr * o[i][u].x; x.y += wr * o[i][u].y; x.z += wr * o[i][u].z; x.w += wr * o[i][u].w;
-      }
-    }
-    a[i].x = (acc[0].x + acc[1].x + acc[2].x + acc[3].x) * inv;
-    a[i].y = (acc[0].y + acc[1].y + acc[2].y + acc[3].y) * inv;
-    a[i].z = (acc[0].z + acc[1].z + acc[2].z + acc[3].z) * inv;
-    a[i].w = (acc[0].w + acc[1].w + acc[2].w + acc[3].w) * inv;
-    lse_out[i] = den > 0.f ? top + __logf(den) : -INFINITY;
-  }
-}
-
-__device__ __forceinline__ void tail_push(const AttnParams& p, const ItemCoord& it, int lane) {
-  char* local = p.push_peer[p.push_rank];
-  const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(local) + 1)) + 1u;
-  const int64_t rows = static_cast<int64_t>(p.B) * p.Hq;
-  if (it.parts > 1) {
-    __threadfence();  // this warp's partial rows are visible before its arrival is
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      int* counter = reinterpret_cast<int*>(local + kExchCtrlBytes) + it.b * p.Hkv + it.h;
-      last = atomicAdd(counter, 1) == it.parts - 1;
-      if (last) *counter = 0;  // nobody touches it again before the next call
-    }
-    last = __shfl_sync(kFull, last, 0);
-    if (!last) return;
-    __threadfence();  // the other parts' arrivals are seen: so are their rows
-    // the group's first row in part 0, and the distance between parts
-    const int hq0 = it.h * p.G;
-    const float* base0;
-    int64_t stride_r;
-    if (it.first_part >= 0) {  // device-planned parts: consecutive part indices
-      base0 = p.part + (static_cast<int64_t>(it.first_part) * p.Hq + hq0) * p.row_floats;
-      stride_r = static_cast<int64_t>(p.Hq) * p.row_floats;
-    } else {
-      base0 = p.part + (static_cast<int64_t>(it.b) * p.Hq + hq0) * p.row_floats;
-      stride_r = rows * p.row_floats;
-    }
-    const int64_t out_row0 = static_cast<int64_t>(it.b) * p.Hq + hq0;
-    if (it.parts <= 8) {
-      for (int hg = 0; hg < p.G; hg += 2) {
-        const int second = hg + 1 < p.G ? hg + 1 : hg;
-        float4 a[2];
-        float lse[2];
-        merge_two_rows_small(base0 + hg * p.row_floats, base0 + second * p.row_floats, stride_r, it.parts, p.D, lane, a, lse);
-        push_row_pairs(p, epoch, out_row0 + hg, a[0], lse[0], lane);
-        if (second != hg) push_row_pairs(p, epoch, out_row0 + second, a[1], lse[1], lane);
-      }
-    } else {
-      for (int hg = 0; hg < p.G; ++hg) {
-        float4 a;
-        float lse;
-        merge_row_core(base0 + hg * p.row_floats, stride_r, it.parts, p.D, lane, a, lse);
-        push_row_pairs(p, epoch, out_row0 + hg, a, lse, lane);
-      }
-    }
-  } else {
-    // a planned sequence with a single part: this warp has just left its final rows in the staging area
-    __syncwarp();
-    const float* staged = p.direct_part + (static_cast<int64_t>(it.b) * p.Hq + it.h * p.G) * p.row_floats;
-    for (int hg = 0; hg < p.G; ++hg) {
-      const float4 a = __ldcg(reinterpret_cast<const float4*>(staged + hg * p.row_floats) + lane);
-      const float lse = __ldcg(staged + hg * p.row_floats + p.D);
-      push_row_pairs(p, epoch, static_cast<int64_t>(it.b) * p.Hq + it.h * p.G + hg, a, lse, lane);
-    }
   }
 }
 
@@ -713,7 +573,7 @@ __device__ __noinline__ void fused_row_write(const void* kc, const void* vc, int
 // than a run-time test, so that the kernel that serves small calls does not carry the planning code.
 // QQ: the reference's optional INT8 query (quantize_q), one limb; its own instantiation as well.
 // CHAINED: the CTAs behind the attention items merge the previous layer's partial rows (chained_merge).
-template <int NST, int MODE, bool PLANNED, bool QQ, bool CHAINED, bool TAIL = false>
+template <int NST, int MODE, bool PLANNED, bool QQ, bool CHAINED>
 __global__ void __launch_bounds__(kTiledWarpsPerCta * kWarp, 3)
 paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                        const AttnParams p, const ChainedMerge cm) {
@@ -815,7 +675,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
   if (it.t0 >= it.t1) {  // nothing was issued yet, so the warp may leave
     resolve_dependency();
     write_empty(p, it, lane, prow);
-    if constexpr (TAIL) tail_push(p, it, lane);
     merge_duty();
     return;
   }
@@ -1094,7 +953,6 @@ paged_attn_int8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_con
       if (g == 0) row[p.D] = l > 0.f ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
-  if constexpr (TAIL) tail_push(p, it, lane);
   merge_duty();
 }
 
@@ -1897,6 +1755,26 @@ __global__ void __launch_bounds__(128, GM == 4 ? 4 : (GM == 8 ? 3 : 2)) paged_at
 // ---------------------------------------------------------------------------------------------
 constexpr int kMergeWarps = 4;
 
+// 16- and 8-byte accesses that are neither cached in L1 nor reordered with one another: the (value, epoch) pairs of
+// the sequence-parallel exchange (see exchange_push_kernel)
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void st_volatile_v2(void* p, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
 template <bool PUSH>
 struct PushTarget {};
 template <>
@@ -1929,7 +1807,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
     const ExchangeParams& e = push.e;
     push_epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
     const int64_t rank_floats = e.rows * e.row_floats;
-    push_off = exch_data_off(e.rows) + rank_floats * 4 + (((push_epoch & 1u) * e.world + e.rank) * rank_floats + row * p.row_floats) * 8;
+    push_off = kExchCtrlBytes + rank_floats * 4 + (((push_epoch & 1u) * e.world + e.rank) * rank_floats + row * p.row_floats) * 8;
   }
   if (p.seq_table != nullptr) {
     // device-planned splits: this sequence's parts are consecutive part indices; a single part was written to
@@ -2068,8 +1946,8 @@ __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams
   const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
   const int64_t rank_floats = e.rows * e.row_floats;
   const int64_t n4 = rank_floats / 4;  // row_floats is a multiple of 4
-  const float4* src = reinterpret_cast<const float4*>(e.peer[e.rank] + exch_data_off(e.rows));
-  const int64_t dst_off = exch_data_off(e.rows) + rank_floats * 4 + ((epoch & 1u) * e.world + e.rank) * rank_floats * 8;
+  const float4* src = reinterpret_cast<const float4*>(e.peer[e.rank] + kExchCtrlBytes);
+  const int64_t dst_off = kExchCtrlBytes + rank_floats * 4 + ((epoch & 1u) * e.world + e.rank) * rank_floats * 8;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const float4 v = __ldcg(src + i);
@@ -2308,12 +2186,12 @@ static TiledGrid tiled_grid(const AttnParams& p, int64_t items, int wpc, int cta
 }
 
 // One instantiation of the INT8 kernel: raises its dynamic shared-memory limit once, sizes the grid, launches.
-template <int NST, int MODE, bool PLANNED, bool QQ = false, bool CHAINED = false, bool TAIL = false>
+template <int NST, int MODE, bool PLANNED, bool QQ = false, bool CHAINED = false>
 static int launch_int8_variant(const AttnParams& p, const CUtensorMap& tmK, const CUtensorMap& tmV, int sm_count,
                                cudaStream_t stream, const MergeParams* prev = nullptr) {
   constexpr int per_warp = NST * (4096 + 8 + (MODE == kDynScales ? 128 : 0));  // stages, barriers, scale slots
-  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED, QQ, CHAINED, TAIL>;
-  if (set_smem<100 + NST * 32 + MODE * 8 + (PLANNED ? 4 : 0) + (QQ ? 2 : 0) + (CHAINED ? 1 : 0) + (TAIL ? 1000 : 0)>(
+  auto kernel = paged_attn_int8_kernel<NST, MODE, PLANNED, QQ, CHAINED>;
+  if (set_smem<100 + NST * 32 + MODE * 8 + (PLANNED ? 4 : 0) + (QQ ? 2 : 0) + (CHAINED ? 1 : 0)>(
           kernel, kTiledWarpsPerCta * per_warp + 1024) != 0)
     return INT8KV_E_LAUNCH;
   const int64_t items = grid_items(p);
@@ -2330,9 +2208,6 @@ int launch_attn_tiled_int8(const AttnParams& p, const CUtensorMap& tmK, const CU
                            cudaStream_t stream, const MergeParams* prev) {
   constexpr int N = kInt8Stages;
   const bool planned = p.plan_table != nullptr;
-  if (p.push_world > 0)  // sequence-parallel tail: static scales, plain query, no fused write, nothing carried
-    return planned ? launch_int8_variant<N, kPlain, true, false, false, true>(p, tmK, tmV, sm_count, stream)
-                   : launch_int8_variant<N, kPlain, false, false, false, true>(p, tmK, tmV, sm_count, stream);
   if (prev != nullptr && prev->rows > 0) {  // static scales, no INT8 query: the caller has checked
     if (planned)
       return p.new_k != nullptr ? launch_int8_variant<N, kFusedWrite, true, false, true>(p, tmK, tmV, sm_count, stream, prev)

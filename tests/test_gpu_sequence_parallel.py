@@ -88,8 +88,7 @@ def _worker(rank, world, port, ret):
         got_1 = out_1.float().cpu()
         unsplit_ok = max_abs(got_1, want.to(torch.bfloat16).float()) <= 2e-2 and cosine(got_1, want) >= 0.9999
         peer_equal = peer_equal and unsplit_ok
-        # few parts per (sequence, kv head) group: the attention kernel's last part of a group merges and pushes by
-        # itself, so the rows cross NVLink while other warps still stream; same bits as gathering the same rows
+        # a forced split count: same bits as gathering the same rows through NCCL
         for _ in range(2):
             kv.int8_paged_attention_partial_push(*args, peer.exchange, num_splits=6, max_seq_len=max(max(local_lens), 1))
             out_6 = kv.merge_exchanged(peer.exchange, len(lens), 28, 128, device=dev)
