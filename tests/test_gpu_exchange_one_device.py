@@ -26,9 +26,10 @@ def _buffers(lib_mod, world, B, Hq, D):
     return [torch.zeros(n, dtype=torch.uint8, device=DEV) for _ in range(world)]
 
 
-def _case(wl, lens, seed):
-    case = wl.make_decode_case(lens, wl.QWEN25_7B, seed=seed)
-    kc = torch.zeros(case.num_blocks, 16, 4, 128, dtype=torch.int8)
+def _case(wl, lens, seed, shape=None):
+    shape = shape or wl.QWEN25_7B
+    case = wl.make_decode_case(lens, shape, seed=seed)
+    kc = torch.zeros(case.num_blocks, shape.block_size, shape.num_kv_heads, shape.head_dim, dtype=torch.int8)
     vc = torch.zeros_like(kc)
     oracle.cache_write(case.key, case.value, kc, vc, case.slot_mapping, case.k_scale, case.v_scale)
     return case, kc, vc
@@ -54,6 +55,28 @@ def test_world_of_one_equals_the_ordinary_call(kv, workloads, num_splits):
         assert torch.equal(got, want), f"step {step}"
     assert kv.device_status() == 0
     assert int(bufs[0][:8].view(torch.int32)[1]) == 3  # the step count lives in the buffer
+
+
+@pytest.mark.parametrize("hq,hkv,d,num_splits", [(8, 2, 64, None), (8, 2, 64, 1), (6, 2, 66, 3), (16, 1, 256, None)])
+def test_head_dims_outside_the_tiled_kernels_go_through_the_exchange(kv, workloads, hq, hkv, d, num_splits):
+    """Head dims 64, 66 (not a multiple of 4: the row's last 16-byte piece holds the lse and padding) and 256 (two
+    pieces per lane in the merge): world of one, the bits of the ordinary call."""
+    lib_mod = package("_lib")
+    shape = workloads.LayerShape(hq, hkv, d, 16)
+    lens = [700, 33, 1, 0, 257]
+    case, kc, vc = _case(workloads, lens, seed=3, shape=shape)
+    args = [t.to(DEV) for t in (case.query, kc, vc, case.block_tables, case.seq_lens, case.k_scale, case.v_scale)]
+    want = kv.int8_paged_attention(*args, num_splits=num_splits, max_seq_len=max(lens))
+    ref = oracle.int8_paged_attention_oracle(case.query, kc, vc, case.block_tables, lens, case.k_scale, case.v_scale)
+    assert max_abs(want.float().cpu(), ref.to(torch.bfloat16).float()) <= 2e-2
+    bufs = _buffers(lib_mod, 1, len(lens), hq, d)
+    ex = _exchange(lib_mod, 1, 0, bufs)
+    for step in range(2):
+        kv.int8_paged_attention_partial_push(*args, ex, num_splits=num_splits, max_seq_len=max(lens))
+        got = kv.merge_exchanged(ex, len(lens), hq, d, device=DEV)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"step {step}"
+    assert kv.device_status() == 0
 
 
 @pytest.mark.parametrize("num_splits", ["planned", 8, None])
