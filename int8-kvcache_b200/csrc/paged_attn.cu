@@ -1815,15 +1815,11 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
     const int2 e = __ldg(p.seq_table + b);
     if (e.y <= 1) {
       if constexpr (PUSH) {  // ... or, here, to the staging area: forward the row
-        if (static_cast<int>(threadIdx.x) * 4 < p.row_floats) {
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_out + row * p.row_floats) + threadIdx.x);
-          const uint4 lo = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
-          const uint4 hi = make_uint4(__float_as_uint(v.z), push_epoch, __float_as_uint(v.w), push_epoch);
-          for (int r = 0; r < push.e.world; ++r) {
-            char* dst = push.e.peer[r] + push_off + 32 * threadIdx.x;
-            st_volatile_v4(dst, lo);
-            st_volatile_v4(dst + 16, hi);
-          }
+        // two floats -> one 16-byte store per thread: a warp's store covers 512 consecutive bytes
+        for (int t = threadIdx.x; 2 * t < p.row_floats; t += blockDim.x) {
+          const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_out + row * p.row_floats) + t);
+          const uint4 q = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
+          for (int r = 0; r < push.e.world; ++r) st_volatile_v4(push.e.peer[r] + push_off + 16 * t, q);
         }
       }
       return;
@@ -1888,13 +1884,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
       a.z = (a.z + x1.z + x2.z + x3.z) * inv;
       a.w = (a.w + x1.w + x2.w + x3.w) * inv;
       if constexpr (PUSH) {
-        const uint4 lo = make_uint4(__float_as_uint(a.x), push_epoch, __float_as_uint(a.y), push_epoch);
-        const uint4 hi = make_uint4(__float_as_uint(a.z), push_epoch, __float_as_uint(a.w), push_epoch);
-        for (int r = 0; r < push.e.world; ++r) {
-          char* dst = push.e.peer[r] + push_off + 8 * d;
-          st_volatile_v4(dst, lo);
-          st_volatile_v4(dst + 16, hi);
-        }
+        *reinterpret_cast<float4*>(&red_s[0][4 * lane]) = a;  // this lane's own slot: stored below by two warps
       } else if (p.part_out != nullptr) {
         *reinterpret_cast<float4*>(p.part_out + row * p.row_floats + d) = a;
       } else if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
@@ -1912,6 +1902,17 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
       }
     }
     __syncthreads();
+    if constexpr (PUSH) {
+      // the chunk's merged floats leave as pairs, two floats -> one 16-byte store per thread, so that every store
+      // instruction of a warp covers 512 consecutive bytes of the peer's slab (whole 128-byte lines on the links)
+      const int t = threadIdx.x;
+      if (t < 2 * kWarp && d0 + 2 * t < p.D) {
+        const float2 v = *reinterpret_cast<const float2*>(&red_s[0][2 * t]);
+        const uint4 q = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
+        for (int r = 0; r < push.e.world; ++r) st_volatile_v4(push.e.peer[r] + push_off + 8 * d0 + 16 * t, q);
+      }
+      __syncthreads();  // before the next chunk reuses the slot
+    }
   }
   if constexpr (PUSH) {
     if (threadIdx.x == 0) {
@@ -1945,19 +1946,15 @@ __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams
   grid_launch_dependents();
   const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
   const int64_t rank_floats = e.rows * e.row_floats;
-  const int64_t n4 = rank_floats / 4;  // row_floats is a multiple of 4
-  const float4* src = reinterpret_cast<const float4*>(e.peer[e.rank] + kExchCtrlBytes);
+  const int64_t n2 = rank_floats / 2;  // row_floats is a multiple of 4
+  const float2* src = reinterpret_cast<const float2*>(e.peer[e.rank] + kExchCtrlBytes);
   const int64_t dst_off = kExchCtrlBytes + rank_floats * 4 + ((epoch & 1u) * e.world + e.rank) * rank_floats * 8;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+  // two floats -> one 16-byte store per thread: a warp's store instruction covers 512 consecutive bytes
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n2;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float4 v = __ldcg(src + i);
-    const uint4 lo = make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
-    const uint4 hi = make_uint4(__float_as_uint(v.z), epoch, __float_as_uint(v.w), epoch);
-    for (int r = 0; r < e.world; ++r) {
-      char* dst = e.peer[r] + dst_off + 32 * i;
-      st_volatile_v4(dst, lo);
-      st_volatile_v4(dst + 16, hi);
-    }
+    const float2 v = __ldcg(src + i);
+    const uint4 q = make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
+    for (int r = 0; r < e.world; ++r) st_volatile_v4(e.peer[r] + dst_off + 16 * i, q);
   }
 }
 
@@ -2084,9 +2081,9 @@ __global__ void __launch_bounds__(kExchMergeWarps * kWarp) merge_exchanged_kerne
 }
 
 int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream) {
-  const int64_t n4 = e.rows * e.row_floats / 4;
-  if (n4 <= 0) return INT8KV_OK;
-  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n4 + 255) / 256, 148 * 4));
+  const int64_t n2 = e.rows * e.row_floats / 2;
+  if (n2 <= 0) return INT8KV_OK;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n2 + 255) / 256, 148 * 8));
   return launch_pdl(exchange_push_kernel, grid, 256, 0, stream, e);
 }
 
