@@ -42,6 +42,9 @@ class LayerArgs(C.Structure):
     ]
 
 
+EXCHANGE_BOTH_PHASES, EXCHANGE_MERGE_PHASE, EXCHANGE_GATHER_PHASE = 0, 1, 2  # int8kv_merge_exchanged_phase
+
+
 class Exchange(C.Structure):
     """int8kv_exchange of include/int8kv_b200.h: the peer-mapped buffers of the sequence-parallel exchange."""
 
@@ -129,6 +132,9 @@ _SIGNATURES = {
     ),
     "int8kv_merge_exchanged": (
         C.c_int, [C.POINTER(Exchange), C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP, C.c_int64, _VP],
+    ),
+    "int8kv_merge_exchanged_phase": (
+        C.c_int, [C.POINTER(Exchange), C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP, C.c_int64, C.c_int, _VP],
     ),
     "int8kv_selftest_bounded_wait": (C.c_int, [_VP, C.c_int64, C.c_int, _VP]),
     "int8kv_merge_partials": (C.c_int, [_VP, C.c_int, C.c_int, C.c_int, C.c_int, _VP, C.c_int, _I64P, _VP]),

@@ -617,10 +617,12 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
 
 int64_t int8kv_exchange_bytes(int world, int batch, int num_q_heads, int head_dim) {
   if (world <= 0 || world > kMaxPeers || batch < 0 || num_q_heads <= 0 || head_dim <= 0) return -1;
-  // control block | staging rows (fp32) | 2 slabs x world ranks x rows of (value, epoch) pairs
-  const int64_t rows4 = static_cast<int64_t>(batch) * num_q_heads * partial_row_floats(head_dim) * 4;
-  return kExchCtrlBytes + rows4 * (1 + 4 * static_cast<int64_t>(world));
+  // control block | staging rows (fp32) | 2 slabs x world ranks x rows of (value, epoch) pairs | output slab of pairs
+  const int64_t rows = static_cast<int64_t>(batch) * num_q_heads;
+  return exch_out_off(world, rows, partial_row_floats(head_dim)) + rows * ((head_dim + 3) / 4 * 4) * 8;
 }
+
+constexpr int kScatterMinWorld = 8;  // ranks from which the exchange scatters rows to owners instead of sending all to all
 
 static int exchange_params(const int8kv_exchange* ex, int batch, int num_q_heads, int head_dim, ExchangeParams* e) {
   if (ex == nullptr) return INT8KV_E_NULLPTR;
@@ -636,6 +638,10 @@ static int exchange_params(const int8kv_exchange* ex, int batch, int num_q_heads
   }
   e->rows = static_cast<int64_t>(batch) * num_q_heads;
   e->row_floats = partial_row_floats(head_dim);
+  e->out_floats = (head_dim + 3) / 4 * 4;
+  // many ranks: a row goes to one owner, the owner sends the merged row to everyone (measured on eight GPUs against
+  // sending every row to every rank: 15 MB of pairs per rank and step become 3.7 MB)
+  e->scatter = ex->world >= kScatterMinWorld && e->rows % ex->world == 0 && e->rows > 0;
   return INT8KV_OK;
 }
 
@@ -670,6 +676,15 @@ int int8kv_paged_attn_int8_partial_push(const void* query, int q_dtype, const in
 int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q_heads, int head_dim, void* out,
                            int out_dtype, const int64_t out_strides[3], void* workspace, int64_t workspace_bytes,
                            void* stream) {
+  return int8kv_merge_exchanged_phase(exchange, batch, num_q_heads, head_dim, out, out_dtype, out_strides, workspace,
+                                      workspace_bytes, INT8KV_EXCHANGE_BOTH_PHASES, stream);
+}
+
+int int8kv_merge_exchanged_phase(const int8kv_exchange* exchange, int batch, int num_q_heads, int head_dim, void* out,
+                                 int out_dtype, const int64_t out_strides[3], void* workspace, int64_t workspace_bytes,
+                                 int phase, void* stream) {
+  if (phase != INT8KV_EXCHANGE_BOTH_PHASES && phase != INT8KV_EXCHANGE_MERGE_PHASE && phase != INT8KV_EXCHANGE_GATHER_PHASE)
+    return INT8KV_E_BAD_SHAPE;
   if (batch < 0 || num_q_heads <= 0 || head_dim <= 0) return INT8KV_E_BAD_SHAPE;
   if (!valid_float_dtype(out_dtype)) return INT8KV_E_BAD_DTYPE;
   ExchangeParams e;
@@ -689,7 +704,7 @@ int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q
   m.slab_floats = rank_floats * e.world;  // pairs per slab
   if (workspace != nullptr && workspace_bytes >= 16)
     m.status = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + int8kv_workspace_status_offset(workspace_bytes));
-  return launch_merge_exchanged(m, static_cast<cudaStream_t>(stream));
+  return launch_merge_exchanged(m, e, phase, static_cast<cudaStream_t>(stream));
 }
 
 int int8kv_selftest_bounded_wait(void* workspace, int64_t workspace_bytes, int attempts, void* stream) {

@@ -109,10 +109,11 @@ struct AttnParams {
 
 // Cross-GPU exchange of partial rows through peer-mapped buffers (sequence-parallel attention).  Every rank owns one
 // buffer of the same layout, mapped into every other rank's address space:
-//   [0, 64)     control words of the owner: {ticket of the push kernel's CTAs, epoch = pushes completed}
-//   [64, 256)   arrival flags: flag[q] = epoch of the last push of rank q whose rows have landed in this buffer
-//   [256, ...)  staging [rows, row_floats]: the owner's own partial rows before they are pushed
-//   then        2 slabs x [world, rows, row_floats] fp32, used alternately (epoch parity): slab[s][q] = rows of rank q
+//   [0, 256)    control words of the owner: {ticket of the last kernel of a step, epoch = steps completed}
+//   [256, ...)  staging [rows, row_floats] fp32: rows that a kernel leaves for a separate push
+//   then        2 slabs x [world, rows, row_floats] pairs {fp32 value, epoch}, used alternately (epoch parity):
+//               slab[s][q] = rows of rank q
+//   then        output slab [rows, out_floats] pairs (scatter form only): merged rows from their owners
 constexpr int kMaxPeers = 16;
 constexpr int kExchCtrlBytes = 256;
 struct ExchangeParams {
@@ -120,7 +121,16 @@ struct ExchangeParams {
   char* peer[kMaxPeers];  // base of every rank's buffer as mapped here; peer[rank] is the local buffer
   int64_t rows;           // B * Hq
   int row_floats;
+  // Scatter form (many ranks, rows divisible by them): rank q owns rows [q, q + 1) * rows / world.  A push sends a row
+  // to its owner only, the owner merges it and stores the merged fp32 row, again as pairs, into every rank's output
+  // slab, from which every rank writes its `out`: 1/world of the bytes of sending every row to every rank.
+  int scatter;
+  int out_floats;         // floats of an output-slab row (head_dim rounded up to 4)
 };
+// Offset of the output slab: behind the control block, the staging rows and the two slabs of row pairs.
+__host__ __device__ inline int64_t exch_out_off(int world, int64_t rows, int row_floats) {
+  return kExchCtrlBytes + rows * row_floats * 4 + 2 * static_cast<int64_t>(world) * rows * row_floats * 8;
+}
 
 struct MergeParams {
   const float* parts;  // [R, rows, row_floats]
@@ -166,7 +176,7 @@ int launch_attn_tiled_f16(const AttnParams& p, const CUtensorMap& tmK, const CUt
 int launch_attn_generic(const AttnParams& p, cudaStream_t stream);
 int launch_merge(const MergeParams& p, cudaStream_t stream);
 int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream);
-int launch_merge_exchanged(const MergeParams& p, cudaStream_t stream);
+int launch_merge_exchanged(const MergeParams& p, const ExchangeParams& e, int phase, cudaStream_t stream);
 // The merge of a rank's split-KV parts and the push of the merged rows in one kernel (head_dim % 4 == 0): p.part_out
 // names the staging area of the local exchange buffer, where rows of sequences with a single part already lie; the
 // merged rows go straight into every rank's slab.

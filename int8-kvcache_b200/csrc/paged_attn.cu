@@ -1803,11 +1803,18 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   if (p.early_trigger) grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before reading
   uint32_t push_epoch = 0;
   int64_t push_off = 0;  // byte offset of this row in slab[epoch & 1][rank] of any rank's buffer
+  int push_lo = 0, push_hi = 0;  // destination ranks
   if constexpr (PUSH) {
     const ExchangeParams& e = push.e;
     push_epoch = static_cast<uint32_t>(ld_acquire_sys(reinterpret_cast<const int*>(e.peer[e.rank]) + 1)) + 1u;
     const int64_t rank_floats = e.rows * e.row_floats;
     push_off = kExchCtrlBytes + rank_floats * 4 + (((push_epoch & 1u) * e.world + e.rank) * rank_floats + row * p.row_floats) * 8;
+    if (e.scatter) {  // the row goes to its owner only
+      push_lo = static_cast<int>(row / (e.rows / e.world));
+      push_hi = push_lo + 1;
+    } else {
+      push_hi = e.world;
+    }
   }
   if (p.seq_table != nullptr) {
     // device-planned splits: this sequence's parts are consecutive part indices; a single part was written to
@@ -1819,7 +1826,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
         for (int t = threadIdx.x; 2 * t < p.row_floats; t += blockDim.x) {
           const float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_out + row * p.row_floats) + t);
           const uint4 q = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
-          for (int r = 0; r < push.e.world; ++r) st_volatile_v4(push.e.peer[r] + push_off + 16 * t, q);
+          for (int r = push_lo; r < push_hi; ++r) st_volatile_v4(push.e.peer[r] + push_off + 16 * t, q);
         }
       }
       return;
@@ -1909,7 +1916,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
       if (t < 2 * kWarp && d0 + 2 * t < p.D) {
         const float2 v = *reinterpret_cast<const float2*>(&red_s[0][2 * t]);
         const uint4 q = make_uint4(__float_as_uint(v.x), push_epoch, __float_as_uint(v.y), push_epoch);
-        for (int r = 0; r < push.e.world; ++r) st_volatile_v4(push.e.peer[r] + push_off + 8 * d0 + 16 * t, q);
+        for (int r = push_lo; r < push_hi; ++r) st_volatile_v4(push.e.peer[r] + push_off + 8 * d0 + 16 * t, q);
       }
       __syncthreads();  // before the next chunk reuses the slot
     }
@@ -1917,7 +1924,7 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
   if constexpr (PUSH) {
     if (threadIdx.x == 0) {
       const float l = den > 0.f ? top + __logf(den) : -INFINITY;
-      for (int r = 0; r < push.e.world; ++r)
+      for (int r = push_lo; r < push_hi; ++r)
         st_volatile_v2(push.e.peer[r] + push_off + 8 * p.D, make_uint2(__float_as_uint(l), push_epoch));
     }
   } else if (p.part_out != nullptr && threadIdx.x == 0) {
@@ -1939,6 +1946,23 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 // merge of step e - 1.  The epoch lives in the local buffer and is advanced by the merge (its last CTA), so a
 // captured graph replays.
 // ---------------------------------------------------------------------------------------------
+// End of a step's last kernel: the ticket; the last CTA advances the epoch for the next step's kernels.  That grid
+// does not wait for the push before it on the stream: whoever waits for it may find that push still waiting for the
+// other GPUs to acknowledge its stores (measured: 8 us per step on two GPUs), but never reading or storing locally,
+// because every row of the local push has arrived, and the next push writes the other slab.
+__device__ __forceinline__ void step_ticket(int* ctrl, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const int ticket = atomicAdd(ctrl, 1);
+    if (ticket == static_cast<int>(gridDim.x) - 1) {
+      ctrl[0] = 0;
+      __threadfence();
+      st_release_sys(ctrl + 1, static_cast<int>(epoch));
+    }
+  }
+}
+
 // Push of this rank's staged rows into slab[epoch & 1][rank] of EVERY rank's buffer: plain 16-byte stores of two
 // pairs each to peer-mapped memory (no TMA, no multicast, no fence).  Nothing here waits for another GPU.
 __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams e) {
@@ -1954,7 +1978,12 @@ __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const float2 v = __ldcg(src + i);
     const uint4 q = make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
-    for (int r = 0; r < e.world; ++r) st_volatile_v4(e.peer[r] + dst_off + 16 * i, q);
+    if (e.scatter) {  // the row goes to its owner only
+      const int owner = static_cast<int>((2 * i / e.row_floats) / (e.rows / e.world));
+      st_volatile_v4(e.peer[owner] + dst_off + 16 * i, q);
+    } else {
+      for (int r = 0; r < e.world; ++r) st_volatile_v4(e.peer[r] + dst_off + 16 * i, q);
+    }
   }
 }
 
@@ -1967,14 +1996,36 @@ __global__ void __launch_bounds__(256) exchange_push_kernel(const ExchangeParams
 // about a second in all); a rank that never arrives is reported in the status word and the row is left unwritten.
 constexpr int kExchMergeWarps = 4;
 constexpr int kExchChunk = 8;  // ranks whose rows a lane holds at once (two 16-byte vectors each)
-__global__ void __launch_bounds__(kExchMergeWarps * kWarp) merge_exchanged_kernel(const MergeParams p) {
+// The kernel's piece of an output row to `out`, in its type and strides.
+__device__ __forceinline__ void store_out4(const MergeParams& p, int b, int hq, int d, const float4& a) {
+  const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
+  if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
+      ((reinterpret_cast<uintptr_t>(p.out) + 2 * (ob + d)) & 7u) == 0) {
+    uint2 v;
+    v.x = pack_bf162(a.x, a.y);
+    v.y = pack_bf162(a.z, a.w);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + ob + d) = v;
+  } else {
+    store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
+    if (d + 1 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
+    if (d + 2 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
+    if (d + 3 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
+  }
+}
+
+// SCATTER: the grid covers the rows this rank owns; the merged fp32 row is not written to `out` but, as pairs, into
+// the output slab of EVERY rank, and gather_outputs_kernel (next on the stream) finishes the step.
+template <bool SCATTER>
+__global__ void __launch_bounds__(kExchMergeWarps * kWarp) merge_exchanged_kernel(const MergeParams p, const ExchangeParams e) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * kExchMergeWarps + warp;
+  const int64_t local = static_cast<int64_t>(blockIdx.x) * kExchMergeWarps + warp;
+  const int64_t owned = SCATTER ? p.rows / e.world : p.rows;
+  const int64_t row = SCATTER ? e.rank * owned + local : local;
   int* ctrl = const_cast<int*>(p.exchange_ctrl);
-  // The epoch is only advanced by this kernel's last CTA, after every CTA has read it here.
+  // The epoch is only advanced by the last CTA of the step's last kernel, after every CTA has read it.
   const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(ctrl + 1)) + 1u;
   grid_launch_dependents();  // the next kernel may be scheduled; it waits for this grid before it reads
-  if (row < p.rows) {
+  if (local < owned) {
     const int R = p.exchange_world;
     const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
     const int64_t rank_stride = p.rows * p.row_floats * 8;
@@ -2048,36 +2099,62 @@ __global__ void __launch_bounds__(kExchMergeWarps * kWarp) merge_exchanged_kerne
       a.y = (acc[0].y + acc[1].y + acc[2].y + acc[3].y) * inv;
       a.z = (acc[0].z + acc[1].z + acc[2].z + acc[3].z) * inv;
       a.w = (acc[0].w + acc[1].w + acc[2].w + acc[3].w) * inv;
-      const int64_t ob = b * p.o_st[0] + hq * p.o_st[1];
-      if (p.out_dtype == INT8KV_BF16 && p.o_st[2] == 1 && d + 3 < p.D &&
-          ((reinterpret_cast<uintptr_t>(p.out) + 2 * (ob + d)) & 7u) == 0) {
-        uint2 v;
-        v.x = pack_bf162(a.x, a.y);
-        v.y = pack_bf162(a.z, a.w);
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + ob + d) = v;
+      if constexpr (SCATTER) {
+        const int64_t off = exch_out_off(e.world, e.rows, e.row_floats) + (row * e.out_floats + d) * 8;
+        const uint4 lo = make_uint4(__float_as_uint(a.x), epoch, __float_as_uint(a.y), epoch);
+        const uint4 hi = make_uint4(__float_as_uint(a.z), epoch, __float_as_uint(a.w), epoch);
+        for (int r = 0; r < e.world; ++r) {
+          st_volatile_v4(e.peer[r] + off, lo);
+          st_volatile_v4(e.peer[r] + off + 16, hi);
+        }
       } else {
-        store_from_float(p.out, p.out_dtype, ob + (d + 0) * p.o_st[2], a.x);
-        if (d + 1 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 1) * p.o_st[2], a.y);
-        if (d + 2 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 2) * p.o_st[2], a.z);
-        if (d + 3 < p.D) store_from_float(p.out, p.out_dtype, ob + (d + 3) * p.o_st[2], a.w);
+        store_out4(p, b, hq, d, a);
       }
     }
     if (!ok && lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
   }
-  // The ticket; the last CTA advances the epoch for the next step's push and merge.  This grid does not wait for the
-  // push before it on the stream: whoever waits for this grid may find that push still waiting for the other GPUs to
-  // acknowledge its stores (measured: 8 us per step on two GPUs), but never reading or storing locally, because every
-  // row of the local push has arrived here, and the next push writes the other slab.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const int ticket = atomicAdd(ctrl, 1);
-    if (ticket == static_cast<int>(gridDim.x) - 1) {
-      ctrl[0] = 0;
-      __threadfence();
-      st_release_sys(ctrl + 1, static_cast<int>(epoch));
+  if constexpr (!SCATTER) step_ticket(ctrl, epoch);
+}
+
+// Last kernel of a step in the scatter form: every rank takes every merged row from its output slab (one warp per
+// row, polling as above, bounded) and writes it to `out`.
+__global__ void __launch_bounds__(kExchMergeWarps * kWarp) gather_outputs_kernel(const MergeParams p, const ExchangeParams e) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kExchMergeWarps + warp;
+  int* ctrl = const_cast<int*>(p.exchange_ctrl);
+  const uint32_t epoch = static_cast<uint32_t>(ld_acquire_sys(ctrl + 1)) + 1u;
+  grid_launch_dependents();
+  if (row < p.rows) {
+    const int b = static_cast<int>(row / p.Hq), hq = static_cast<int>(row - static_cast<int64_t>(b) * p.Hq);
+    const char* base = e.peer[e.rank] + exch_out_off(e.world, e.rows, e.row_floats) + row * e.out_floats * 8;
+    uint32_t budget = kFlagSpinLimit;
+    bool ok = true;
+    for (int d0 = 0; ok && d0 < p.D; d0 += 4 * kWarp) {
+      const int d = d0 + 4 * lane;
+      const bool live = d < p.D;
+      uint4 lo = make_uint4(0u, epoch, 0u, epoch), hi = lo;  // lanes beyond the row count as arrived
+      if (live) {
+        lo = ld_volatile_v4(base + 8 * d);
+        hi = ld_volatile_v4(base + 8 * d + 16);
+      }
+      for (;;) {
+        const bool here = lo.y == epoch && lo.w == epoch && hi.y == epoch && hi.w == epoch;
+        if (__all_sync(kFull, here)) break;
+        if (budget == 0) {
+          ok = false;
+          break;
+        }
+        --budget;
+        __nanosleep(budget + 64 > kFlagSpinLimit ? 50 : 1000);
+        if (lo.y != epoch || lo.w != epoch) lo = ld_volatile_v4(base + 8 * d);
+        if (hi.y != epoch || hi.w != epoch) hi = ld_volatile_v4(base + 8 * d + 16);
+      }
+      if (ok && live)
+        store_out4(p, b, hq, d, make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z)));
     }
+    if (!ok && lane == 0 && p.status != nullptr) atomicOr(p.status, INT8KV_DEV_WAIT_TIMEOUT);
   }
+  step_ticket(ctrl, epoch);
 }
 
 int launch_exchange_push(const ExchangeParams& e, cudaStream_t stream) {
@@ -2316,10 +2393,22 @@ int launch_merge_push(const MergeParams& p_in, const ExchangeParams& e, cudaStre
   return launch_pdl(merge_partials_kernel<true>, static_cast<unsigned>(p.rows), kMergeWarps * kWarp, 0, stream, p, t);
 }
 
-int launch_merge_exchanged(const MergeParams& p, cudaStream_t stream) {
+// phase: INT8KV_EXCHANGE_BOTH_PHASES, or one of the two halves of the scatter form (without the scatter form the merge
+// phase is the whole step and the gather phase nothing)
+int launch_merge_exchanged(const MergeParams& p, const ExchangeParams& e, int phase, cudaStream_t stream) {
   if (p.rows <= 0) return INT8KV_OK;
   const unsigned grid = static_cast<unsigned>((p.rows + kExchMergeWarps - 1) / kExchMergeWarps);
-  return launch_pdl(merge_exchanged_kernel, grid, kExchMergeWarps * kWarp, 0, stream, p);
+  if (!e.scatter) {
+    if (phase == INT8KV_EXCHANGE_GATHER_PHASE) return INT8KV_OK;
+    return launch_pdl(merge_exchanged_kernel<false>, grid, kExchMergeWarps * kWarp, 0, stream, p, e);
+  }
+  if (phase != INT8KV_EXCHANGE_GATHER_PHASE) {
+    const int64_t owned = p.rows / e.world;
+    const unsigned own_grid = static_cast<unsigned>((owned + kExchMergeWarps - 1) / kExchMergeWarps);
+    const int rc = launch_pdl(merge_exchanged_kernel<true>, own_grid, kExchMergeWarps * kWarp, 0, stream, p, e);
+    if (rc != INT8KV_OK || phase == INT8KV_EXCHANGE_MERGE_PHASE) return rc;
+  }
+  return launch_pdl(gather_outputs_kernel, grid, kExchMergeWarps * kWarp, 0, stream, p, e);
 }
 
 }  // namespace int8kv

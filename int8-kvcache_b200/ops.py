@@ -746,19 +746,20 @@ def int8_paged_attention_partial_push(
 
 
 def merge_exchanged(exchange, batch: int, num_q_heads: int, head_dim: int, dtype=torch.bfloat16,
-                    out: Optional[torch.Tensor] = None, device=None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, device=None, phase: int = _lib.EXCHANGE_BOTH_PHASES) -> torch.Tensor:
     """Wait (bounded, on the device) for every rank's pushed rows of the current step and merge them -> [B, Hq, D].
-    A wait that runs out is reported through device_status()."""
+    A wait that runs out is reported through device_status().  phase: one of the two halves of the step
+    (_lib.EXCHANGE_MERGE_PHASE, then _lib.EXCHANGE_GATHER_PHASE with the same `out`) instead of both."""
     lib = _require_lib()
     if out is None:
         out = torch.empty((batch, num_q_heads, head_dim), device=device, dtype=dtype)
     assert out.is_cuda and out.dtype in _FLOAT_CODES and out.shape == (batch, num_q_heads, head_dim)
     ws = _workspace(out.device, 16)
-    rc = lib.int8kv_merge_exchanged(
+    rc = lib.int8kv_merge_exchanged_phase(
         C.byref(exchange), batch, num_q_heads, head_dim, out.data_ptr(), _FLOAT_CODES[out.dtype],
-        _lib.i64(out.stride()), ws.data_ptr(), ws.numel(), _stream_ptr(out.device),
+        _lib.i64(out.stride()), ws.data_ptr(), ws.numel(), int(phase), _stream_ptr(out.device),
     )
-    _lib.check("int8kv_merge_exchanged", rc)
+    _lib.check("int8kv_merge_exchanged_phase", rc)
     return out
 
 

@@ -158,9 +158,9 @@ def test_argument_validation_returns_codes_before_any_launch(lib):
     assert layers_call(arr, 2) == _lib.E_NULLPTR and failed.value == 0
     # peer exchange: layout size, and descriptors that cannot be right are refused before anything is launched
     rows = 32 * 64 * 132 * 4
-    assert lib.int8kv_exchange_bytes(8, 32, 64, 128) == 256 + rows * 33  # staging + 2 slabs x 8 ranks x 8-byte pairs
+    assert lib.int8kv_exchange_bytes(8, 32, 64, 128) == 256 + rows * 33 + 32 * 64 * 128 * 8  # staging + 2 slabs x 8 ranks x 8-byte pairs + output slab
     assert lib.int8kv_exchange_bytes(17, 32, 64, 128) == -1 and lib.int8kv_exchange_bytes(0, 32, 64, 128) == -1
-    ex = _lib.Exchange(2, 0, (C.c_void_p * 16)(), 256 + 3 * 28 * 132 * 4 * 9)
+    ex = _lib.Exchange(2, 0, (C.c_void_p * 16)(), 256 + 3 * 28 * 132 * 4 * 9 + 3 * 28 * 128 * 8)
     merge = lambda e: lib.int8kv_merge_exchanged(C.byref(e), 3, 28, 128, None, 0, st3, None, 0, None)
     assert merge(ex) == _lib.E_NULLPTR  # no buffers
     ex.peer_buffers[0], ex.peer_buffers[1] = 4096, 8192 + 16

@@ -102,12 +102,13 @@ def test_many_ragged_sequences_through_the_exchange(kv, workloads, num_splits):
     assert kv.device_status() == 0
 
 
-@pytest.mark.parametrize("world,num_splits", [(2, None), (9, None), (2, "planned"), (3, 1), (2, 6)])
+@pytest.mark.parametrize("world,num_splits", [(2, None), (9, None), (2, "planned"), (3, 1), (2, 6), (8, None), (8, 1), (16, None)])
 def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads, world, num_splits):
     """Several "ranks" on one device, run one after the other on one stream: all of them push into all buffers (the
     last rank first), then each merges (its wait finds everything there).  All must return what merge_partials gives
     for the ranks' rows stacked, bit for bit, eagerly and replayed as a CUDA graph.  Nine ranks make the merge take
-    the other ranks' rows in two batches."""
+    the other ranks' rows in two batches; eight and sixteen ranks (the 112 rows divide by them) use the scatter form:
+    a row goes to its owner only, the owner's merged row to every rank's output slab, and a last kernel writes out."""
     lib_mod, sh = package("_lib"), package("sharding")
     lens = [2000, 333, 64, 1]
     case, kc, vc = _case(workloads, lens, seed=77)
@@ -140,8 +141,10 @@ def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workl
         for r in reversed(range(world)):
             kv.int8_paged_attention_partial_push(*rank_args[r][0], exs[r], max_seq_len=rank_args[r][1],
                                                  num_splits=num_splits)
-        for r in range(world):
-            kv.merge_exchanged(exs[r], len(lens), 28, 128, out=outs[r])
+        # one phase for all ranks, then the other: in the scatter form a rank's second phase needs every owner's first
+        for phase in (lib_mod.EXCHANGE_MERGE_PHASE, lib_mod.EXCHANGE_GATHER_PHASE):
+            for r in range(world):
+                kv.merge_exchanged(exs[r], len(lens), 28, 128, out=outs[r], phase=phase)
 
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
