@@ -352,7 +352,7 @@ int int8kv_merge_partials(const float* parts, int num_parts, int batch, int num_
  *   - int8kv_merge_exchanged, enqueued behind it on the same stream, waits until every rank's rows of the current
  *     step have arrived and merges them from LOCAL memory.  The wait is bounded (about a second); if it runs out,
  *     INT8KV_DEV_WAIT_TIMEOUT is set in the status word of `workspace` (optional) and the output is left unwritten.
- *     (With 8 ranks or more the rows are scattered to owner ranks and the merged rows gathered from them instead
+ *     (With 4 ranks or more the rows are scattered to owner ranks and the merged rows gathered from them instead
  *     of every row going to every rank; see int8kv_merge_exchanged_phase.  The calls stay the same.)
  * Both keep their step count on the device, so the pair can be captured in a CUDA graph and replayed.  Every rank must
  * make the same sequence of push / merge pairs; buffers alternate between two slabs so that a fast rank's next step
@@ -384,11 +384,11 @@ int int8kv_merge_exchanged(const int8kv_exchange* exchange, int batch, int num_q
                            void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
- * The two halves of int8kv_merge_exchanged, for hosts that put other work between them.  With 8 ranks or more (and a
+ * The two halves of int8kv_merge_exchanged, for hosts that put other work between them.  With 4 ranks or more (and a
  * row count B * Hq that divides by them) the exchange does not send every row to every rank: a push sends a row to one
  * owner rank, the owner merges its rows (INT8KV_EXCHANGE_MERGE_PHASE) and stores the merged fp32 rows into every
- * rank's buffer, and every rank then writes `out` from what the owners sent (INT8KV_EXCHANGE_GATHER_PHASE) — one
- * eighth of the bytes on eight GPUs.  With fewer ranks the merge phase is the whole step and the gather phase does
+ * rank's buffer, and every rank then writes `out` from what the owners sent (INT8KV_EXCHANGE_GATHER_PHASE) — a
+ * quarter of the bytes on eight GPUs.  With fewer ranks the merge phase is the whole step and the gather phase does
  * nothing.  INT8KV_EXCHANGE_BOTH_PHASES is int8kv_merge_exchanged.  Every rank must run both phases, in this order,
  * with the same arguments.
  */

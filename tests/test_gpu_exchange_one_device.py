@@ -102,12 +102,14 @@ def test_many_ragged_sequences_through_the_exchange(kv, workloads, num_splits):
     assert kv.device_status() == 0
 
 
-@pytest.mark.parametrize("world,num_splits", [(2, None), (9, None), (2, "planned"), (3, 1), (2, 6), (8, None), (8, 1), (16, None)])
+@pytest.mark.parametrize("world,num_splits", [(2, None), (9, None), (2, "planned"), (3, 1), (2, 6), (8, None), (8, 1),
+                                              (16, None), (4, "planned"), (7, 4)])
 def test_emulated_ranks_equal_the_gathered_merge_and_replay_as_a_graph(kv, workloads, world, num_splits):
     """Several "ranks" on one device, run one after the other on one stream: all of them push into all buffers (the
     last rank first), then each merges (its wait finds everything there).  All must return what merge_partials gives
     for the ranks' rows stacked, bit for bit, eagerly and replayed as a CUDA graph.  Nine ranks make the merge take
-    the other ranks' rows in two batches; eight and sixteen ranks (the 112 rows divide by them) use the scatter form:
+    the other ranks' rows in two batches; four, seven, eight and sixteen ranks (the 112 rows divide by them) use the
+    scatter form:
     a row goes to its owner only, the owner's merged row to every rank's output slab, and a last kernel writes out."""
     lib_mod, sh = package("_lib"), package("sharding")
     lens = [2000, 333, 64, 1]
