@@ -1,0 +1,40 @@
+"""bench.py --impl reference on the host cores: the one arm of the bench that runs without a GPU.  Holds its JSON
+line to the contract the driver reads (same metric, unit, config.workload as the GPU arm; impl, cpu_baseline, e2e)."""
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent.parent
+
+
+def _line(*extra):
+    out = subprocess.run([sys.executable, str(REPO / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0",
+                          *extra], capture_output=True, text=True, timeout=300, cwd=str(REPO))
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.strip().splitlines() if l.startswith("{")]
+    assert len(lines) == 1  # ONE JSON line
+    return json.loads(lines[0])
+
+
+def test_reference_arm_prints_the_contract_line():
+    d = _line()
+    assert d["impl"] == "reference" and d["metric"] == "int8_paged_decode_attn_achieved_hbm_gbps" and d["unit"] == "GB/s"
+    assert d["higher_is_better"] is True and d["vs_baseline"] is None and d["data"] == "synthetic"
+    assert d["n_gpus"] == 1 and d["steps"] == 1 and d["value"] > 0 and d["ms_per_step"] > 0
+    assert d["config"]["workload"].startswith("c4:") and d["config"]["batch"] == 256 and d["config"]["layers"] == 28
+    cb = d["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == d["value"] and "sequences" in cb["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_reference_arm_under_a_launcher_prints_on_rank_zero_only():
+    """Launched as rank 1 of 2 (the environment a launcher sets), the arm does no work and prints nothing."""
+    import os
+
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29517")
+    out = subprocess.run([sys.executable, str(REPO / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                          "--warmup", "0"], capture_output=True, text=True, timeout=300, cwd=str(REPO), env=env)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.strip() == ""
