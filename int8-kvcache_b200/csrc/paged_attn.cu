@@ -1935,7 +1935,8 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 // ---------------------------------------------------------------------------------------------
 // Sequence-parallel exchange over NVLink: partial rows travel as (value, epoch) pairs.
 //
-// A rank's buffer is [256 B control: ticket, epoch | staging rows, fp32 | 2 slabs x world x rows x row_floats pairs].
+// A rank's buffer is [256 B control: ticket, epoch | staging rows, fp32 | 2 slabs x world x rows x row_floats pairs |
+// output slab, rows x out_floats pairs].
 // Every float of a row crosses as an 8-byte pair {value, epoch of the step}; a pair is written by one store (or
 // by one half of a 16-byte store) and therefore arrives whole, so the receiver needs no flag behind the data and
 // the sender no system-scope fence before such a flag: it reads a pair, and the pair is this step's as soon as
@@ -1943,8 +1944,11 @@ __global__ void __launch_bounds__(kMergeWarps * kWarp) merge_partials_kernel(con
 // push alone then cost 19 us per step on two GPUs, most of it fences.)  The slab alternates with the parity of
 // the epoch, so a fast rank's next step cannot overwrite what a slow rank is still merging: a rank pushes step
 // e + 1 only after its own merge of step e, which needed every rank's push of step e, which followed that rank's
-// merge of step e - 1.  The epoch lives in the local buffer and is advanced by the merge (its last CTA), so a
-// captured graph replays.
+// merge of step e - 1.  The epoch lives in the local buffer and is advanced by the last CTA of the step's last
+// kernel, so a captured graph replays.  From four ranks on a row is not sent to every rank but to one owner, which
+// sends the merged row to every rank's output slab (ExchangeParams::scatter); that slab needs no second copy: an
+// owner can only write step e + 1 into it after it has every rank's push of step e + 1, which follows that rank's
+// last kernel of step e.
 // ---------------------------------------------------------------------------------------------
 // End of a step's last kernel: the ticket; the last CTA advances the epoch for the next step's kernels.  That grid
 // does not wait for the push before it on the stream: whoever waits for it may find that push still waiting for the
