@@ -1021,8 +1021,8 @@ def leg_sequence_parallel(ctx, hq, hkv, seq_lens):
             "partial_rows": a_ms * 1e3, "partial_rows_and_push": b_ms * 1e3,
             "whole_step": result["peer_stores"]["us_per_step"],
             "what": "max over ranks of: the rank's attention and the merge of its parts into rows; the same followed by "
-                    "the push into every rank's buffer (no rank waits for flags); the whole step with the flag wait and "
-                    "the merge of all ranks' rows"}
+                    "the push (to every rank, or from four ranks on to the rows' owner ranks; nobody waits); the whole step with "
+                    "the kernels that poll for the other ranks' rows, merge them and write the output"}
     status, = ctx.reduce([kv.device_status(device)], "max")
     result["device_status"] = int(status)
     result["collective"] = {"bytes_per_rank": len(seq_lens) * hq * 132 * 4,
