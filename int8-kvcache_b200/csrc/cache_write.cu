@@ -43,7 +43,7 @@ __device__ __noinline__ int quant1_exact(float x, float scale) {
 //  * no separate test for huge quotients.  For q >= 2^22 the bits of t lie above those of 1.5 * 2^23 by at least
 //    2^22 and the difference saturates to +127, as it must; for q <= -2^22 they lie below (t <= 2^23, down to zero)
 //    and it saturates to -127; the one failure is t < 0, whose sign bit would wrap the integer subtraction, so
-//    the bits are clamped at zero first (one integer max).  Infinities and NaN make q - n NaN and take the exact
+//    the bits are clamped from below first (one integer max).  Infinities and NaN make q - n NaN and take the exact
 //    path through the comparison itself.
 //  * the rare branch is out of line (quant1_exact).
 __device__ __forceinline__ void quant2_stream(float x0, float x1, float scale, float2 rscale2, int& n0, int& n1) {
@@ -51,10 +51,22 @@ __device__ __forceinline__ void quant2_stream(float x0, float x1, float scale, f
   const float2 t = __fadd2_rn(q, make_float2(kRoundMagic, kRoundMagic));
   const float2 n = __fadd2_rn(t, make_float2(-kRoundMagic, -kRoundMagic));
   const float2 d = __ffma2_rn(n, make_float2(-1.f, -1.f), q);  // q - n, exact
-  n0 = max(__float_as_int(t.x), 0) - kRoundMagicBits;  // (a fused add-then-max would wrap for -1.5 * 2^23 < t < 0)
-  n1 = max(__float_as_int(t.y), 0) - kRoundMagicBits;
+  // The bits are clamped from below at those of 1.5 * 2^23 - 127 before the subtraction: -127 is the least result
+  // (also for t < 0, whose sign bit would wrap the subtraction), so packing only has to saturate at +127 and the
+  // four-byte maximum that raises -128 to -127 is not needed.  (A fused add-then-max would wrap for
+  // -1.5 * 2^23 < t < 0.)
+  n0 = max(__float_as_int(t.x), kRoundMagicBits - 127) - kRoundMagicBits;
+  n1 = max(__float_as_int(t.y), kRoundMagicBits - 127) - kRoundMagicBits;
   if (!(fabsf(d.x) < 0.5f - 6.2e-5f)) n0 = quant1_exact(x0, scale);
   if (!(fabsf(d.y) < 0.5f - 6.2e-5f)) n1 = quant1_exact(x1, scale);
+}
+
+// Four integers >= -127 saturated at +127 and packed little-endian.
+__device__ __forceinline__ uint32_t pack4_sat_upper(int n0, int n1, int n2, int n3) {
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(n3), "r"(n2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(n1), "r"(n0), "r"(hi));
+  return w;
 }
 
 // Sixteen consecutive elements as raw 16-byte vectors (requested before anything depends on them) ...
@@ -76,7 +88,7 @@ struct Raw16 {
       int n[4];
       quant2_stream(to_f32<T>(e[4 * i]), to_f32<T>(e[4 * i + 1]), scale, r2, n[0], n[1]);
       quant2_stream(to_f32<T>(e[4 * i + 2]), to_f32<T>(e[4 * i + 3]), scale, r2, n[2], n[3]);
-      w[i] = pack4_sat(n[0], n[1], n[2], n[3]);
+      w[i] = pack4_sat_upper(n[0], n[1], n[2], n[3]);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
   }
