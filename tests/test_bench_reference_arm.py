@@ -38,3 +38,16 @@ def test_reference_arm_under_a_launcher_prints_on_rank_zero_only():
                           "--warmup", "0"], capture_output=True, text=True, timeout=300, cwd=str(REPO), env=env)
     assert out.returncode == 0, out.stderr[-2000:]
     assert out.stdout.strip() == ""
+
+
+def test_reference_arm_under_torchrun_prints_one_line_for_the_job():
+    """Two ranks launched the way the driver launches them: one JSON line in all, with the job's rank count."""
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29543", str(REPO / "bench.py"), "--impl",
+                          "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=str(REPO))
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.strip().splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["config"]["workload"].startswith("c4:")
